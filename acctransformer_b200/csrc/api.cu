@@ -1,0 +1,396 @@
+// C-ABI entry points of libacct_b200.so: argument validation (the role the reference's Python
+// checks and its C++ InferShape play), tensor-map construction and kernel launches.
+#include <mutex>
+#include <stdarg.h>
+
+#include "common.cuh"
+#include "fa_kernels.cuh"
+
+namespace acct {
+
+// ---------------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------------
+char* last_error_buf() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buf(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int fail_cuda(cudaError_t e, const char* what) {
+  return fail(ACCT_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+// ---------------------------------------------------------------------------------------------
+// per-device state
+// ---------------------------------------------------------------------------------------------
+__device__ unsigned int g_status_word = 0;
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_mutex;
+struct PerDevice {
+  bool ready = false;
+  int rc = 0;
+  DeviceInfo info{};
+  unsigned int* status = nullptr;
+};
+PerDevice g_dev[kMaxDevices];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int init_device(PerDevice** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ACCT_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(ACCT_ERR_NO_DEVICE, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  PerDevice& d = g_dev[dev];
+  if (!d.ready) {
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetDeviceProperties");
+    d.info.sm_count = prop.multiProcessorCount;
+    d.info.cc_major = prop.major;
+    d.info.cc_minor = prop.minor;
+    d.info.max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+    if (prop.major != 10) {
+      d.rc = ACCT_ERR_NO_DEVICE;
+    } else {
+      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_status_word);
+      if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(status)");
+      if (g_encode == nullptr) {
+        cudaDriverEntryPointQueryResult q;
+        void* fn = nullptr;
+        e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || fn == nullptr) return fail(ACCT_ERR_CUDA, "cuTensorMapEncodeTiled unavailable");
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+      }
+    }
+    d.ready = true;
+  }
+  if (d.rc != 0)
+    return fail(d.rc, "device %d is sm_%d%d; this library is built for sm_100a only", dev, d.info.cc_major,
+                d.info.cc_minor);
+  *out = &d;
+  return 0;
+}
+}  // namespace
+
+int device_info(DeviceInfo* out) {
+  PerDevice* d = nullptr;
+  int rc = init_device(&d);
+  if (rc) return rc;
+  *out = d->info;
+  return 0;
+}
+
+unsigned int* device_status_ptr() {
+  PerDevice* d = nullptr;
+  if (init_device(&d)) return nullptr;
+  return d->status;
+}
+
+int make_tmap_4d(CUtensorMap* out, const TensorDesc4& t, int box_rows) {
+  cuuint64_t dims[4] = {(cuuint64_t)t.dims[0], (cuuint64_t)t.dims[1], (cuuint64_t)t.dims[2], (cuuint64_t)t.dims[3]};
+  cuuint64_t strides[3] = {(cuuint64_t)t.strides[0] * 2, (cuuint64_t)t.strides[1] * 2, (cuuint64_t)t.strides[2] * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = g_encode(out, t.dtype == ACCT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        4, const_cast<void*>(t.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ACCT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// validation
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kMaxHeadDimCell = 256;   // the reference cell's limit (nn/layer/flash_attention.py:26,105-106)
+constexpr int kMaxHeadDimKernel = 128; // what the tcgen05 kernels here are instantiated for
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_strides(const char* name, const int64_t s[3], int64_t S, int64_t N, int64_t D, int64_t out[3]) {
+  out[2] = packed_or(s[2], D);
+  out[1] = packed_or(s[1], S * D);
+  out[0] = packed_or(s[0], N * S * D);
+  for (int i = 0; i < 3; ++i) {
+    if (out[i] <= 0) return fail(ACCT_ERR_SHAPE, "%s stride %d must be positive", name, i);
+    if (out[i] % 8 != 0) return fail(ACCT_ERR_ALIGN, "%s stride %d (%lld elements) is not a multiple of 8", name, i, (long long)out[i]);
+  }
+  if (out[2] < D) return fail(ACCT_ERR_SHAPE, "%s sequence stride smaller than head_dim", name);
+  return 0;
+}
+
+int check_head_dim(int D) {
+  if (D <= 0 || D > kMaxHeadDimCell) return fail(ACCT_ERR_UNSUPPORTED_D, "head_dim %d outside (0, %d]", D, kMaxHeadDimCell);
+  if (D % 8 != 0) return fail(ACCT_ERR_UNSUPPORTED_D, "head_dim %d is not a multiple of 8", D);
+  if (D > kMaxHeadDimKernel) return fail(ACCT_ERR_UNSUPPORTED_D, "head_dim %d > %d is not built in this library", D, kMaxHeadDimKernel);
+  return 0;
+}
+
+struct Strides {
+  int64_t q[3], k[3], v[3], o[3];
+};
+
+int validate_fa(const acct_fa_args* a, Strides* st) {
+  if (a == nullptr) return fail(ACCT_ERR_NULL, "args is NULL");
+  if (a->dtype != ACCT_F16 && a->dtype != ACCT_BF16) return fail(ACCT_ERR_DTYPE, "dtype must be ACCT_F16 or ACCT_BF16");
+  if (a->B <= 0 || a->N <= 0 || a->S_q <= 0 || a->S_k <= 0) return fail(ACCT_ERR_SHAPE, "B, N, S_q, S_k must be positive");
+  if (static_cast<int64_t>(a->B) * a->N > 65535) return fail(ACCT_ERR_SHAPE, "B*N = %lld exceeds 65535", (long long)a->B * a->N);
+  int rc = check_head_dim(a->D);
+  if (rc) return rc;
+  if (!a->q || !a->k || !a->v || !a->o) return fail(ACCT_ERR_NULL, "q, k, v, o must be non-NULL");
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o))
+    return fail(ACCT_ERR_ALIGN, "q, k, v, o must be 16-byte aligned");
+  if ((rc = check_strides("q", a->q_stride, a->S_q, a->N, a->D, st->q))) return rc;
+  if ((rc = check_strides("k", a->k_stride, a->S_k, a->N, a->D, st->k))) return rc;
+  if ((rc = check_strides("v", a->v_stride, a->S_k, a->N, a->D, st->v))) return rc;
+  if ((rc = check_strides("o", a->o_stride, a->S_q, a->N, a->D, st->o))) return rc;
+  if (!(a->scale > 0.f) || !(a->scale < 1e30f)) return fail(ACCT_ERR_SHAPE, "scale must be a positive finite number");
+  if (a->prev_block_num < 0 || a->next_block_num < 0) return fail(ACCT_ERR_SHAPE, "prev/next_block_num must be >= 0");
+  switch (a->mask_kind) {
+    case ACCT_MASK_NONE: break;
+    case ACCT_MASK_FULL:
+      if (!a->attn_mask) return fail(ACCT_ERR_NULL, "attn_mask is NULL for ACCT_MASK_FULL");
+      if (a->mask_batch != 1 && a->mask_batch != a->B) return fail(ACCT_ERR_SHAPE, "mask_batch must be 1 or B");
+      break;
+    case ACCT_MASK_TILE128:
+      if (!a->attn_mask) return fail(ACCT_ERR_NULL, "attn_mask is NULL for ACCT_MASK_TILE128");
+      break;
+    default: return fail(ACCT_ERR_SHAPE, "unknown mask_kind %d", a->mask_kind);
+  }
+  if (a->mask_kind != ACCT_MASK_NONE && a->mask_dtype != ACCT_F16 && a->mask_dtype != ACCT_BF16 && a->mask_dtype != ACCT_U8)
+    return fail(ACCT_ERR_DTYPE, "attn_mask dtype must be F16, BF16 or U8");
+  if (a->dropout_mask) {
+    if (a->dropout_dtype != ACCT_F16 && a->dropout_dtype != ACCT_BF16 && a->dropout_dtype != ACCT_U8)
+      return fail(ACCT_ERR_DTYPE, "dropout_mask dtype must be U8, F16 or BF16");
+    if (a->dropout_dtype == ACCT_U8 && !(a->keep_prob > 0.f && a->keep_prob <= 1.f))
+      return fail(ACCT_ERR_SHAPE, "keep_prob must be in (0, 1]");
+  }
+  if (a->alibi && a->alibi_slopes) return fail(ACCT_ERR_SHAPE, "give either alibi or alibi_slopes, not both");
+  return 0;
+}
+
+ScoreMods make_mods(const acct_fa_args* a) {
+  ScoreMods m;
+  m.causal = a->causal ? 1 : 0;
+  m.prev_block_num = a->prev_block_num >= ACCT_BAND_UNBOUNDED ? ACCT_BAND_UNBOUNDED : a->prev_block_num;
+  m.next_block_num = a->next_block_num >= ACCT_BAND_UNBOUNDED ? ACCT_BAND_UNBOUNDED : a->next_block_num;
+  m.mask_kind = a->mask_kind;
+  m.mask_dtype = a->mask_dtype;
+  m.mask_batch = a->mask_batch;
+  m.mask = a->mask_kind == ACCT_MASK_NONE ? nullptr : a->attn_mask;
+  m.drop = a->dropout_mask;
+  m.drop_dtype = a->dropout_dtype;
+  m.drop_scale = (a->dropout_mask && a->dropout_dtype == ACCT_U8) ? 1.0f / a->keep_prob : 1.0f;
+  m.alibi = a->alibi;
+  m.alibi_slopes = a->alibi_slopes;
+  m.seq_lens = a->seq_lens;
+  return m;
+}
+
+int make_qkv_maps(const acct_fa_args* a, const Strides& st, CUtensorMap* mq, CUtensorMap* mk, CUtensorMap* mv) {
+  TensorDesc4 t;
+  t.dtype = a->dtype;
+  int rc;
+  t.ptr = a->q; t.dims[0] = a->D; t.dims[1] = a->S_q; t.dims[2] = a->N; t.dims[3] = a->B;
+  t.strides[0] = st.q[2]; t.strides[1] = st.q[1]; t.strides[2] = st.q[0];
+  if ((rc = make_tmap_4d(mq, t, kTile))) return rc;
+  t.ptr = a->k; t.dims[1] = a->S_k;
+  t.strides[0] = st.k[2]; t.strides[1] = st.k[1]; t.strides[2] = st.k[0];
+  if ((rc = make_tmap_4d(mk, t, kTile))) return rc;
+  t.ptr = a->v;
+  t.strides[0] = st.v[2]; t.strides[1] = st.v[1]; t.strides[2] = st.v[0];
+  return make_tmap_4d(mv, t, kTile);
+}
+
+}  // namespace
+}  // namespace acct
+
+using namespace acct;
+
+extern "C" {
+
+int acct_abi_version(void) { return ACCT_ABI_VERSION; }
+
+const char* acct_last_error(void) { return last_error_buf(); }
+
+int acct_device_status(void* stream) {
+  unsigned int* st = device_status_ptr();
+  if (st == nullptr) return ACCT_ERR_NO_DEVICE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned int host = 0;
+  cudaError_t e = cudaMemcpyAsync(&host, st, sizeof(host), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail_cuda(e, "reading the device status word");
+  if (host != 0) {
+    e = cudaMemsetAsync(st, 0, sizeof(host), s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    return fail(ACCT_ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded wait (code %u: 1=TMA load, 2=MMA completion, 3=hand-off)", host);
+  }
+  return ACCT_OK;
+}
+
+int acct_fa_fwd(const acct_fa_args* a, void* stream) {
+  Strides st;
+  int rc = validate_fa(a, &st);
+  if (rc) return rc;
+  unsigned int* status = device_status_ptr();
+  if (status == nullptr) return ACCT_ERR_NO_DEVICE;
+  FwdParams p;
+  memset(&p, 0, sizeof(p));
+  if ((rc = make_qkv_maps(a, st, &p.map_q, &p.map_k, &p.map_v))) return rc;
+  p.o = a->o;
+  p.lse = a->lse;
+  p.o_stride_b = st.o[0]; p.o_stride_h = st.o[1]; p.o_stride_s = st.o[2];
+  p.B = a->B; p.N = a->N; p.S_q = a->S_q; p.S_k = a->S_k; p.D = a->D;
+  p.scale_log2 = a->scale * kLog2e;
+  p.mods = make_mods(a);
+  p.status = status;
+  cudaError_t e = launch_fa_fwd(p, a->dtype == ACCT_BF16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda(e, "launching the forward kernel");
+  return ACCT_OK;
+}
+
+size_t acct_fa_bwd_workspace_bytes(const acct_fa_args* a) {
+  if (a == nullptr || a->B <= 0 || a->N <= 0 || a->S_q <= 0 || a->D <= 0) return 0;
+  const size_t rows = static_cast<size_t>(a->B) * a->N * a->S_q;
+  // delta [rows] fp32 (padded to 256 bytes) + dQ accumulator [rows, D] fp32
+  return ((rows * 4 + 255) / 256) * 256 + rows * static_cast<size_t>(a->D) * 4;
+}
+
+int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
+  Strides st;
+  int rc = validate_fa(a, &st);
+  if (rc) return rc;
+  if (g == nullptr) return fail(ACCT_ERR_NULL, "backward io is NULL");
+  if (!g->d_o || !g->dq || !g->dk || !g->dv || !a->lse) return fail(ACCT_ERR_NULL, "d_o, dq, dk, dv and lse must be non-NULL");
+  if (!aligned16(g->d_o) || !aligned16(g->dq) || !aligned16(g->dk) || !aligned16(g->dv))
+    return fail(ACCT_ERR_ALIGN, "d_o, dq, dk, dv must be 16-byte aligned");
+  const size_t need = acct_fa_bwd_workspace_bytes(a);
+  if (g->workspace == nullptr || g->workspace_bytes < need)
+    return fail(ACCT_ERR_WORKSPACE, "backward workspace: need %zu bytes, got %zu", need, g->workspace ? g->workspace_bytes : (size_t)0);
+  if ((reinterpret_cast<uintptr_t>(g->workspace) & 255u) != 0) return fail(ACCT_ERR_ALIGN, "workspace must be 256-byte aligned");
+  unsigned int* status = device_status_ptr();
+  if (status == nullptr) return ACCT_ERR_NO_DEVICE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool bf16 = a->dtype == ACCT_BF16;
+  const size_t rows = static_cast<size_t>(a->B) * a->N * a->S_q;
+  float* delta = static_cast<float*>(g->workspace);
+  float* dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(g->workspace) + ((rows * 4 + 255) / 256) * 256);
+
+  BwdParams p;
+  memset(&p, 0, sizeof(p));
+  if ((rc = make_qkv_maps(a, st, &p.map_q, &p.map_k, &p.map_v))) return rc;
+  TensorDesc4 t;
+  t.dtype = a->dtype; t.ptr = g->d_o;
+  t.dims[0] = a->D; t.dims[1] = a->S_q; t.dims[2] = a->N; t.dims[3] = a->B;
+  t.strides[0] = st.o[2]; t.strides[1] = st.o[1]; t.strides[2] = st.o[0];
+  if ((rc = make_tmap_4d(&p.map_do, t, kTile))) return rc;
+
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, rows * static_cast<size_t>(a->D) * 4, s);
+  if (e != cudaSuccess) return fail_cuda(e, "zero-filling the dQ accumulator");
+  e = launch_bwd_delta(a->o, g->d_o, delta, static_cast<int64_t>(rows), a->D, st.o[0], st.o[1], st.o[2], a->N, a->S_q, bf16, s);
+  if (e != cudaSuccess) return fail_cuda(e, "launching the row-sum kernel");
+  p.lse = a->lse; p.delta = delta; p.dq_acc = dq_acc;
+  p.dk = g->dk; p.dv = g->dv;
+  p.grads_f32 = (a->flags & ACCT_FLAG_GRAD_F32) ? 1 : 0;
+  p.B = a->B; p.N = a->N; p.S_q = a->S_q; p.S_k = a->S_k; p.D = a->D;
+  p.scale = a->scale; p.scale_log2 = a->scale * kLog2e;
+  p.mods = make_mods(a);
+  p.status = status;
+  e = launch_fa_bwd(p, bf16, s);
+  if (e != cudaSuccess) return fail_cuda(e, "launching the backward kernel");
+  e = launch_bwd_convert_dq(dq_acc, g->dq, static_cast<int64_t>(rows) * a->D, bf16, p.grads_f32 != 0, s);
+  if (e != cudaSuccess) return fail_cuda(e, "launching the dQ conversion kernel");
+  return ACCT_OK;
+}
+
+// The reference's InferShape accepts rank 3 or 4, requires k and v of one shape, q/k/v agreeing on
+// batch*heads and head_dim, and bounds every dimension (op_proto/flash_attention_tik.cpp:30-193;
+// tbe/impl/flash_attention_fwd.py:34-40,89-119).  Its numeric limits are properties of the Ascend
+// kernels; the limits enforced here are this library's own.
+int acct_infer_prefill(const acct_infer_args* a, void* stream) {
+  if (a == nullptr) return fail(ACCT_ERR_NULL, "args is NULL");
+  if (a->rank != 3 && a->rank != 4) return fail(ACCT_ERR_SHAPE, "rank must be 3 or 4, got %d", a->rank);
+  if (a->rank == 3 && a->B != 1) return fail(ACCT_ERR_SHAPE, "rank-3 input is [B*N, S, D]: pass B = 1");
+  if (!a->y) return fail(ACCT_ERR_NULL, "y is NULL");
+  acct_fa_args f;
+  memset(&f, 0, sizeof(f));
+  f.dtype = a->dtype;
+  f.B = a->B; f.N = a->N; f.S_q = a->S_q; f.S_k = a->S_k; f.D = a->D;
+  f.q = a->q; f.k = a->k; f.v = a->v; f.o = a->y; f.lse = nullptr;
+  f.mask_kind = ACCT_MASK_NONE;
+  f.causal = a->causal;
+  f.prev_block_num = ACCT_BAND_UNBOUNDED; f.next_block_num = ACCT_BAND_UNBOUNDED;
+  f.scale = a->scale;
+  f.seq_lens = a->seq_lens;
+  f.keep_prob = 1.0f;
+  return acct_fa_fwd(&f, stream);
+}
+
+size_t acct_infer_decode_workspace_bytes(const acct_decode_args* a) {
+  if (a == nullptr || a->B <= 0 || a->N <= 0 || a->D <= 0) return 0;
+  int splits = a->num_splits;
+  if (splits <= 0) splits = 64;   // upper bound of what the automatic choice may pick
+  return static_cast<size_t>(a->B) * a->N * splits * (static_cast<size_t>(a->D) + 2) * 4;
+}
+
+int acct_infer_decode(const acct_decode_args* a, void* stream) {
+  if (a == nullptr) return fail(ACCT_ERR_NULL, "args is NULL");
+  if (a->dtype != ACCT_F16 && a->dtype != ACCT_BF16) return fail(ACCT_ERR_DTYPE, "dtype must be ACCT_F16 or ACCT_BF16");
+  if (a->B <= 0 || a->N <= 0 || a->S_max <= 0) return fail(ACCT_ERR_SHAPE, "B, N, S_max must be positive");
+  if (a->D <= 0 || a->D % 8 != 0 || a->D > 256) return fail(ACCT_ERR_UNSUPPORTED_D, "decode head_dim %d must be a multiple of 8 in (0, 256]", a->D);
+  if (!a->q || !a->k_cache || !a->v_cache || !a->y) return fail(ACCT_ERR_NULL, "q, k_cache, v_cache, y must be non-NULL");
+  if (!aligned16(a->q) || !aligned16(a->k_cache) || !aligned16(a->v_cache) || !aligned16(a->y))
+    return fail(ACCT_ERR_ALIGN, "q, k_cache, v_cache, y must be 16-byte aligned");
+  if (!(a->scale > 0.f)) return fail(ACCT_ERR_SHAPE, "scale must be positive");
+  int64_t kvs[3];
+  int rc = check_strides("kv", a->kv_stride, a->S_max, a->N, a->D, kvs);
+  if (rc) return rc;
+  DeviceInfo info;
+  if ((rc = device_info(&info))) return rc;
+  int splits = a->num_splits;
+  if (splits < 0 || splits > 64) return fail(ACCT_ERR_SHAPE, "num_splits must be in [0, 64]");
+  if (splits == 0) {
+    // enough CTAs for ~4 waves of 2 resident CTAs per SM, but never splits shorter than 256 keys
+    const int64_t units = static_cast<int64_t>(a->B) * a->N;
+    int64_t want = (static_cast<int64_t>(info.sm_count) * 8 + units - 1) / units;
+    int64_t cap = (a->S_max + 255) / 256;
+    splits = static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+  }
+  const size_t need = static_cast<size_t>(a->B) * a->N * splits * (static_cast<size_t>(a->D) + 2) * 4;
+  if (a->workspace == nullptr || a->workspace_bytes < need)
+    return fail(ACCT_ERR_WORKSPACE, "decode workspace: need %zu bytes, got %zu", need, a->workspace ? a->workspace_bytes : (size_t)0);
+  if (!aligned16(a->workspace)) return fail(ACCT_ERR_ALIGN, "workspace must be 16-byte aligned");
+  DecodeParams p;
+  p.q = a->q; p.k = a->k_cache; p.v = a->v_cache; p.y = a->y; p.seq_lens = a->seq_lens;
+  p.part_acc = static_cast<float*>(a->workspace);
+  p.part_ml = p.part_acc + static_cast<size_t>(a->B) * a->N * splits * a->D;
+  p.kv_stride_b = kvs[0]; p.kv_stride_h = kvs[1]; p.kv_stride_s = kvs[2];
+  p.B = a->B; p.N = a->N; p.S_max = a->S_max; p.D = a->D;
+  p.splits = splits;
+  p.scale_log2 = a->scale * kLog2e;
+  cudaError_t e = launch_decode(p, a->dtype == ACCT_BF16, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda(e, "launching the decode kernels");
+  return ACCT_OK;
+}
+
+}  // extern "C"

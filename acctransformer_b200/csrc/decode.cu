@@ -1,0 +1,211 @@
+// Decode (one query token per sequence) over a KV cache: split-KV streaming + merge.
+//
+// The step is bound by reading K and V once from HBM, so it runs on CUDA cores with 128-bit
+// loads: a group of LPR lanes covers one cache row (8 elements each), a warp covers 32/LPR
+// consecutive rows per load instruction (one contiguous span of memory), and every thread keeps
+// 2*kChunk such loads in flight.  Each lane group carries its own online-softmax state
+// (max, sum, partial output slice); states are merged inside the CTA, written per split to the
+// workspace, and merged across splits by a second small kernel.
+//
+// Semantics: y[b,n,0,:] = softmax(scale * q K[:len_b]^T) V[:len_b] -- the q_len = 1 case of the
+// reference's inference op (infer/flash_attention/tik/tbe/impl/flash_attention_fwd.py:583-705
+// computes the same recurrence with m, l, O kept in global memory).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "fa_kernels.cuh"
+
+namespace acct {
+namespace {
+
+constexpr int kDecodeThreads = 128;
+constexpr int kChunk = 8;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <bool BF16>
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (BF16) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      const float2 t = __half22float2(h);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+}
+
+template <int LPR, bool BF16>
+__global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const DecodeParams p) {
+  constexpr int RPW = 32 / LPR;                 // cache rows per warp per load instruction
+  constexpr int kWarps = kDecodeThreads / 32;
+  constexpr int kGroups = kWarps * RPW;         // independent softmax states per CTA
+  constexpr int DMAX = LPR * 8;
+
+  __shared__ float s_m[kGroups], s_l[kGroups];
+  __shared__ float s_acc[kGroups][DMAX];
+
+  const int split = blockIdx.x;
+  const int unit = blockIdx.y;
+  const int b = unit / p.N, h = unit % p.N;
+  int len = p.S_max;
+  if (p.seq_lens != nullptr) len = min(p.S_max, max(0, p.seq_lens[b]));
+  const int per = (((len + p.splits - 1) / p.splits) + 63) & ~63;
+  const int k0 = split * per;
+  const int k1 = min(len, k0 + per);
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % LPR, rsub = lane / LPR;
+  const int dcol = sub * 8;
+  const bool active = dcol < p.D;
+
+  float qf[8];
+  {
+    uint4 qu = make_uint4(0, 0, 0, 0);
+    if (active) qu = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + static_cast<int64_t>(unit) * p.D + dcol);
+    unpack8<BF16>(qu, qf);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qf[e] *= p.scale_log2;
+  }
+  const uint16_t* kbase = reinterpret_cast<const uint16_t*>(p.k) + b * p.kv_stride_b + h * p.kv_stride_h + dcol;
+  const uint16_t* vbase = reinterpret_cast<const uint16_t*>(p.v) + b * p.kv_stride_b + h * p.kv_stride_h + dcol;
+
+  float m = -INFINITY, l = 0.f;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+
+  for (int row0 = k0 + warp * (RPW * kChunk); row0 < k1; row0 += kWarps * RPW * kChunk) {
+    uint4 ku[kChunk], vu[kChunk];
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) {
+      const int row = row0 + i * RPW + rsub;
+      ku[i] = (active && row < k1) ? ld_stream(kbase + static_cast<int64_t>(row) * p.kv_stride_s) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) {
+      const int row = row0 + i * RPW + rsub;
+      vu[i] = (active && row < k1) ? ld_stream(vbase + static_cast<int64_t>(row) * p.kv_stride_s) : make_uint4(0, 0, 0, 0);
+    }
+    float s[kChunk];
+    float cmax = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) {
+      float kf[8];
+      unpack8<BF16>(ku[i], kf);
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) d = fmaf(kf[e], qf[e], d);
+#pragma unroll
+      for (int off = 1; off < LPR; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+      const int row = row0 + i * RPW + rsub;
+      s[i] = row < k1 ? d : -INFINITY;
+      cmax = fmaxf(cmax, s[i]);
+    }
+    const float m_new = fmaxf(m, cmax);
+    if (m_new != -INFINITY) {
+      const float alpha = ex2(m - m_new);   // m = -inf gives 0
+      l *= alpha;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= alpha;
+      m = m_new;
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) {
+        const float pr = ex2(s[i] - m);
+        l += pr;
+        float vf[8];
+        unpack8<BF16>(vu[i], vf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(pr, vf[e], acc[e]);
+      }
+    }
+  }
+
+  // merge the CTA's groups
+  const int g = warp * RPW + rsub;
+  if (sub == 0) { s_m[g] = m; s_l[g] = l; }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) s_acc[g][dcol + e] = acc[e];
+  __syncthreads();
+  const int64_t slot = static_cast<int64_t>(unit) * p.splits + split;
+  float big = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kGroups; ++i) big = fmaxf(big, s_m[i]);
+  for (int t = threadIdx.x; t < p.D; t += kDecodeThreads) {
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGroups; ++i) {
+      const float w = (s_m[i] == -INFINITY) ? 0.f : ex2(s_m[i] - big);
+      a = fmaf(s_acc[i][t], w, a);
+    }
+    p.part_acc[slot * p.D + t] = a;
+  }
+  if (threadIdx.x == 0) {
+    float lsum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGroups; ++i) lsum += (s_m[i] == -INFINITY) ? 0.f : s_l[i] * ex2(s_m[i] - big);
+    p.part_ml[slot * 2] = big;
+    p.part_ml[slot * 2 + 1] = lsum;
+  }
+}
+
+template <bool BF16>
+__global__ void decode_merge_kernel(const DecodeParams p) {
+  const int unit = blockIdx.x;
+  const float* ml = p.part_ml + static_cast<int64_t>(unit) * p.splits * 2;
+  float big = -INFINITY;
+  for (int s = 0; s < p.splits; ++s) big = fmaxf(big, ml[2 * s]);
+  float lsum = 0.f;
+  for (int s = 0; s < p.splits; ++s) lsum += (ml[2 * s] == -INFINITY) ? 0.f : ml[2 * s + 1] * ex2(ml[2 * s] - big);
+  const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+  for (int t = threadIdx.x; t < p.D; t += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float w = (ml[2 * s] == -INFINITY) ? 0.f : ex2(ml[2 * s] - big);
+      a = fmaf(p.part_acc[(static_cast<int64_t>(unit) * p.splits + s) * p.D + t], w, a);
+    }
+    a *= inv;
+    if constexpr (BF16) reinterpret_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(unit) * p.D + t] = __float2bfloat16(a);
+    else reinterpret_cast<__half*>(p.y)[static_cast<int64_t>(unit) * p.D + t] = __float2half(a);
+  }
+}
+
+template <int LPR>
+cudaError_t launch_decode_lpr(const DecodeParams& p, bool bf16, cudaStream_t stream) {
+  dim3 grid(p.splits, p.B * p.N);
+  if (bf16) decode_split_kernel<LPR, true><<<grid, kDecodeThreads, 0, stream>>>(p);
+  else decode_split_kernel<LPR, false><<<grid, kDecodeThreads, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int threads = p.D <= 64 ? 64 : (p.D <= 128 ? 128 : 256);
+  if (bf16) decode_merge_kernel<true><<<p.B * p.N, threads, 0, stream>>>(p);
+  else decode_merge_kernel<false><<<p.B * p.N, threads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_decode(const DecodeParams& p, bool bf16, cudaStream_t stream) {
+  if (p.D <= 64) return launch_decode_lpr<8>(p, bf16, stream);
+  if (p.D <= 128) return launch_decode_lpr<16>(p, bf16, stream);
+  return launch_decode_lpr<32>(p, bf16, stream);
+}
+
+}  // namespace acct

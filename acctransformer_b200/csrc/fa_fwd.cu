@@ -1,0 +1,423 @@
+// FlashAttention-2 forward for sm_100a.
+//
+// One CTA owns two consecutive 128-row Q tiles of one (batch, head) slice and walks the K/V tiles
+// they need.  Warp roles:
+//   warps 0-3   softmax group for Q tile 0 (thread t owns score row t: row max / sum are in-thread)
+//   warps 4-7   softmax group for Q tile 1
+//   warp  8     TMA producer: Q once, then K_j / V_j into a two-stage ring
+//   warp  9     MMA issuer (one elected thread): S = Q K^T and O += P V on tcgen05
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 columns each.  The 16-bit probabilities are
+// written back over the first 64 columns of their own S buffer and feed the second MMA straight
+// from tensor memory.  While one group runs softmax on its tile the tensor pipe works on the other
+// group's tile, so the two overlap.
+//
+// Follows the reference's forward (train/acctransformer/flash_attention/ops/flash_attention/
+// flash_attention_fwd.py:308-457): per K/V tile  S -> (+alibi, +mask*-10000) -> running max ->
+// exp -> row sum (before dropout) -> dropout -> O = O*e^(m_old-m_new) + P V, and at the end
+// O / l and L = m + ln l (:258-306).  The running max is only refreshed when it grows by more than
+// 8 (in log2 units); P, l and O then share the same stale offset, which cancels in O / l and in L.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "fa_kernels.cuh"
+#include "ptx.cuh"
+
+namespace acct {
+
+namespace {
+
+constexpr int kFwdThreads = 320;
+constexpr int kStages = 2;
+constexpr float kNegInf = -INFINITY;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ float load16(const void* base, int64_t idx) {
+  if constexpr (BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+  else return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+}
+
+__device__ __forceinline__ float load_mask_value(const void* base, int dtype, int64_t idx) {
+  if (dtype == 2 /*U8*/) return static_cast<float>(reinterpret_cast<const uint8_t*>(base)[idx]);
+  if (dtype == 1 /*BF16*/) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+  return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+}
+
+struct TileRange {
+  int lo, hi;   // inclusive K/V tile indices; empty when lo > hi
+};
+
+// K/V tiles that Q tile `i` needs: the block band  j - next <= i <= j + prev, the causal triangle,
+// and the valid key length.
+__device__ __forceinline__ TileRange kv_tile_range(int i, int s_q, int kv_len, const ScoreMods& m) {
+  TileRange r;
+  if (i * kTile >= s_q || kv_len <= 0) { r.lo = 0; r.hi = -1; return r; }
+  r.lo = 0;
+  r.hi = (kv_len + kTile - 1) / kTile - 1;
+  if (m.prev_block_num < 65536) r.lo = max(r.lo, i - m.prev_block_num);
+  if (m.next_block_num < 65536) r.hi = min(r.hi, i + m.next_block_num);
+  if (m.causal) r.hi = min(r.hi, i);
+  return r;
+}
+
+struct FwdShared {
+  uint64_t q_full;
+  uint64_t k_full[kStages], k_empty[kStages];
+  uint64_t v_full[kStages], v_empty[kStages];
+  uint64_t s_full[2], p_ready[2], o_done[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+}  // namespace
+
+template <int DPAD, bool BF16>
+__global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_constant__ FwdParams p) {
+  constexpr int NB = DPAD / 64;                 // 64-column (128-byte) blocks per row
+  constexpr uint32_t kTileBytes = NB * 16384u;  // one 128-row tile
+  constexpr uint32_t kColS = 0, kColO = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                          // 2 tiles
+  uint8_t* sK = sQ + 2 * kTileBytes;           // kStages tiles
+  uint8_t* sV = sK + kStages * kTileBytes;     // kStages tiles
+  __shared__ FwdShared sh;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int b = bh / p.N, h = bh % p.N;
+  // heavier (later) tile pairs first: under a causal mask they have the most K/V tiles
+  const int pair = gridDim.x - 1 - blockIdx.x;
+  const ScoreMods& mods = p.mods;
+
+  int kv_len = p.S_k;
+  if (mods.seq_lens != nullptr) kv_len = min(p.S_k, max(0, mods.seq_lens[b]));
+
+  const TileRange r0 = kv_tile_range(2 * pair, p.S_q, kv_len, mods);
+  const TileRange r1 = kv_tile_range(2 * pair + 1, p.S_q, kv_len, mods);
+  const bool any0 = r0.lo <= r0.hi, any1 = r1.lo <= r1.hi;
+  int cta_lo = 0, cta_hi = -1;
+  if (any0 && any1) { cta_lo = min(r0.lo, r1.lo); cta_hi = max(r0.hi, r1.hi); }
+  else if (any0) { cta_lo = r0.lo; cta_hi = r0.hi; }
+  else if (any1) { cta_lo = r1.lo; cta_hi = r1.hi; }
+
+  if (tid == 0) {
+    mbar_init(&sh.q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sh.k_full[s], 1); mbar_init(&sh.k_empty[s], 1);
+      mbar_init(&sh.v_full[s], 1); mbar_init(&sh.v_empty[s], 1);
+    }
+    for (int q = 0; q < 2; ++q) {
+      mbar_init(&sh.s_full[q], 1); mbar_init(&sh.p_ready[q], 128); mbar_init(&sh.o_done[q], 1);
+    }
+    sh.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 8) { tmem_alloc(&sh.tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sh.tmem_base;
+  volatile uint32_t* abort_flag = &sh.abort_flag;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && cta_hi >= cta_lo) {
+      prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v);
+      mbar_expect_tx(&sh.q_full, 2 * kTileBytes);
+      for (int qt = 0; qt < 2; ++qt)
+        for (int nb = 0; nb < NB; ++nb)
+          tma_load_4d(sQ + qt * kTileBytes + nb * 16384, &p.map_q, &sh.q_full, nb * 64,
+                      (2 * pair + qt) * kTile, h, b);
+      int it = 0;
+      for (int j = cta_lo; j <= cta_hi; ++j, ++it) {
+        const int st = it % kStages;
+        const uint32_t reuse_parity = ((it / kStages) - 1) & 1;
+        if (it >= kStages && !mbar_wait(&sh.k_empty[st], reuse_parity, abort_flag)) {
+          *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break;
+        }
+        mbar_expect_tx(&sh.k_full[st], kTileBytes);
+        for (int nb = 0; nb < NB; ++nb)
+          tma_load_4d(sK + st * kTileBytes + nb * 16384, &p.map_k, &sh.k_full[st], nb * 64, j * kTile, h, b);
+        if (it >= kStages && !mbar_wait(&sh.v_empty[st], reuse_parity, abort_flag)) {
+          *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break;
+        }
+        mbar_expect_tx(&sh.v_full[st], kTileBytes);
+        for (int nb = 0; nb < NB; ++nb)
+          tma_load_4d(sV + st * kTileBytes + nb * 16384, &p.map_v, &sh.v_full[st], nb * 64, j * kTile, h, b);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && cta_hi >= cta_lo) {
+      const uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);
+      const uint32_t idesc_o = make_idesc(BF16, 128, DPAD, false, true);
+      const uint64_t kmajor = make_sdesc_base(16, 1024);
+      const uint64_t mnmajor = make_sdesc_base(16384, 1024);
+      const TileRange rng[2] = {r0, r1};
+      int n_done[2] = {0, 0};   // P tiles consumed so far per Q tile
+      bool ok = mbar_wait(&sh.q_full, 0, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); }
+
+      auto issue_s = [&](int qt, int st) {
+        const uint32_t a0 = smem_u32(sQ + qt * kTileBytes);
+        const uint32_t b0 = smem_u32(sK + st * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < DPAD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
+          umma_ss(tmem + kColS + qt * 128, sdesc_at(kmajor, a0 + off), sdesc_at(kmajor, b0 + off), idesc_s, kk > 0);
+        }
+        umma_commit(&sh.s_full[qt]);
+      };
+
+      if (ok) {
+        // prologue: scores of the first K/V tile
+        ok = mbar_wait(&sh.k_full[0], 0, abort_flag);
+        if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); }
+        if (ok) {
+          tc_fence_after_sync();
+          for (int qt = 0; qt < 2; ++qt)
+            if (cta_lo >= rng[qt].lo && cta_lo <= rng[qt].hi) issue_s(qt, 0);
+          umma_commit(&sh.k_empty[0]);
+        }
+      }
+      int it = 0;
+      for (int j = cta_lo; ok && j <= cta_hi; ++j, ++it) {
+        const int st = it % kStages;
+        const int stn = (it + 1) % kStages;
+        const uint32_t full_parity = (it / kStages) & 1;
+        const uint32_t full_parity_n = ((it + 1) / kStages) & 1;
+        for (int qt = 0; ok && qt < 2; ++qt) {
+          if (j >= rng[qt].lo && j <= rng[qt].hi) {
+            ok = mbar_wait(&sh.p_ready[qt], n_done[qt] & 1, abort_flag);
+            if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break; }
+            ok = mbar_wait(&sh.v_full[st], full_parity, abort_flag);
+            if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); break; }
+            tc_fence_after_sync();
+            const uint32_t v0 = smem_u32(sV + st * kTileBytes);
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)
+              umma_ts(tmem + kColO + qt * DPAD, tmem + kColS + qt * 128 + kk * 8,
+                      sdesc_at(mnmajor, v0 + kk * 2048u), idesc_o, n_done[qt] > 0 || kk > 0);
+            umma_commit(&sh.o_done[qt]);
+            ++n_done[qt];
+          }
+          if (j + 1 <= cta_hi && j + 1 >= rng[qt].lo && j + 1 <= rng[qt].hi) {
+            ok = mbar_wait(&sh.k_full[stn], full_parity_n, abort_flag);
+            if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); break; }
+            tc_fence_after_sync();
+            issue_s(qt, stn);
+          }
+        }
+        if (!ok) break;
+        umma_commit(&sh.v_empty[st]);
+        if (j + 1 <= cta_hi) umma_commit(&sh.k_empty[stn]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax groups
+    const int qt = warp >> 2;
+    const TileRange rng = qt == 0 ? r0 : r1;
+    const int q_tile = 2 * pair + qt;
+    const int row_in_tile = tid & 127;
+    const int q_row = q_tile * kTile + row_in_tile;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + kColS + qt * 128;
+    const uint32_t t_o = tmem + lane_base + kColO + qt * DPAD;
+    const bool has_alibi = mods.alibi != nullptr || mods.alibi_slopes != nullptr;
+    const float slope_l2 = mods.alibi_slopes != nullptr ? mods.alibi_slopes[h] * kLog2e : 0.f;
+    const int64_t alibi_row = static_cast<int64_t>(bh) * p.S_k;
+    const int64_t mask_row =
+        (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q + min(q_row, p.S_q - 1)) * p.S_k;
+    const int64_t drop_row = (static_cast<int64_t>(bh) * p.S_q + min(q_row, p.S_q - 1)) * p.S_k;
+
+    float m_run = kNegInf, l_run = 0.f;
+    int n = 0;
+    bool ok = true;
+    for (int j = rng.lo; j <= rng.hi; ++j, ++n) {
+      ok = mbar_wait(&sh.s_full[qt], n & 1, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); break; }
+      tc_fence_after_sync();
+      const int col_base = j * kTile;
+      const bool diag = mods.causal && (col_base + kTile - 1 > q_tile * kTile);
+      const bool tail = col_base + kTile > kv_len;
+      const bool use_mask = (mods.mask_kind == 1) || (mods.mask_kind == 2 && j == q_tile);
+      const bool transform = diag || tail || use_mask || has_alibi;
+
+      // pass 1: (transform and) row max
+      float m_tile = kNegInf;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_s + c * 32, r);
+        tmem_wait_ld();
+        if (transform) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = col_base + c * 32 + i;
+            float x = __uint_as_float(r[i]) * p.scale_log2;
+            if (col < kv_len) {
+              if (mods.alibi != nullptr) x += load16<BF16>(mods.alibi, alibi_row + col) * kLog2e;
+              else if (mods.alibi_slopes != nullptr) x += slope_l2 * static_cast<float>(col);
+              if (use_mask) {
+                const float mv = mods.mask_kind == 1
+                                     ? load_mask_value(mods.mask, mods.mask_dtype, mask_row + col)
+                                     : load_mask_value(mods.mask, mods.mask_dtype,
+                                                       static_cast<int64_t>(row_in_tile) * kTile + (col - col_base));
+                x += mv * (-10000.0f * kLog2e);
+              }
+            }
+            if (col >= kv_len || (mods.causal && col > q_row)) x = kNegInf;
+            r[i] = __float_as_uint(x);
+            m_tile = fmaxf(m_tile, x);
+          }
+          tmem_st32(t_s + c * 32, r);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(r[i]));
+        }
+      }
+      float mult = 1.0f;
+      if (transform) tmem_wait_st();
+      else { m_tile *= p.scale_log2; mult = p.scale_log2; }   // scale > 0: max commutes with the scaling
+
+      // running max, refreshed only when it grows by more than the threshold
+      const float m_new = fmaxf(m_run, m_tile);
+      const bool grow = (m_new > m_run + kRescaleThreshold) || (m_run == kNegInf && m_new != kNegInf);
+      float alpha = 1.0f;
+      if (grow) {
+        alpha = (m_run == kNegInf) ? 0.f : ex2(m_run - m_new);
+        m_run = m_new;
+        l_run *= alpha;
+      }
+      if (n > 0 && __any_sync(0xffffffffu, grow)) {
+        // O of the previous tiles is complete (the S MMA just waited for was issued after their P V)
+#pragma unroll 1
+        for (int c = 0; c < DPAD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_o + c * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st32(t_o + c * 32, r);
+        }
+        tmem_wait_st();
+      }
+      const float m_use = (m_run == kNegInf) ? 0.f : m_run;
+
+      // pass 2: P = exp2(x - m), row sum before dropout, 16-bit P over the S buffer
+      float l_tile = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_s + c * 32, r);
+        tmem_wait_ld();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          pr[i] = ex2(fmaf(__uint_as_float(r[i]), mult, -m_use));
+          l_tile += pr[i];
+        }
+        if (mods.drop != nullptr) {
+          const int col0 = col_base + c * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = col0 + i;
+            float f = 0.f;
+            if (col < p.S_k) f = load_mask_value(mods.drop, mods.drop_dtype, drop_row + col) * mods.drop_scale;
+            pr[i] *= f;
+          }
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pk[i] = pack2<BF16>(pr[2 * i], pr[2 * i + 1]);
+        tmem_st16(t_s + c * 16, pk);
+      }
+      l_run += l_tile;
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&sh.p_ready[qt]);
+    }
+
+    // epilogue: O / l and L = m + ln l
+    if (ok && q_tile * kTile < p.S_q) {
+      if (n > 0) {
+        ok = mbar_wait(&sh.o_done[qt], (n - 1) & 1, abort_flag);
+        if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); }
+        tc_fence_after_sync();
+      }
+      if (ok) {
+        const float inv_l = (n > 0 && l_run > 0.f) ? 1.0f / l_run : 0.f;
+        const bool row_ok = q_row < p.S_q;
+        uint8_t* o_row = reinterpret_cast<uint8_t*>(p.o) +
+                         2 * (b * p.o_stride_b + h * p.o_stride_h + static_cast<int64_t>(q_row) * p.o_stride_s);
+#pragma unroll 1
+        for (int c = 0; c < DPAD / 32; ++c) {
+          uint32_t r[32];
+          if (n > 0) { tmem_ld32(t_o + c * 32, r); tmem_wait_ld(); }
+          else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            pk[i] = pack2<BF16>(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = c * 32 + g * 8;
+              if (col + 8 <= p.D)
+                *reinterpret_cast<uint4*>(o_row + col * 2) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+            }
+          }
+        }
+        if (row_ok && p.lse != nullptr)
+          p.lse[static_cast<int64_t>(bh) * p.S_q + q_row] =
+              (n > 0 && l_run > 0.f) ? m_run * kLn2 + logf(l_run) : kNegInf;
+      }
+    }
+    tc_fence_before_sync();
+  }
+
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
+  const int dpad = p.D <= 64 ? 64 : 128;
+  const size_t smem = static_cast<size_t>(2 + 2 * kStages) * (dpad / 64) * 16384 + 1024;
+  dim3 grid((p.S_q + 2 * kTile - 1) / (2 * kTile), p.B * p.N);
+  void (*kern)(const FwdParams) = nullptr;
+  if (dpad == 64) kern = bf16 ? fa_fwd_kernel<64, true> : fa_fwd_kernel<64, false>;
+  else kern = bf16 ? fa_fwd_kernel<128, true> : fa_fwd_kernel<128, false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  kern<<<grid, kFwdThreads, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace acct

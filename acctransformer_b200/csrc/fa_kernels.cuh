@@ -1,0 +1,77 @@
+// Parameter blocks and launchers of the attention kernels (internal to the library).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace acct {
+
+constexpr int kTile = 128;          // rows of a Q tile and of a K/V tile; also the band block
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// What the softmax stage must look at besides the raw scores.
+struct ScoreMods {
+  int causal;
+  int prev_block_num, next_block_num;
+  int mask_kind, mask_dtype, mask_batch;
+  const void* mask;
+  const void* drop;
+  int drop_dtype;
+  float drop_scale;                 // 1/keep_prob for uint8 masks, 1 for pre-scaled 16-bit masks
+  const void* alibi;                // [B,N,1,S_k] in the tensor dtype
+  const float* alibi_slopes;        // [N]
+  const int* seq_lens;              // [B]
+};
+
+struct alignas(64) FwdParams {
+  CUtensorMap map_q, map_k, map_v;
+  void* o;
+  float* lse;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  int B, N, S_q, S_k, D;
+  float scale_log2;                 // scale * log2(e)
+  ScoreMods mods;
+  unsigned int* status;
+};
+
+struct alignas(64) BwdParams {
+  CUtensorMap map_q, map_k, map_v, map_do;
+  const float* lse;                 // [B,N,S_q]
+  const float* delta;               // [B,N,S_q]  rowsum(dO * O)
+  float* dq_acc;                    // [B,N,S_q,D] fp32, zeroed before launch
+  void* dk;
+  void* dv;
+  int grads_f32;
+  int B, N, S_q, S_k, D;
+  float scale;                      // multiplies dS for dQ and dK
+  float scale_log2;
+  ScoreMods mods;
+  unsigned int* status;
+};
+
+struct DecodeParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* y;
+  const int* seq_lens;
+  float* part_acc;                  // [B*N, splits, D]
+  float* part_ml;                   // [B*N, splits, 2]
+  int64_t kv_stride_b, kv_stride_h, kv_stride_s;
+  int B, N, S_max, D;
+  int splits;
+  float scale_log2;
+};
+
+// Launchers: return cudaGetLastError() of the launch.
+cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream);
+cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream);
+cudaError_t launch_bwd_delta(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t o_stride_b,
+                             int64_t o_stride_h, int64_t o_stride_s, int N, int S_q, bool bf16,
+                             cudaStream_t stream);
+cudaError_t launch_bwd_convert_dq(const float* dq_acc, void* dq, int64_t n_elems, bool bf16, bool f32_out,
+                                  cudaStream_t stream);
+cudaError_t launch_decode(const DecodeParams& p, bool bf16, cudaStream_t stream);
+
+}  // namespace acct

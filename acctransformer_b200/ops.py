@@ -1,0 +1,229 @@
+"""Torch-tensor front end of the C ABI: fills the argument structs from CUDA tensors and launches
+on torch's current stream.  torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+from ._lib import (ACCT_BF16, ACCT_F16, ACCT_U8, BAND_UNBOUNDED, FLAG_GRAD_F32, MASK_FULL, MASK_NONE,
+                   MASK_TILE128, DecodeArgs, FaArgs, FaBwdIO, InferArgs, check, load)
+
+_DTYPES = {torch.float16: ACCT_F16, torch.bfloat16: ACCT_BF16, torch.uint8: ACCT_U8, torch.bool: ACCT_U8}
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(name, t):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+
+
+def _dtype_code(t, what):
+    if t.dtype not in _DTYPES:
+        raise ValueError(f"{what}: unsupported dtype {t.dtype}")
+    return _DTYPES[t.dtype]
+
+
+def _strides3(t):
+    if t.stride(-1) != 1:
+        raise ValueError("head_dim must be contiguous")
+    return (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
+                  alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, flags=0):
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda(name, t)
+        if t.dim() != 4:
+            raise ValueError(f"{name} must be [B, N, S, D]")
+    if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("q, k, v must share dtype float16 or bfloat16")
+    B, N, S_q, D = q.shape
+    S_k = k.shape[2]
+    if k.shape != (B, N, S_k, D) or v.shape != (B, N, S_k, D):
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
+    a = FaArgs()
+    a.dtype = _DTYPES[q.dtype]
+    a.B, a.N, a.S_q, a.S_k, a.D = B, N, S_q, S_k, D
+    a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.q_stride, a.k_stride, a.v_stride, a.o_stride = _strides3(q), _strides3(k), _strides3(v), _strides3(o)
+    keep = []
+    a.mask_kind = MASK_NONE
+    if attn_mask is not None:
+        _require_cuda("attn_mask", attn_mask)
+        m = attn_mask.contiguous()
+        keep.append(m)
+        a.mask_dtype = _dtype_code(m, "attn_mask")
+        if mask_tile128:
+            if m.numel() != 128 * 128:
+                raise ValueError("the tile form of attn_mask must hold 128x128 elements")
+            a.mask_kind, a.mask_batch = MASK_TILE128, 1
+        else:
+            if m.dim() == 2:
+                m = m.unsqueeze(0)
+            if m.dim() != 3 or m.shape[1] != S_q or m.shape[2] != S_k or m.shape[0] not in (1, B):
+                raise ValueError(f"attn_mask must be [1 or B, S_q, S_k], got {tuple(attn_mask.shape)}")
+            a.mask_kind, a.mask_batch = MASK_FULL, m.shape[0]
+        a.attn_mask = m.data_ptr()
+    a.causal = 1 if causal else 0
+    a.keep_prob = float(keep_prob)
+    if dropout_mask is not None:
+        _require_cuda("dropout_mask", dropout_mask)
+        dm = dropout_mask.contiguous()
+        keep.append(dm)
+        if tuple(dm.shape) != (B, N, S_q, S_k):
+            raise ValueError("dropout_mask must be [B, N, S_q, S_k]")
+        a.dropout_mask = dm.data_ptr()
+        a.dropout_dtype = _dtype_code(dm, "dropout_mask")
+    if alibi is not None:
+        _require_cuda("alibi", alibi)
+        al = alibi.contiguous()
+        keep.append(al)
+        if tuple(al.shape) != (B, N, 1, S_k) or al.dtype != q.dtype:
+            raise ValueError("alibi must be [B, N, 1, S_k] in the dtype of q")
+        a.alibi = al.data_ptr()
+    if alibi_slopes is not None:
+        _require_cuda("alibi_slopes", alibi_slopes)
+        sl = alibi_slopes.to(torch.float32).contiguous()
+        keep.append(sl)
+        if sl.numel() != N:
+            raise ValueError("alibi_slopes must hold N values")
+        a.alibi_slopes = sl.data_ptr()
+    a.prev_block_num = min(int(prev_block_num), BAND_UNBOUNDED)
+    a.next_block_num = min(int(next_block_num), BAND_UNBOUNDED)
+    a.scale = float(scale)
+    if seq_lens is not None:
+        _require_cuda("seq_lens", seq_lens)
+        sl = seq_lens.to(torch.int32).contiguous()
+        keep.append(sl)
+        a.seq_lens = sl.data_ptr()
+    a.flags = flags
+    return a, keep
+
+
+def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dropout_mask=None,
+               keep_prob=1.0, alibi=None, alibi_slopes=None, prev_block_num=BAND_UNBOUNDED,
+               next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None, need_lse=True):
+    """Forward primitive: returns (output [B,N,S_q,D] in q's dtype, lse [B,N,S_q] fp32 or None)."""
+    lib = load()
+    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if need_lse else None
+    a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
+                            alibi_slopes, prev_block_num, next_block_num, scale, seq_lens)
+    with torch.cuda.device(q.device):
+        check(lib.acct_fa_fwd(C.byref(a), _stream()))
+    del keep
+    return o, lse
+
+
+def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, causal=False,
+                dropout_mask=None, keep_prob=1.0, alibi=None, alibi_slopes=None,
+                prev_block_num=BAND_UNBOUNDED, next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None,
+                grads_fp32=False):
+    """Grad primitive: returns (dq, dk, dv), fp32 when ``grads_fp32`` (what the reference primitive
+    returns) else in q's dtype (what its bprop hands back after the cast)."""
+    lib = load()
+    _require_cuda("o", o)
+    _require_cuda("d_o", d_o)
+    _require_cuda("lse", lse)
+    if d_o.stride() != o.stride():
+        d_o = d_o.contiguous()
+        o = o.contiguous()
+    gdt = torch.float32 if grads_fp32 else q.dtype
+    dq = torch.empty(q.shape, dtype=gdt, device=q.device)
+    dk = torch.empty(k.shape, dtype=gdt, device=q.device)
+    dv = torch.empty(v.shape, dtype=gdt, device=q.device)
+    lse = lse.contiguous()
+    a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
+                            alibi_slopes, prev_block_num, next_block_num, scale, seq_lens,
+                            flags=FLAG_GRAD_F32 if grads_fp32 else 0)
+    nbytes = lib.acct_fa_bwd_workspace_bytes(C.byref(a))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    g = FaBwdIO()
+    g.d_o, g.dq, g.dk, g.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    g.workspace, g.workspace_bytes = ws.data_ptr(), nbytes
+    with torch.cuda.device(q.device):
+        check(lib.acct_fa_bwd(C.byref(a), C.byref(g), _stream()))
+    del keep
+    return dq, dk, dv
+
+
+def infer_prefill(q, k, v, *, causal=False, scale=1.0, seq_lens=None):
+    """The inference op y = softmax(scale * q k^T) v on rank-3 [B*N,S,D] or rank-4 [B,N,S,D] input."""
+    lib = load()
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda(name, t)
+    rank = q.dim()
+    if rank not in (3, 4):
+        raise ValueError("q must have rank 3 or 4")
+    if k.dim() != rank or v.dim() != rank or k.shape != v.shape:
+        raise ValueError("k and v must have q's rank and one shape")
+    q4, k4, v4 = (t.contiguous() if rank == 4 else t.contiguous().unsqueeze(0) for t in (q, k, v))
+    if q4.shape[:2] != k4.shape[:2] or q4.shape[3] != k4.shape[3]:
+        raise ValueError("q and k must agree on batch, heads and head_dim")
+    y = torch.empty_like(q4)
+    a = InferArgs()
+    a.dtype = _DTYPES[q.dtype] if q.dtype in (torch.float16, torch.bfloat16) else -1
+    a.rank = rank
+    a.B, a.N, a.S_q, a.D = q4.shape[0], q4.shape[1], q4.shape[2], q4.shape[3]
+    a.S_k = k4.shape[2]
+    a.q, a.k, a.v, a.y = q4.data_ptr(), k4.data_ptr(), v4.data_ptr(), y.data_ptr()
+    a.causal = 1 if causal else 0
+    a.scale = float(scale)
+    sl = None
+    if seq_lens is not None:
+        sl = seq_lens.to(torch.int32).contiguous()
+        a.seq_lens = sl.data_ptr()
+    with torch.cuda.device(q.device):
+        check(lib.acct_infer_prefill(C.byref(a), _stream()))
+    return y if rank == 4 else y.squeeze(0)
+
+
+class DecodeWorkspace:
+    """Caller-owned scratch for ``infer_decode`` (partial results of the key splits)."""
+
+    def __init__(self, B, N, D, device, num_splits=0):
+        a = DecodeArgs()
+        a.B, a.N, a.D, a.num_splits = B, N, D, num_splits
+        self.nbytes = load().acct_infer_decode_workspace_bytes(C.byref(a))
+        self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+
+
+def infer_decode(q, k_cache, v_cache, seq_lens=None, *, scale=None, num_splits=0, workspace=None, out=None):
+    """y[b,n,0,:] = softmax(scale * q K[:len_b]^T) V[:len_b] for q [B,N,1,D], caches [B,N,S_max,D]."""
+    lib = load()
+    for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache)):
+        _require_cuda(name, t)
+    B, N, one, D = q.shape
+    if one != 1:
+        raise ValueError("decode takes one query token: q must be [B, N, 1, D]")
+    if k_cache.shape != v_cache.shape or k_cache.shape[0] != B or k_cache.shape[1] != N or k_cache.shape[3] != D:
+        raise ValueError("k_cache and v_cache must be [B, N, S_max, D]")
+    if k_cache.stride() != v_cache.stride():
+        raise ValueError("k_cache and v_cache must share strides")
+    q = q.contiguous()
+    y = out if out is not None else torch.empty_like(q)
+    if workspace is None:
+        workspace = DecodeWorkspace(B, N, D, q.device, num_splits)
+    a = DecodeArgs()
+    a.dtype = _DTYPES.get(q.dtype, -1)
+    a.B, a.N, a.S_max, a.D = B, N, k_cache.shape[2], D
+    a.q, a.k_cache, a.v_cache, a.y = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), y.data_ptr()
+    a.kv_stride = _strides3(k_cache)
+    sl = None
+    if seq_lens is not None:
+        sl = seq_lens.to(torch.int32).contiguous()
+        a.seq_lens = sl.data_ptr()
+    a.scale = float(scale if scale is not None else 1.0 / math.sqrt(D))
+    a.num_splits = num_splits
+    a.workspace, a.workspace_bytes = workspace.buf.data_ptr(), workspace.nbytes
+    with torch.cuda.device(q.device):
+        check(lib.acct_infer_decode(C.byref(a), _stream()))
+    return y

@@ -1,0 +1,211 @@
+/* acct_b200.h -- C ABI of libacct_b200.so: the attention hot path of acctransformer
+ * (FlashAttention2 forward / backward, TriangleAttention's block-causal tiling, and the
+ * inference prefill / decode op) as hand-written CUDA for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - Plain C types only.  Every pointer named "device" is a CUDA device pointer owned by the
+ *     caller; the library never allocates, frees or retains them.  `stream` is a cudaStream_t
+ *     passed as void* (NULL = the legacy default stream).  Calls enqueue work and return; they do
+ *     not synchronise the host.
+ *   - Tensors are [B, N, S, D] ("batch, heads, sequence, head_dim"), D contiguous.  The element
+ *     strides of B, N and S are given explicitly; 0 means "packed" (S stride D, N stride S*D,
+ *     B stride N*S*D).  Every stride must be a multiple of 8 elements (16 bytes) and every base
+ *     pointer 16-byte aligned.
+ *   - Return value: 0 on success, otherwise one of the ACCT_ERR_* codes; acct_last_error() gives
+ *     a message for the calling thread.  No C++ exception crosses this boundary.
+ *   - There is no CPU fallback: without a usable sm_100 device the entry points fail.
+ *
+ * Paths below are relative to the reference project (mindspore-ai/acctransformer).
+ */
+#ifndef ACCT_B200_H_
+#define ACCT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ACCT_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define ACCT_API __attribute__((visibility("default")))
+#else
+#define ACCT_API
+#endif
+
+/* element types */
+#define ACCT_F16 0
+#define ACCT_BF16 1
+#define ACCT_U8 2
+#define ACCT_F32 3
+
+/* status codes */
+#define ACCT_OK 0
+#define ACCT_ERR_NULL 1           /* a required pointer is NULL */
+#define ACCT_ERR_SHAPE 2          /* a dimension is out of range or inconsistent */
+#define ACCT_ERR_DTYPE 3          /* unsupported element type for this argument */
+#define ACCT_ERR_UNSUPPORTED_D 4  /* head_dim not a multiple of 8 or larger than the kernels take */
+#define ACCT_ERR_ALIGN 5          /* pointer or stride not 16-byte aligned */
+#define ACCT_ERR_WORKSPACE 6      /* workspace missing or too small */
+#define ACCT_ERR_CUDA 7           /* a CUDA call failed; acct_last_error() carries its text */
+#define ACCT_ERR_DEVICE_TIMEOUT 8 /* a kernel gave up on a bounded wait (see acct_device_status) */
+#define ACCT_ERR_NO_DEVICE 9      /* no sm_100 device / library built for another architecture */
+
+/* attn_mask forms */
+#define ACCT_MASK_NONE 0
+#define ACCT_MASK_FULL 1    /* [mask_batch, S_q, S_k], mask_batch in {1, B}; 1 = masked */
+#define ACCT_MASK_TILE128 2 /* [1,128,128], applied to diagonal 128x128 tiles only */
+
+/* "no limit" for prev_block_num / next_block_num (the reference's default) */
+#define ACCT_BAND_UNBOUNDED 65536
+/* the band predicate is evaluated on 128x128 tiles */
+#define ACCT_BAND_BLOCK 128
+/* value added to a score per unit of attn_mask */
+#define ACCT_MASK_FILL_VALUE (-10000.0f)
+
+/* flags */
+#define ACCT_FLAG_GRAD_F32 1u      /* acct_fa_bwd writes dq/dk/dv as fp32 (what the reference primitive returns) */
+#define ACCT_FLAG_DETERMINISTIC 2u /* acct_fa_bwd reduces dq in a fixed order */
+
+/* Arguments shared by the training forward and backward.
+ *
+ * Replaces the I/O contract of the reference's forward primitive
+ *   train/acctransformer/flash_attention/ops/flash_attention/flash_attention_impl.py:30-56,129-154
+ *   inputs  query, key, value, [attn_mask], [dropout_mask], [alibi_mask]; outputs output, rowsum;
+ *   attrs   prev_block_num, next_block_num, tiling_stgy_name (tile sizes are internal here).
+ * Semantics per (b, n) slice, all arithmetic in fp32 except the two matrix products, whose
+ * operands are the 16-bit inputs / the 16-bit rounded probabilities:
+ *   S = scale * Q K^T + alibi[b,n,0,:] + (-10000) * attn_mask[b or 0]     (flash_attention_fwd.py:308-392,
+ *                                                                           attention.py:347-371)
+ *   entries outside the block band  j - next <= i <= j + prev  (128-tiles i, j), above the diagonal
+ *   when `causal`, or at key positions >= seq_lens[b] do not exist       (flash_attention_fwd.py:444-445)
+ *   P = softmax(S);  O = (P * dropout_mask / keep_prob) V;  lse = rowmax(S) + log(rowsum(exp(S - rowmax)))
+ *                                                                          (flash_attention_fwd.py:117-153,258-306)
+ */
+typedef struct acct_fa_args {
+  int32_t dtype;            /* ACCT_F16 or ACCT_BF16: type of q, k, v, o, do, alibi */
+  int32_t B, N, S_q, S_k, D;
+  const void* q;            /* device [B,N,S_q,D] */
+  const void* k;            /* device [B,N,S_k,D] */
+  const void* v;            /* device [B,N,S_k,D] */
+  void* o;                  /* device [B,N,S_q,D]; written by fwd, read by bwd */
+  float* lse;               /* device [B,N,S_q] fp32, packed; written by fwd (may be NULL), read by bwd */
+  int64_t q_stride[3];      /* element strides of B, N, S; 0 = packed */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  int32_t mask_kind;        /* ACCT_MASK_* */
+  int32_t mask_dtype;       /* ACCT_F16 / ACCT_BF16 / ACCT_U8 */
+  int32_t mask_batch;       /* 1 or B (ACCT_MASK_FULL) */
+  int32_t causal;           /* 1: key j > query i does not exist (no mask tensor is read for it) */
+  const void* attn_mask;    /* device, see mask_kind */
+  const void* dropout_mask; /* device [B,N,S_q,S_k] or NULL */
+  int32_t dropout_dtype;    /* ACCT_U8: {0,1}, P is multiplied by mask/keep_prob;
+                               ACCT_F16/ACCT_BF16: values {0, 1/keep_prob} as the reference cell builds them
+                               (nn/layer/flash_attention.py:198-203), P is multiplied by the value */
+  float keep_prob;          /* 1 - dropout_rate; used with ACCT_U8 */
+  const void* alibi;        /* device [B,N,1,S_k] in `dtype`, packed, or NULL */
+  const float* alibi_slopes;/* device [N] fp32 or NULL: bias = slope[n] * key_position (computed, not loaded) */
+  int32_t prev_block_num;   /* >= ACCT_BAND_UNBOUNDED: no limit */
+  int32_t next_block_num;
+  float scale;              /* multiplies Q K^T; 1.0 = the raw primitive, head_dim^-1/2 = what the cell's two
+                               fp16 multiplies by head_dim^-1/4 amount to (nn/layer/flash_attention.py:188-189) */
+  const int32_t* seq_lens;  /* device [B] int32 or NULL: valid key count per batch entry */
+  uint32_t flags;           /* ACCT_FLAG_* */
+  uint32_t reserved;
+} acct_fa_args;
+
+/* Extra I/O of the backward.
+ *
+ * Replaces the reference's grad primitive
+ *   train/acctransformer/flash_attention/ops/flash_attention/flash_attention_impl.py:59-126
+ *   inputs query, key, value, output, do, rowsum, [attn_mask], [dropout_mask], [alibi_mask] -> dq, dk, dv (fp32),
+ * which `bprop` then casts to fp16 (:117-124).  dq/dk/dv here are written in `dtype` unless
+ * ACCT_FLAG_GRAD_F32 is set.  Gradient strides follow q / k / v strides when packed == 0.
+ *   dV = (P*M)^T dO;  dP = (dO V^T)*M;  Dl = rowsum(dO*O);  dS = P*(dP - Dl);
+ *   dQ = scale * dS K;  dK = scale * dS^T Q     (flash_attention_bwd.py:88-257, with M = dropout_mask/keep_prob)
+ */
+typedef struct acct_fa_bwd_io {
+  const void* d_o;          /* device [B,N,S_q,D], strides = o_stride */
+  void* dq;                 /* device [B,N,S_q,D] packed */
+  void* dk;                 /* device [B,N,S_k,D] packed */
+  void* dv;                 /* device [B,N,S_k,D] packed */
+  void* workspace;          /* device, >= acct_fa_bwd_workspace_bytes(); contents undefined on entry */
+  size_t workspace_bytes;
+} acct_fa_bwd_io;
+
+/* Forward: writes o and (if non-NULL) lse. */
+ACCT_API int acct_fa_fwd(const acct_fa_args* a, void* stream);
+
+/* Bytes of scratch acct_fa_bwd needs for `a` (row sums Dl and an fp32 dQ accumulator).
+ * The reference declares its fp32 gradient outputs "atomic add" buffers that the runtime zero-fills
+ * (flash_attention_bwd.py:55-57); here the library zero-fills its own accumulator on `stream`. */
+ACCT_API size_t acct_fa_bwd_workspace_bytes(const acct_fa_args* a);
+
+/* Backward: reads q,k,v,o,lse,d_o (+ the same mask/dropout/alibi/band arguments as the forward). */
+ACCT_API int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream);
+
+/* Inference op  y = softmax(scale * q k^T) v.
+ *
+ * Replaces  FlashAttentionTik(q, k, v) -> y
+ *   infer/flash_attention/tik/op_proto/flash_attention_tik.h:22-27 (registration),
+ *   infer/flash_attention/tik/op_proto/flash_attention_tik.cpp:30-193 (shape checks: rank 3 or 4, k and v of
+ *   equal shape, q/k/v agreeing on batch*heads and head_dim, y shaped like q),
+ *   infer/flash_attention/tik/tbe/impl/flash_attention_fwd.py:19-748 (kernel).
+ * The reference op has no scale, mask or lengths: scale = 1, causal = 0, seq_lens = NULL reproduce it;
+ * the other settings are this library's extensions.  rank 3 ([B*N,S,D]) is expressed as B = 1.
+ */
+typedef struct acct_infer_args {
+  int32_t dtype;
+  int32_t rank;             /* 3 or 4, validated like the reference's InferShape; layout is the same memory */
+  int32_t B, N, S_q, S_k, D;
+  const void* q;
+  const void* k;
+  const void* v;
+  void* y;
+  int32_t causal;
+  float scale;
+  const int32_t* seq_lens;  /* device [B] or NULL */
+} acct_infer_args;
+
+ACCT_API int acct_infer_prefill(const acct_infer_args* a, void* stream);
+
+/* Decode (one query token per sequence over a KV cache).  The reference has no decode path; this is the
+ * q_len = 1 case of the op above with per-sequence valid lengths:
+ *   y[b,n,0,:] = softmax(scale * q[b,n,0,:] K[b,n,0:len_b,:]^T) V[b,n,0:len_b,:]
+ * Keys are split into `num_splits` ranges processed by separate thread blocks; partial (max, sum, acc)
+ * triples go to `workspace` and a second kernel merges them. */
+typedef struct acct_decode_args {
+  int32_t dtype;
+  int32_t B, N, S_max, D;
+  const void* q;            /* device [B,N,1,D] packed */
+  const void* k_cache;      /* device [B,N,S_max,D] */
+  const void* v_cache;      /* device [B,N,S_max,D] */
+  int64_t kv_stride[3];     /* element strides of B, N, S in the caches; 0 = packed */
+  const int32_t* seq_lens;  /* device [B] int32, each in [1, S_max]; NULL = S_max everywhere */
+  void* y;                  /* device [B,N,1,D] packed */
+  float scale;
+  int32_t num_splits;       /* 0 = choose from the device's SM count */
+  void* workspace;          /* device, >= acct_infer_decode_workspace_bytes() */
+  size_t workspace_bytes;
+} acct_decode_args;
+
+ACCT_API size_t acct_infer_decode_workspace_bytes(const acct_decode_args* a);
+ACCT_API int acct_infer_decode(const acct_decode_args* a, void* stream);
+
+/* Reads and clears the device-side status word of the current device (synchronises `stream`).
+ * Returns ACCT_OK, or ACCT_ERR_DEVICE_TIMEOUT if some kernel gave up on a bounded wait since the last call. */
+ACCT_API int acct_device_status(void* stream);
+
+/* Message for the last non-zero return on the calling thread ("" if none). */
+ACCT_API const char* acct_last_error(void);
+
+/* ACCT_ABI_VERSION the library was built with. */
+ACCT_API int acct_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ACCT_B200_H_ */
