@@ -1,6 +1,442 @@
+// FlashAttention-2 backward for sm_100a.
+//
+// One CTA owns one 128-row K/V tile of one (batch, head) slice and walks the Q tiles that touch
+// it; dK and dV accumulate in tensor memory for the whole walk, dQ tiles are reduced into an fp32
+// global accumulator.  Scores are recomputed TRANSPOSED (rows = keys, columns = queries) so that
+// P^T and dS^T come out in the layout the dV / dK products need:
+//   S^T  = K_j Q_i^T          (tcgen05, both operands K-major from shared memory)
+//   dP^T = V_j dO_i^T
+//   P^T  = exp2(S^T*scale*log2e - L_i*log2e);  dS^T = P^T * (dP^T * M - D_i)        (registers)
+//   dV  += (P^T*M) dO_i       (A from tensor memory, written over S^T; B = dO_i, MN-major)
+//   dK  += dS^T Q_i           (A = dS^T from shared memory, K-major; B = Q_i, MN-major)
+//   dQ_i = dS K_j             (A = the same dS^T tile read MN-major; B = K_j, MN-major) -> over dP^T
+// Warp roles: warps 0-3 compute (thread t owns key row t), warp 4 = TMA producer, warp 5 = MMA
+// issuer.  Tensor memory: S^T/P^T | dP^T/dQ | dK | dV, 128 columns each.
+//
+// Follows the reference's backward (train/acctransformer/flash_attention/ops/flash_attention/
+// flash_attention_bwd.py:259-415): K/V tile outer, Q tile inner, P recomputed from L, D = rowsum(dO*O)
+// (:138-159, here computed once by a separate kernel instead of per tile pair), dS with the
+// un-dropped P (:161-181), fp32 accumulation of dQ/dK/dV (:183-257).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "fa_common.cuh"
 #include "fa_kernels.cuh"
+#include "ptx.cuh"
+
 namespace acct {
-cudaError_t launch_fa_bwd(const BwdParams&, bool, cudaStream_t) { return cudaErrorNotSupported; }
-cudaError_t launch_bwd_delta(const void*, const void*, float*, int64_t, int, int64_t, int64_t, int64_t, int, int, bool, cudaStream_t) { return cudaErrorNotSupported; }
-cudaError_t launch_bwd_convert_dq(const float*, void*, int64_t, bool, bool, cudaStream_t) { return cudaErrorNotSupported; }
+
+namespace {
+
+constexpr int kBwdThreads = 192;
+constexpr int kQStages = 2;
+
+struct BwdShared {
+  uint64_t kv_full;
+  uint64_t q_full[kQStages];
+  uint64_t do_full;
+  uint64_t st_full, dp_full;
+  uint64_t pds_ready;     // compute -> MMA: P^T in tensor memory, dS^T in shared memory
+  uint64_t tail_done;     // MMA -> everyone: dV, dK, dQ products of this Q tile finished
+  uint64_t dq_read;       // compute -> MMA: dQ has been drained, dP^T columns are free again
+  uint64_t stats_ready;   // compute -> compute: lse2 / delta of this Q tile are in shared memory
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+  float lse2[2][kTile];   // L * log2(e) per query of the tile (+inf for rows past S_q)
+  float delta[2][kTile];
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
 }
+
+}  // namespace
+
+template <int DPAD, bool BF16>
+__global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_constant__ BwdParams p) {
+  constexpr int NB = DPAD / 64;
+  constexpr uint32_t kTileBytes = NB * 16384u;   // 128 rows x DPAD 16-bit elements
+  constexpr uint32_t kDsBytes = 32768u;          // dS^T: 128 key rows x 128 query columns
+  constexpr uint32_t kColST = 0, kColDP = 128, kColDK = 256, kColDV = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + kTileBytes;
+  uint8_t* sQ = sV + kTileBytes;                 // kQStages tiles
+  uint8_t* sDO = sQ + kQStages * kTileBytes;
+  uint8_t* sDS = sDO + kTileBytes;
+  __shared__ BwdShared sh;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int b = bh / p.N, h = bh % p.N;
+  const int j = blockIdx.x;                      // K/V tile
+  const ScoreMods& mods = p.mods;
+
+  int kv_len = p.S_k;
+  if (mods.seq_lens != nullptr) kv_len = min(p.S_k, max(0, mods.seq_lens[b]));
+
+  // Q tiles i that need K/V tile j:  j - next <= i <= j + prev, i >= j under the causal triangle
+  int i_lo = 0, i_hi = (p.S_q + kTile - 1) / kTile - 1;
+  if (mods.next_block_num < 65536) i_lo = max(i_lo, j - mods.next_block_num);
+  if (mods.prev_block_num < 65536) i_hi = min(i_hi, j + mods.prev_block_num);
+  if (mods.causal) i_lo = max(i_lo, j);
+  if (j * kTile >= kv_len) i_hi = i_lo - 1;
+  const int n_iter = max(0, i_hi - i_lo + 1);
+
+  if (tid == 0) {
+    mbar_init(&sh.kv_full, 1);
+    for (int s = 0; s < kQStages; ++s) mbar_init(&sh.q_full[s], 1);
+    mbar_init(&sh.do_full, 1);
+    mbar_init(&sh.st_full, 1);
+    mbar_init(&sh.dp_full, 1);
+    mbar_init(&sh.pds_ready, 128);
+    mbar_init(&sh.tail_done, 1);
+    mbar_init(&sh.dq_read, 128);
+    mbar_init(&sh.stats_ready, 128);
+    sh.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) { tmem_alloc(&sh.tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sh.tmem_base;
+  volatile uint32_t* abort_flag = &sh.abort_flag;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_iter > 0) {
+      prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_do);
+      mbar_expect_tx(&sh.kv_full, 2 * kTileBytes);
+      for (int nb = 0; nb < NB; ++nb) tma_load_4d(sK + nb * 16384, &p.map_k, &sh.kv_full, nb * 64, j * kTile, h, b);
+      for (int nb = 0; nb < NB; ++nb) tma_load_4d(sV + nb * 16384, &p.map_v, &sh.kv_full, nb * 64, j * kTile, h, b);
+      for (int n = 0; n < n_iter; ++n) {
+        const int i = i_lo + n;
+        const int st = n % kQStages;
+        // Q stage st was last read by the products of iteration n-2, whose completion this thread
+        // already observed before loading dO in iteration n-1; dO is read by those of iteration n-1.
+        mbar_expect_tx(&sh.q_full[st], kTileBytes);
+        for (int nb = 0; nb < NB; ++nb)
+          tma_load_4d(sQ + st * kTileBytes + nb * 16384, &p.map_q, &sh.q_full[st], nb * 64, i * kTile, h, b);
+        if (n >= 1 && !mbar_wait(&sh.tail_done, (n - 1) & 1, abort_flag)) {
+          *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break;
+        }
+        mbar_expect_tx(&sh.do_full, kTileBytes);
+        for (int nb = 0; nb < NB; ++nb)
+          tma_load_4d(sDO + nb * 16384, &p.map_do, &sh.do_full, nb * 64, i * kTile, h, b);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_iter > 0) {
+      const uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);     // S^T, dP^T
+      const uint32_t idesc_kv = make_idesc(BF16, 128, DPAD, false, true);    // dV, dK
+      const uint32_t idesc_dq = make_idesc(BF16, 128, DPAD, true, true);     // dQ
+      const uint64_t kmajor = make_sdesc_base(16, 1024);
+      const uint64_t mnmajor = make_sdesc_base(16384, 1024);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
+      bool ok = mbar_wait(&sh.kv_full, 0, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); }
+      for (int n = 0; ok && n < n_iter; ++n) {
+        const int st = n % kQStages;
+        const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
+        // S^T = K Q^T (its tensor-memory columns were last read by the dV product of iteration n-1,
+        // which the tensor pipe finishes first)
+        ok = mbar_wait(&sh.q_full[st], (n / kQStages) & 1, abort_flag);
+        if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < DPAD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
+          umma_ss(tmem + kColST, sdesc_at(kmajor, aK + off), sdesc_at(kmajor, aQ + off), idesc_s, kk > 0);
+        }
+        umma_commit(&sh.st_full);
+        // dP^T = V dO^T, once the previous dQ has been drained from those columns
+        ok = mbar_wait(&sh.do_full, n & 1, abort_flag);
+        if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); break; }
+        if (n > 0) {
+          ok = mbar_wait(&sh.dq_read, (n - 1) & 1, abort_flag);
+          if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break; }
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < DPAD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
+          umma_ss(tmem + kColDP, sdesc_at(kmajor, aV + off), sdesc_at(kmajor, aDO + off), idesc_s, kk > 0);
+        }
+        umma_commit(&sh.dp_full);
+        // the three products that consume P^T and dS^T
+        ok = mbar_wait(&sh.pds_ready, n & 1, abort_flag);
+        if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)   // dV += P^T dO
+          umma_ts(tmem + kColDV, tmem + kColST + kk * 8, sdesc_at(mnmajor, aDO + kk * 2048u), idesc_kv, n > 0 || kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)   // dK += dS^T Q
+          umma_ss(tmem + kColDK, sdesc_at(kmajor, aDS + (kk >> 2) * 16384u + (kk & 3) * 32u),
+                  sdesc_at(mnmajor, aQ + kk * 2048u), idesc_kv, n > 0 || kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)   // dQ = dS K
+          umma_ss(tmem + kColDP, sdesc_at(mnmajor, aDS + kk * 2048u), sdesc_at(mnmajor, aK + kk * 2048u), idesc_dq, kk > 0);
+        umma_commit(&sh.tail_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    const int r = tid;                                   // key row inside the tile (and dQ row when draining)
+    const int kv_idx = j * kTile + r;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t t_st = tmem + lane_base + kColST;
+    const uint32_t t_dp = tmem + lane_base + kColDP;
+    const bool kv_ok = kv_idx < kv_len;
+    float alibi_l2 = 0.f;
+    if (kv_ok) {
+      if (mods.alibi != nullptr) alibi_l2 = load16<BF16>(mods.alibi, static_cast<int64_t>(bh) * p.S_k + kv_idx) * kLog2e;
+      else if (mods.alibi_slopes != nullptr) alibi_l2 = mods.alibi_slopes[h] * static_cast<float>(kv_idx) * kLog2e;
+    }
+    bool ok = true;
+    for (int n = 0; n < n_iter; ++n) {
+      const int i = i_lo + n;
+      const int q_base = i * kTile;
+      {
+        const int q_row = q_base + r;
+        const bool q_ok = q_row < p.S_q;
+        const int64_t idx = static_cast<int64_t>(bh) * p.S_q + q_row;
+        sh.lse2[n & 1][r] = q_ok ? p.lse[idx] * kLog2e : INFINITY;
+        sh.delta[n & 1][r] = q_ok ? p.delta[idx] : 0.f;
+      }
+      // an mbarrier rather than a named barrier, so that this hand-off is bounded like every other wait
+      mbar_arrive(&sh.stats_ready);
+      ok = mbar_wait(&sh.stats_ready, n & 1, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break; }
+      const float* lse2 = sh.lse2[n & 1];
+      const float* dlt = sh.delta[n & 1];
+      ok = mbar_wait(&sh.st_full, n & 1, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); break; }
+      ok = mbar_wait(&sh.dp_full, n & 1, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); break; }
+      tc_fence_after_sync();
+      const bool use_mask = (mods.mask_kind == 1) || (mods.mask_kind == 2 && i == j);
+      const bool diag = mods.causal && (q_base < j * kTile + kTile - 1);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32], dp[32];
+        tmem_ld32(t_st + c * 32, s);
+        tmem_ld32(t_dp + c * 32, dp);
+        tmem_wait_ld();
+        uint32_t pk[16], dk_[16];
+        float pd_prev = 0.f, ds_prev = 0.f;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int q_row = q_base + c * 32 + e;
+          float x = fmaf(__uint_as_float(s[e]), p.scale_log2, alibi_l2);
+          if (use_mask && kv_ok && q_row < p.S_q) {
+            const float mv = mods.mask_kind == 1
+                                 ? load_mask_value(mods.mask, mods.mask_dtype,
+                                                   (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q + q_row) * p.S_k + kv_idx)
+                                 : load_mask_value(mods.mask, mods.mask_dtype, static_cast<int64_t>(c * 32 + e) * kTile + r);
+            x += mv * (-10000.0f * kLog2e);
+          }
+          float pr = ex2(x - lse2[c * 32 + e]);
+          if (!kv_ok || (diag && kv_idx > q_row)) pr = 0.f;
+          float fac = 1.0f;
+          if (mods.drop != nullptr) {
+            fac = 0.f;
+            if (kv_ok && q_row < p.S_q)
+              fac = load_mask_value(mods.drop, mods.drop_dtype,
+                                    (static_cast<int64_t>(bh) * p.S_q + q_row) * p.S_k + kv_idx) * mods.drop_scale;
+          }
+          const float pd = pr * fac;
+          const float ds = pr * (__uint_as_float(dp[e]) * fac - dlt[c * 32 + e]);
+          if (e & 1) {
+            pk[e >> 1] = pack2<BF16>(pd_prev, pd);
+            dk_[e >> 1] = pack2<BF16>(ds_prev, ds);
+          } else {
+            pd_prev = pd;
+            ds_prev = ds;
+          }
+        }
+        tmem_st16(t_st + c * 16, pk);
+        // dS^T row r, query columns [32c, 32c+32) -> 64 bytes = four 16-byte chunks of block c/2
+        uint8_t* blk = sDS + (c >> 1) * 16384u;
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          *reinterpret_cast<uint4*>(blk + swz128(r, (c & 1) * 4 + g)) =
+              make_uint4(dk_[4 * g], dk_[4 * g + 1], dk_[4 * g + 2], dk_[4 * g + 3]);
+      }
+      tmem_wait_st();
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&sh.pds_ready);
+
+      // drain dQ_i (thread t now owns query row t of the tile) into the fp32 accumulator
+      ok = mbar_wait(&sh.tail_done, n & 1, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); break; }
+      tc_fence_after_sync();
+      {
+        const int q_row = q_base + r;
+        float* dst = p.dq_acc + (static_cast<int64_t>(bh) * p.S_q + q_row) * p.D;
+#pragma unroll 1
+        for (int c = 0; c < DPAD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(t_dp + c * 32, v);
+          tmem_wait_ld();
+          if (q_row < p.S_q) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const int col = c * 32 + g * 4;
+              if (col + 4 <= p.D)
+                red_add_v4(dst + col, __uint_as_float(v[4 * g]) * p.scale, __uint_as_float(v[4 * g + 1]) * p.scale,
+                           __uint_as_float(v[4 * g + 2]) * p.scale, __uint_as_float(v[4 * g + 3]) * p.scale);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&sh.dq_read);
+    }
+
+    // epilogue: dK (scaled) and dV rows of this tile
+    // (the tensor-memory loads are warp-collective: every lane runs them, only the stores are guarded)
+    if (ok) {
+      tc_fence_after_sync();
+      const bool row_ok = kv_idx < p.S_k;
+      const int64_t row_off = (static_cast<int64_t>(bh) * p.S_k + kv_idx) * p.D;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t t_src = tmem + lane_base + (which == 0 ? kColDK : kColDV);
+        const float mul = which == 0 ? p.scale : 1.0f;
+        void* out = which == 0 ? p.dk : p.dv;
+#pragma unroll 1
+        for (int c = 0; c < DPAD / 32; ++c) {
+          uint32_t v[32];
+          if (n_iter > 0) { tmem_ld32(t_src + c * 32, v); tmem_wait_ld(); }
+          else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0u;
+          }
+          if (!row_ok) continue;
+          if (p.grads_f32) {
+            float* dst = reinterpret_cast<float*>(out) + row_off;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const int col = c * 32 + g * 4;
+              if (col + 4 <= p.D)
+                *reinterpret_cast<float4*>(dst + col) =
+                    make_float4(__uint_as_float(v[4 * g]) * mul, __uint_as_float(v[4 * g + 1]) * mul,
+                                __uint_as_float(v[4 * g + 2]) * mul, __uint_as_float(v[4 * g + 3]) * mul);
+            }
+          } else {
+            uint8_t* dst = reinterpret_cast<uint8_t*>(out) + row_off * 2;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = c * 32 + g * 8;
+              if (col + 8 <= p.D) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  w[e] = pack2<BF16>(__uint_as_float(v[8 * g + 2 * e]) * mul, __uint_as_float(v[8 * g + 2 * e + 1]) * mul);
+                *reinterpret_cast<uint4*>(dst + col * 2) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before_sync();
+  }
+
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// D[row] = sum_d dO[row,d] * O[row,d]  (fp32), one warp per row.
+template <bool BF16>
+__global__ void bwd_delta_kernel(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t sb,
+                                 int64_t sh_, int64_t ss, int N, int S_q) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t bh = row / S_q;
+  const int64_t off = (bh / N) * sb + (bh % N) * sh_ + (row % S_q) * ss;
+  float acc = 0.f;
+  if (lane * 8 < D) {
+    const uint4 a = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(o) + off + lane * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(d_o) + off + lane * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 x, y;
+      if constexpr (BF16) {
+        x = make_float2(__uint_as_float(aw[e] << 16), __uint_as_float(aw[e] & 0xffff0000u));
+        y = make_float2(__uint_as_float(gw[e] << 16), __uint_as_float(gw[e] & 0xffff0000u));
+      } else {
+        x = __half22float2(*reinterpret_cast<const __half2*>(&aw[e]));
+        y = __half22float2(*reinterpret_cast<const __half2*>(&gw[e]));
+      }
+      acc = fmaf(x.x, y.x, acc);
+      acc = fmaf(x.y, y.y, acc);
+    }
+  }
+#pragma unroll
+  for (int off2 = 16; off2 > 0; off2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off2);
+  if (lane == 0) delta[row] = acc;
+}
+
+template <bool BF16>
+__global__ void bwd_convert_kernel(const float* __restrict__ src, void* __restrict__ dst, int64_t n, int f32_out) {
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;   // n is a multiple of 8 (head_dim is)
+  const float4 a = *reinterpret_cast<const float4*>(src + i);
+  const float4 c = *reinterpret_cast<const float4*>(src + i + 4);
+  if (f32_out) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + i) = a;
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + i + 4) = c;
+  } else {
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dst) + i) =
+        make_uint4(pack2<BF16>(a.x, a.y), pack2<BF16>(a.z, a.w), pack2<BF16>(c.x, c.y), pack2<BF16>(c.z, c.w));
+  }
+}
+
+cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
+  const int dpad = p.D <= 64 ? 64 : 128;
+  const size_t smem = static_cast<size_t>(3 + kQStages) * (dpad / 64) * 16384 + 32768 + 1024;
+  dim3 grid((p.S_k + kTile - 1) / kTile, p.B * p.N);
+  void (*kern)(const BwdParams) = nullptr;
+  if (dpad == 64) kern = bf16 ? fa_bwd_kernel<64, true> : fa_bwd_kernel<64, false>;
+  else kern = bf16 ? fa_bwd_kernel<128, true> : fa_bwd_kernel<128, false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  kern<<<grid, kBwdThreads, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bwd_delta(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t o_stride_b,
+                             int64_t o_stride_h, int64_t o_stride_s, int N, int S_q, bool bf16,
+                             cudaStream_t stream) {
+  const int warps = 8;
+  const unsigned blocks = static_cast<unsigned>((rows + warps - 1) / warps);
+  if (bf16) bwd_delta_kernel<true><<<blocks, warps * 32, 0, stream>>>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q);
+  else bwd_delta_kernel<false><<<blocks, warps * 32, 0, stream>>>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bwd_convert_dq(const float* dq_acc, void* dq, int64_t n_elems, bool bf16, bool f32_out,
+                                  cudaStream_t stream) {
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((n_elems / 8 + threads - 1) / threads);
+  if (bf16) bwd_convert_kernel<true><<<blocks, threads, 0, stream>>>(dq_acc, dq, n_elems, f32_out ? 1 : 0);
+  else bwd_convert_kernel<false><<<blocks, threads, 0, stream>>>(dq_acc, dq, n_elems, f32_out ? 1 : 0);
+  return cudaGetLastError();
+}
+
+}  // namespace acct
