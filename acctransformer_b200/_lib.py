@@ -51,7 +51,7 @@ class FaArgs(C.Structure):
         ("prev_block_num", C.c_int32), ("next_block_num", C.c_int32),
         ("scale", C.c_float),
         ("seq_lens", C.c_void_p),
-        ("flags", C.c_uint32), ("reserved", C.c_uint32),
+        ("flags", C.c_uint32), ("tri_block", C.c_int32),
     ]
 
 

@@ -182,6 +182,7 @@ int validate_fa(const acct_fa_args* a, Strides* st) {
     if (a->dropout_dtype == ACCT_U8 && !(a->keep_prob > 0.f && a->keep_prob <= 1.f))
       return fail(ACCT_ERR_SHAPE, "keep_prob must be in (0, 1]");
   }
+  if (a->tri_block < 0) return fail(ACCT_ERR_SHAPE, "tri_block must be >= 0");
   if (a->alibi && a->alibi_slopes) return fail(ACCT_ERR_SHAPE, "give either alibi or alibi_slopes, not both");
   return 0;
 }
@@ -201,6 +202,7 @@ ScoreMods make_mods(const acct_fa_args* a) {
   m.alibi = a->alibi;
   m.alibi_slopes = a->alibi_slopes;
   m.seq_lens = a->seq_lens;
+  m.tri_block = a->tri_block;
   return m;
 }
 
@@ -363,10 +365,11 @@ int acct_infer_decode(const acct_decode_args* a, void* stream) {
   int64_t kvs[3];
   int rc = check_strides("kv", a->kv_stride, a->S_max, a->N, a->D, kvs);
   if (rc) return rc;
-  DeviceInfo info;
-  if ((rc = device_info(&info))) return rc;
   int splits = a->num_splits;
   if (splits < 0 || splits > 64) return fail(ACCT_ERR_SHAPE, "num_splits must be in [0, 64]");
+  if (static_cast<int64_t>(a->B) * a->N > 65535) return fail(ACCT_ERR_SHAPE, "B*N = %lld exceeds 65535", (long long)a->B * a->N);
+  DeviceInfo info;
+  if ((rc = device_info(&info))) return rc;
   if (splits == 0) {
     // enough CTAs for ~4 waves of 2 resident CTAs per SM, but never splits shorter than 256 keys
     const int64_t units = static_cast<int64_t>(a->B) * a->N;

@@ -44,6 +44,7 @@ struct BwdShared {
   volatile uint32_t abort_flag;
   float lse2[2][kTile];   // L * log2(e) per query of the tile (+inf for rows past S_q)
   float delta[2][kTile];
+  int tri_end[2][kTile];  // first key index that does not exist for each query of the tile
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -85,6 +86,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   if (mods.next_block_num < 65536) i_lo = max(i_lo, j - mods.next_block_num);
   if (mods.prev_block_num < 65536) i_hi = min(i_hi, j + mods.prev_block_num);
   if (mods.causal) i_lo = max(i_lo, j);
+  if (mods.tri_block > 0) i_lo = max(i_lo, (((j * kTile) / mods.tri_block) * mods.tri_block) / kTile);
   if (j * kTile >= kv_len) i_hi = i_lo - 1;
   const int n_iter = max(0, i_hi - i_lo + 1);
 
@@ -210,6 +212,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         const int64_t idx = static_cast<int64_t>(bh) * p.S_q + q_row;
         sh.lse2[n & 1][r] = q_ok ? p.lse[idx] * kLog2e : INFINITY;
         sh.delta[n & 1][r] = q_ok ? p.delta[idx] : 0.f;
+        sh.tri_end[n & 1][r] = mods.tri_block > 0 ? (min(q_row, p.S_q - 1) / mods.tri_block + 1) * mods.tri_block : 0x7fffffff;
       }
       // an mbarrier rather than a named barrier, so that this hand-off is bounded like every other wait
       mbar_arrive(&sh.stats_ready);
@@ -217,6 +220,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break; }
       const float* lse2 = sh.lse2[n & 1];
       const float* dlt = sh.delta[n & 1];
+      const int* tri_end = sh.tri_end[n & 1];
       ok = mbar_wait(&sh.st_full, n & 1, abort_flag);
       if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); break; }
       ok = mbar_wait(&sh.dp_full, n & 1, abort_flag);
@@ -244,7 +248,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
             x += mv * (-10000.0f * kLog2e);
           }
           float pr = ex2(x - lse2[c * 32 + e]);
-          if (!kv_ok || (diag && kv_idx > q_row)) pr = 0.f;
+          if (!kv_ok || (diag && kv_idx > q_row) || kv_idx >= tri_end[c * 32 + e]) pr = 0.f;
           float fac = 1.0f;
           if (mods.drop != nullptr) {
             fac = 0.f;

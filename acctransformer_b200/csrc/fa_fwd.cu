@@ -45,6 +45,12 @@ __device__ __forceinline__ TileRange kv_tile_range(int i, int s_q, int kv_len, c
   if (m.prev_block_num < 65536) r.lo = max(r.lo, i - m.prev_block_num);
   if (m.next_block_num < 65536) r.hi = min(r.hi, i + m.next_block_num);
   if (m.causal) r.hi = min(r.hi, i);
+  if (m.tri_block > 0) {
+    // the tile's last row belongs to the latest row group of the tile, which sees the most keys
+    const int last_row = min(i * kTile + kTile - 1, s_q - 1);
+    const int q_end = (last_row / m.tri_block + 1) * m.tri_block;
+    r.hi = min(r.hi, (q_end - 1) / kTile);
+  }
   return r;
 }
 
@@ -222,6 +228,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q + min(q_row, p.S_q - 1)) * p.S_k;
     const int64_t drop_row = (static_cast<int64_t>(bh) * p.S_q + min(q_row, p.S_q - 1)) * p.S_k;
 
+    // keys at or past this index do not exist for this thread's row (TriangleAttention row groups)
+    const int tri_end = mods.tri_block > 0 ? (min(q_row, p.S_q - 1) / mods.tri_block + 1) * mods.tri_block : 0x7fffffff;
+    const int tri_end_tile = mods.tri_block > 0 ? ((q_tile * kTile) / mods.tri_block + 1) * mods.tri_block : 0x7fffffff;
+
     float m_run = kNegInf, l_run = 0.f;
     int n = 0;
     bool ok = true;
@@ -233,7 +243,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       const bool diag = mods.causal && (col_base + kTile - 1 > q_tile * kTile);
       const bool tail = col_base + kTile > kv_len;
       const bool use_mask = (mods.mask_kind == 1) || (mods.mask_kind == 2 && j == q_tile);
-      const bool transform = diag || tail || use_mask || has_alibi;
+      const bool tri_partial = col_base + kTile > tri_end_tile;
+      const bool transform = diag || tail || use_mask || has_alibi || tri_partial;
 
       // pass 1: (transform and) row max
       float m_tile = kNegInf;
@@ -258,7 +269,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
                 x += mv * (-10000.0f * kLog2e);
               }
             }
-            if (col >= kv_len || (mods.causal && col > q_row)) x = kNegInf;
+            if (col >= kv_len || col >= tri_end || (mods.causal && col > q_row)) x = kNegInf;
             r[i] = __float_as_uint(x);
             m_tile = fmaxf(m_tile, x);
           }

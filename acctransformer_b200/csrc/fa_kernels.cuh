@@ -22,6 +22,7 @@ struct ScoreMods {
   const void* alibi;                // [B,N,1,S_k] in the tensor dtype
   const float* alibi_slopes;        // [N]
   const int* seq_lens;              // [B]
+  int tri_block;                    // > 0: query row r sees keys < (r / tri_block + 1) * tri_block only
 };
 
 struct alignas(64) FwdParams {

@@ -37,7 +37,7 @@ def _strides3(t):
 
 
 def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
-                  alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, flags=0):
+                  alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, flags=0, tri_block=0):
     for name, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda(name, t)
         if t.dim() != 4:
@@ -105,18 +105,19 @@ def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask
         keep.append(sl)
         a.seq_lens = sl.data_ptr()
     a.flags = flags
+    a.tri_block = int(tri_block)
     return a, keep
 
 
 def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dropout_mask=None,
                keep_prob=1.0, alibi=None, alibi_slopes=None, prev_block_num=BAND_UNBOUNDED,
-               next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None, need_lse=True):
+               next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None, need_lse=True, tri_block=0):
     """Forward primitive: returns (output [B,N,S_q,D] in q's dtype, lse [B,N,S_q] fp32 or None)."""
     lib = load()
     o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if need_lse else None
     a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
-                            alibi_slopes, prev_block_num, next_block_num, scale, seq_lens)
+                            alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, tri_block=tri_block)
     with torch.cuda.device(q.device):
         check(lib.acct_fa_fwd(C.byref(a), _stream()))
     del keep
@@ -126,7 +127,7 @@ def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dro
 def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, causal=False,
                 dropout_mask=None, keep_prob=1.0, alibi=None, alibi_slopes=None,
                 prev_block_num=BAND_UNBOUNDED, next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None,
-                grads_fp32=False):
+                grads_fp32=False, tri_block=0):
     """Grad primitive: returns (dq, dk, dv), fp32 when ``grads_fp32`` (what the reference primitive
     returns) else in q's dtype (what its bprop hands back after the cast)."""
     lib = load()
@@ -143,7 +144,7 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
     lse = lse.contiguous()
     a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
                             alibi_slopes, prev_block_num, next_block_num, scale, seq_lens,
-                            flags=FLAG_GRAD_F32 if grads_fp32 else 0)
+                            flags=FLAG_GRAD_F32 if grads_fp32 else 0, tri_block=tri_block)
     nbytes = lib.acct_fa_bwd_workspace_bytes(C.byref(a))
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     g = FaBwdIO()

@@ -1,0 +1,348 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload H]
+
+Headline workload "H": FlashAttention2 forward + backward, fp16, causal, B=2 N=32 S=8192 D=128
+(per GPU; with N GPUs every rank runs its own shard of a batch N times as large -- (batch, head)
+slices are independent, so there is no collective in the timed region and scaling is "weak").
+One step = one forward + one backward over the shard.  The metric is algorithmic TFLOP/s
+(forward 4*B*N*S*S*D/2, backward 2.5x that) summed over ranks, from CUDA-event time, max over ranks.
+
+Prints ONE JSON line.  ``--impl reference`` times the CPU restatement of the reference's
+standard-attention path (oracle/attention_ref.py) on a bounded sample instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "fa2_fwd_bwd_causal_s8k_d128_tflops"
+UNIT = "TFLOP/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="H")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode HBM measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    return ap.parse_args()
+
+
+def workload_config(name):
+    from acctransformer_b200.workloads import CONFIGS
+    c = CONFIGS[name]
+    return {"workload": f"{name}: FA2 fwd+bwd {c['dtype']} causal B={c['B']} N={c['N']} S={c['S']} D={c['D']} per GPU",
+            "B": c["B"], "N": c["N"], "S": c["S"], "D": c["D"], "mask": "causal (in-kernel triangle)",
+            "scale": "D^-1/2", "l2": "inputs_exceed_l2 (q,k,v,dO,O = 671 MB per step vs 126 MB L2)",
+            "sharding": "batch x heads, no collective"}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU baseline (the oracle timed on the host cores) -- also the whole of --impl reference
+# ----------------------------------------------------------------------------------------------
+def cpu_sample(name, seed=0):
+    """One (batch, head) unit of the workload at full sequence length."""
+    import numpy as np
+    from acctransformer_b200.workloads import CONFIGS
+    c = CONFIGS[name]
+    rs = np.random.RandomState(seed)
+    q, k, v, do = (rs.randn(1, 1, c["S"], c["D"]).astype(np.float16) for _ in range(4))
+    return c, q, k, v, do
+
+
+def cpu_step(c, q, k, v, do):
+    import numpy as np
+    from oracle import attention_ref as ref
+    scale = 1.0 / np.sqrt(c["D"])
+    t0 = time.perf_counter()
+    o, lse = ref.sa_fwd(q, k, v, causal=True, scale=scale)
+    dq, dk, dv = ref.sa_grad(q, k, v, do, causal=True, scale=scale)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(name, steps=1, warmup=0):
+    from acctransformer_b200.workloads import fwd_bwd_flops
+    c, q, k, v, do = cpu_sample(name)
+    for _ in range(warmup):
+        cpu_step(c, q, k, v, do)
+    times = [cpu_step(c, q, k, v, do) for _ in range(steps)]
+    sec = sum(times) / len(times)
+    flops = fwd_bwd_flops(c, B=1, N=1)
+    return {"value": flops / sec / 1e12, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+            "sample": f"1 of {c['B'] * c['N']} (batch, head) units at full S={c['S']}, fp32 NumPy "
+                      f"standard attention fwd+grad, {sec:.2f} s per unit, mean of {len(times)}"}, sec
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    cb, sec = cpu_baseline(args.workload, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args.workload), "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.rows.append((time.perf_counter(), ln.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        rows = [r for (t, r) in self.rows if t0 <= t <= t1] or [r for (_, r) in self.rows[-3:]]
+        for r in rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"tflops": d.get("bf16_tflops_sustained"), "tflops_burst": d.get("bf16_tflops"),
+                "hbm_gbs": d.get("hbm_gbs"), "which": "measured"}
+    return {"tflops": 1400.0, "tflops_burst": 1590.0, "hbm_gbs": 6650.0, "which": "fallback"}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from acctransformer_b200 import _lib, ops
+    from acctransformer_b200.workloads import CONFIGS, fwd_bwd_flops, fwd_flops, make_inputs
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    cfg = CONFIGS[args.workload]
+    inp = make_inputs(args.workload, dev, seed_offset=rank)
+    q, k, v, do = inp["q"], inp["k"], inp["v"], inp["do"]
+    scale = inp["scale"]
+
+    def fwd():
+        return ops.fa_forward(q, k, v, causal=True, scale=scale)
+
+    def bwd(o, lse):
+        return ops.fa_backward(q, k, v, o, lse, do, causal=True, scale=scale)
+
+    def step():
+        o, lse = fwd()
+        return bwd(o, lse)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1) / iters
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    t0 = time.perf_counter()
+    ms_step = timed(step, args.steps)
+    t1 = time.perf_counter()
+    clocks = sampler.stop(t0, t1) if sampler else None
+    _lib.device_status()
+
+    # per-kernel legs for the roofline (same inputs, same stream)
+    ms_fwd = timed(fwd, args.steps)
+    o, lse = fwd()
+    ms_bwd = timed(lambda: bwd(o, lse), args.steps)
+
+    if world > 1:
+        t = torch.tensor([ms_step, ms_fwd, ms_bwd], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, ms_fwd, ms_bwd = (float(x) for x in t.tolist())
+
+    flops_step = fwd_bwd_flops(cfg)
+    value = world * flops_step / (ms_step * 1e-3) / 1e12
+
+    # end to end through the public call with host buffers: H2D of q,k,v,dO and D2H of O,dQ,dK,dV every step
+    e2e = None
+    if not args.no_e2e:
+        host_in = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, k, v, do)]
+        for h, t in zip(host_in, (q, k, v, do)):
+            h.copy_(t)
+        host_out = [torch.empty(q.shape, dtype=q.dtype).pin_memory() for _ in range(4)]
+        dq_, dk_, dv_, do_ = (torch.empty_like(q) for _ in range(4))
+
+        def e2e_step():
+            for d, h in zip((dq_, dk_, dv_, do_), host_in):
+                d.copy_(h, non_blocking=True)
+            o2, lse2 = ops.fa_forward(dq_, dk_, dv_, causal=True, scale=scale)
+            g = ops.fa_backward(dq_, dk_, dv_, o2, lse2, do_, causal=True, scale=scale)
+            for h, d in zip(host_out, (o2,) + tuple(g)):
+                h.copy_(d, non_blocking=True)
+
+        e2e_iters = max(2, min(args.steps, 5))
+        e2e_step()
+        ms_e2e = timed(e2e_step, e2e_iters)
+        if world > 1:
+            t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_e2e = float(t.item())
+        nbytes = sum(t.numel() * t.element_size() for t in host_in)
+        e2e = {"value": world * flops_step / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": nbytes,
+               "d2h_bytes_per_step": nbytes, "ms_per_step": ms_e2e, "steps": e2e_iters}
+        del host_in, host_out, dq_, dk_, dv_, do_
+
+    peaks = measured_peaks()
+    bwd_tflops = 2.5 * fwd_flops(cfg) / (ms_bwd * 1e-3) / 1e12
+    fwd_tflops = fwd_flops(cfg) / (ms_fwd * 1e-3) / 1e12
+    roofline = {"kernel": "fa_bwd_kernel (timed as the whole acct_fa_bwd call: + row-sum, zero-fill, dQ convert)",
+                "bound": "tensor", "achieved": bwd_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                "frac": bwd_tflops / peaks["tflops"], "peak_source": f"{peaks['which']} bf16_tflops_sustained",
+                "traffic": None, "ms": ms_bwd,
+                "fwd": {"kernel": "fa_fwd_kernel", "achieved": fwd_tflops, "frac": fwd_tflops / peaks["tflops"], "ms": ms_fwd},
+                "step_frac_of_sustained": (flops_step / (ms_step * 1e-3) / 1e12) / peaks["tflops"],
+                "step_frac_of_burst": (flops_step / (ms_step * 1e-3) / 1e12) / peaks["tflops_burst"],
+                "step_frac_of_datasheet_2250": (flops_step / (ms_step * 1e-3) / 1e12) / 2250.0}
+
+    del q, k, v, do, o, lse, inp
+    torch.cuda.empty_cache()
+
+    decode = None
+    if not args.no_decode and rank == 0:
+        decode = bench_decode(torch, ops, dev, peaks)
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp16", "data": "synthetic", "config": workload_config(args.workload),
+            "roofline": roofline, "e2e": e2e, "gpu_launches": 4 * args.steps, "clocks": clocks, "decode": decode}
+    if rank == 0:
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"], _ = cpu_baseline(args.workload)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def bench_decode(torch, ops, dev, peaks):
+    """Decode step of configuration 5b (B=32 N=32 KV<=16384 D=128 fp16, per-sequence lengths): achieved HBM GB/s
+    counting only the valid K and V rows.  Three cache sets (25.8 GB) are rotated so that no step finds its
+    cache in L2."""
+    from acctransformer_b200.workloads import CONFIGS
+    c = CONFIGS["cfg5b"]
+    B, N, S, D = c["B"], c["N"], c["S"], c["D"]
+    g = torch.Generator(device=dev).manual_seed(6)
+    sets = []
+    for _ in range(3):
+        kc = torch.empty(B, N, S, D, device=dev, dtype=torch.float16)
+        vc = torch.empty(B, N, S, D, device=dev, dtype=torch.float16)
+        kc.normal_(generator=g)
+        vc.normal_(generator=g)
+        sets.append((kc, vc))
+    qd = torch.randn(B, N, 1, D, device=dev, dtype=torch.float16, generator=g)
+    gl = torch.Generator(device="cpu").manual_seed(7)
+    lens = torch.randint(c["len_lo"], S + 1, (B,), generator=gl, dtype=torch.int32).to(dev)
+    ws = ops.DecodeWorkspace(B, N, D, dev)
+    y = torch.empty_like(qd)
+    for i in range(6):
+        ops.infer_decode(qd, sets[i % 3][0], sets[i % 3][1], lens, workspace=ws, out=y)
+    iters = 30
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(iters):
+        ops.infer_decode(qd, sets[i % 3][0], sets[i % 3][1], lens, workspace=ws, out=y)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    nbytes = float(lens.sum().item()) * N * D * 2 * 2
+    gbps = nbytes / (ms * 1e-3) / 1e9
+    return {"workload": "cfg5b decode B=32 N=32 q_len=1 KV<=16384 D=128 fp16", "ms": ms, "bytes": nbytes,
+            "achieved_gbs": gbps, "peak_gbs": peaks["hbm_gbs"], "frac": gbps / peaks["hbm_gbs"],
+            "peak_source": f"{peaks['which']} hbm_gbs"}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -114,7 +114,9 @@ typedef struct acct_fa_args {
                                fp16 multiplies by head_dim^-1/4 amount to (nn/layer/flash_attention.py:188-189) */
   const int32_t* seq_lens;  /* device [B] int32 or NULL: valid key count per batch entry */
   uint32_t flags;           /* ACCT_FLAG_* */
-  uint32_t reserved;
+  int32_t tri_block;        /* 0 = off.  > 0: TriangleAttention row groups of this many query rows; a query row in
+                               group g sees keys [0, min(S_k, (g+1)*tri_block)) only -- the keys the reference slices in
+                               for that group (train/acctransformer/triangle_attention/triangle_attention.py:137-163) */
 } acct_fa_args;
 
 /* Extra I/O of the backward.
@@ -123,7 +125,7 @@ typedef struct acct_fa_args {
  *   train/acctransformer/flash_attention/ops/flash_attention/flash_attention_impl.py:59-126
  *   inputs query, key, value, output, do, rowsum, [attn_mask], [dropout_mask], [alibi_mask] -> dq, dk, dv (fp32),
  * which `bprop` then casts to fp16 (:117-124).  dq/dk/dv here are written in `dtype` unless
- * ACCT_FLAG_GRAD_F32 is set.  Gradient strides follow q / k / v strides when packed == 0.
+ * ACCT_FLAG_GRAD_F32 is set; all three are packed [B,N,S,D].
  *   dV = (P*M)^T dO;  dP = (dO V^T)*M;  Dl = rowsum(dO*O);  dS = P*(dP - Dl);
  *   dQ = scale * dS K;  dK = scale * dS^T Q     (flash_attention_bwd.py:88-257, with M = dropout_mask/keep_prob)
  */
