@@ -17,6 +17,8 @@ import torch
 CONFIGS = {
     # headline metric: causal FA2 fwd+bwd at S = 8K, D = 128
     "H": dict(kind="fa", dtype="float16", B=2, N=32, S=8192, D=128, std=1.0, causal=True, seed=0),
+    # the headline kernel at a size small enough for a full ncu capture (tensors still exceed the 126 MB L2)
+    "P": dict(kind="fa", dtype="float16", B=2, N=16, S=4096, D=128, std=1.0, causal=True, seed=9),
     "cfg1": dict(kind="fa", dtype="float16", B=1, N=2, S=256, D=64, std=1.0, mask="triu", seed=1, fwd_only=True),
     "cfg2": dict(kind="fa", dtype="float16", B=4, N=16, S=2048, D=128, std=1.0, causal=True, alibi=True, seed=2),
     "cfg3": dict(kind="fa", dtype="bfloat16", B=2, N=32, S=8192, D=128, std=0.5, prev=4, next=4, keep_prob=0.9,
