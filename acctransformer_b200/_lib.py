@@ -15,6 +15,7 @@ ACCT_F16, ACCT_BF16, ACCT_U8, ACCT_F32 = 0, 1, 2, 3
 MASK_NONE, MASK_FULL, MASK_TILE128 = 0, 1, 2
 BAND_UNBOUNDED = 65536
 FLAG_GRAD_F32, FLAG_DETERMINISTIC = 1, 2
+DECODE_STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
 
 ERR_NAMES = {
     1: "ACCT_ERR_NULL", 2: "ACCT_ERR_SHAPE", 3: "ACCT_ERR_DTYPE", 4: "ACCT_ERR_UNSUPPORTED_D",
@@ -24,7 +25,7 @@ ERR_NAMES = {
 
 EXPORTS = [
     "acct_fa_fwd", "acct_fa_bwd_workspace_bytes", "acct_fa_bwd", "acct_infer_prefill",
-    "acct_infer_decode_workspace_bytes", "acct_infer_decode", "acct_device_status",
+    "acct_infer_decode_workspace_bytes", "acct_infer_decode", "acct_infer_decode_static", "acct_device_status",
     "acct_last_error", "acct_abi_version",
 ]
 
@@ -107,6 +108,8 @@ def load():
     lib.acct_infer_decode_workspace_bytes.restype = C.c_size_t
     lib.acct_infer_decode.argtypes = [C.POINTER(DecodeArgs), C.c_void_p]
     lib.acct_infer_decode.restype = C.c_int
+    lib.acct_infer_decode_static.argtypes = [C.POINTER(DecodeArgs), C.c_void_p]
+    lib.acct_infer_decode_static.restype = C.c_int
     lib.acct_device_status.argtypes = [C.c_void_p]
     lib.acct_device_status.restype = C.c_int
     lib.acct_last_error.argtypes = []

@@ -197,6 +197,19 @@ typedef struct acct_decode_args {
 ACCT_API size_t acct_infer_decode_workspace_bytes(const acct_decode_args* a);
 ACCT_API int acct_infer_decode(const acct_decode_args* a, void* stream);
 
+/* The decode step for callers that cannot allocate device memory (a server whose pool is already carved up,
+ * a plugin inside a framework that forbids allocation while a step is recorded or replayed, a latency-critical
+ * thread that must stay off the allocator's lock).  No counterpart in the reference: it has no decode path and
+ * its runtime hands every op its workspace.
+ * Same arguments and results as acct_infer_decode, except that `workspace` / `workspace_bytes` are ignored: the
+ * partial results go to an array of ACCT_DECODE_STATIC_SCRATCH_BYTES built into the library, which every GPU that
+ * loads the library holds until the process exits.  Returns ACCT_ERR_WORKSPACE if the call needs more than that
+ * (B*N*splits*(D+2)*4 bytes).  All calls on a GPU share the array: calls that overlap on the GPU race, so keep
+ * them ordered on one stream; nothing in the array needs clearing between calls.  The first call on each GPU
+ * resolves the array's device address and should come before any stream capture.  Calls no cudaMalloc/cudaFree. */
+#define ACCT_DECODE_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+ACCT_API int acct_infer_decode_static(const acct_decode_args* a, void* stream);
+
 /* Reads and clears the device-side status word of the current device (synchronises `stream`).
  * Returns ACCT_OK, or ACCT_ERR_DEVICE_TIMEOUT if some kernel gave up on a bounded wait since the last call. */
 ACCT_API int acct_device_status(void* stream);
