@@ -103,11 +103,15 @@ unsigned int* device_status_ptr() {
 
 int make_tmap_4d(CUtensorMap* out, const TensorDesc4& t, int box_rows) {
   cuuint64_t dims[4] = {(cuuint64_t)t.dims[0], (cuuint64_t)t.dims[1], (cuuint64_t)t.dims[2], (cuuint64_t)t.dims[3]};
-  cuuint64_t strides[3] = {(cuuint64_t)t.strides[0] * 2, (cuuint64_t)t.strides[1] * 2, (cuuint64_t)t.strides[2] * 2};
-  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  // rows of the box are 128 bytes: 64 sixteen-bit elements, or 32 fp32 elements (the dQ accumulator)
+  const cuuint64_t esz = t.dtype == ACCT_F32 ? 4 : 2;
+  cuuint64_t strides[3] = {(cuuint64_t)t.strides[0] * esz, (cuuint64_t)t.strides[1] * esz, (cuuint64_t)t.strides[2] * esz};
+  cuuint32_t box[4] = {(cuuint32_t)(128 / esz), (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = g_encode(out, t.dtype == ACCT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                        4, const_cast<void*>(t.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const CUtensorMapDataType dt = t.dtype == ACCT_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : t.dtype == ACCT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = g_encode(out, dt, 4, const_cast<void*>(t.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(ACCT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -243,7 +247,7 @@ int acct_device_status(void* stream) {
   if (host != 0) {
     e = cudaMemsetAsync(st, 0, sizeof(host), s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-    return fail(ACCT_ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded wait (code %u: 1=TMA load, 2=MMA completion, 3=hand-off)", host);
+    return fail(ACCT_ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded wait (code %u: 1=TMA load, 2=MMA completion, 3=hand-off, 4=shared-memory base misaligned)", host);
   }
   return ACCT_OK;
 }
@@ -304,6 +308,11 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   t.dims[0] = a->D; t.dims[1] = a->S_q; t.dims[2] = a->N; t.dims[3] = a->B;
   t.strides[0] = st.o[2]; t.strides[1] = st.o[1]; t.strides[2] = st.o[0];
   if ((rc = make_tmap_4d(&p.map_do, t, kTile))) return rc;
+  // the fp32 dQ accumulator, packed [B,N,S_q,D]: target of the kernel's TMA reduce-add
+  t.dtype = ACCT_F32; t.ptr = dq_acc;
+  t.strides[0] = a->D; t.strides[1] = static_cast<int64_t>(a->S_q) * a->D;
+  t.strides[2] = static_cast<int64_t>(a->N) * a->S_q * a->D;
+  if ((rc = make_tmap_4d(&p.map_dq, t, kTile))) return rc;
 
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, rows * static_cast<size_t>(a->D) * 4, s);
   if (e != cudaSuccess) return fail_cuda(e, "zero-filling the dQ accumulator");

@@ -1,17 +1,20 @@
 // FlashAttention-2 backward for sm_100a.
 //
 // One CTA owns one 128-row K/V tile of one (batch, head) slice and walks the Q tiles that touch
-// it; dK and dV accumulate in tensor memory for the whole walk, dQ tiles are reduced into an fp32
-// global accumulator.  Scores are recomputed TRANSPOSED (rows = keys, columns = queries) so that
-// P^T and dS^T come out in the layout the dV / dK products need:
+// it; dK and dV accumulate in tensor memory for the whole walk, dQ tiles are added into an fp32
+// global accumulator by TMA reduce.  Scores are recomputed TRANSPOSED (rows = keys, columns =
+// queries) so that P^T and dS^T come out in the layout the dV / dK products need:
 //   S^T  = K_j Q_i^T          (tcgen05, both operands K-major from shared memory)
 //   dP^T = V_j dO_i^T
 //   P^T  = exp2(S^T*scale*log2e - L_i*log2e);  dS^T = P^T * (dP^T * M - D_i)        (registers)
-//   dV  += (P^T*M) dO_i       (A from tensor memory, written over S^T; B = dO_i, MN-major)
 //   dK  += dS^T Q_i           (A = dS^T from shared memory, K-major; B = Q_i, MN-major)
 //   dQ_i = dS K_j             (A = the same dS^T tile read MN-major; B = K_j, MN-major) -> over dP^T
-// Warp roles: warps 0-3 compute (thread t owns key row t), warp 4 = TMA producer, warp 5 = MMA
-// issuer.  Tensor memory: S^T/P^T | dP^T/dQ | dK | dV, 128 columns each.
+//   dV  += (P^T*M) dO_i       (A from tensor memory, written over S^T; B = dO_i, MN-major)
+// Warp roles: warps 0-7 compute (thread = one key row x one half of the query columns), warp 8 =
+// TMA producer (K/V once, Q and dO in two-stage rings), warp 9 = MMA issuer.  Tensor memory:
+// S^T/P^T | dP^T/dQ | dK | dV, 128 columns each.  The MMA issuer runs one step ahead: S^T of the
+// next Q tile is issued right behind the products of the current one, so the tensor pipe works
+// while the compute warps drain dQ and form the next P^T.
 //
 // Follows the reference's backward (train/acctransformer/flash_attention/ops/flash_attention/
 // flash_attention_bwd.py:259-415): K/V tile outer, Q tile inner, P recomputed from L, D = rowsum(dO*O)
@@ -28,28 +31,42 @@ namespace acct {
 
 namespace {
 
-constexpr int kBwdThreads = 192;
-constexpr int kQStages = 2;
+constexpr int kBwdThreads = 320;
+constexpr int kComputeThreads = 256;
+constexpr int kStages = 2;
 
 struct BwdShared {
   uint64_t kv_full;
-  uint64_t q_full[kQStages];
-  uint64_t do_full;
-  uint64_t st_full, dp_full;
-  uint64_t pds_ready;     // compute -> MMA: P^T in tensor memory, dS^T in shared memory
-  uint64_t tail_done;     // MMA -> everyone: dV, dK, dQ products of this Q tile finished
-  uint64_t dq_read;       // compute -> MMA: dQ has been drained, dP^T columns are free again
-  uint64_t stats_ready;   // compute -> compute: lse2 / delta of this Q tile are in shared memory
+  uint64_t q_full[kStages], do_full[kStages];
+  uint64_t qdo_empty[kStages];   // MMA -> producer: every product reading this Q / dO stage has finished
+  uint64_t st_full, dp_full;     // MMA -> compute
+  uint64_t pds_ready;            // compute -> MMA: P^T in tensor memory, dS^T in shared memory
+  uint64_t ds_done;              // MMA -> compute: dK and dQ products finished (dS^T free, dQ in tensor memory)
+  uint64_t dq_read;              // compute -> MMA: dQ drained, the dP^T columns are free again
+  uint64_t stats_ready;          // compute -> compute: lse2 / delta of this Q tile are in shared memory
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
-  float lse2[2][kTile];   // L * log2(e) per query of the tile (+inf for rows past S_q)
+  float lse2[2][kTile];          // L * log2(e) per query of the tile (+inf for rows past S_q)
   float delta[2][kTile];
-  int tri_end[2][kTile];  // first key index that does not exist for each query of the tile
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
+// P = exp2(s*scale + bias - L) for 32 consecutive queries of one key row; `bias` is -inf for key rows
+// that do not exist, L is +inf for query rows that do not exist: both give exactly 0.
+template <bool DIAG>
+__device__ __forceinline__ void p_fast(const uint32_t (&s)[32], const float* lse2c, float scale_log2, float bias,
+                                       int kv_idx, int q0, float (&pr)[32]) {
+#pragma unroll
+  for (int e4 = 0; e4 < 8; ++e4) {
+    const float4 L = *reinterpret_cast<const float4*>(lse2c + 4 * e4);
+    const float l[4] = {L.x, L.y, L.z, L.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = 4 * e4 + u;
+      float v = ex2(fmaf(__uint_as_float(s[e]), scale_log2, bias) - l[u]);
+      if (DIAG) v = (kv_idx > q0 + e) ? 0.f : v;
+      pr[e] = v;
+    }
+  }
 }
 
 }  // namespace
@@ -58,17 +75,17 @@ template <int DPAD, bool BF16>
 __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_constant__ BwdParams p) {
   constexpr int NB = DPAD / 64;
   constexpr uint32_t kTileBytes = NB * 16384u;   // 128 rows x DPAD 16-bit elements
-  constexpr uint32_t kDsBytes = 32768u;          // dS^T: 128 key rows x 128 query columns
   constexpr uint32_t kColST = 0, kColDP = 128, kColDK = 256, kColDV = 384;
+  constexpr int kDrainRounds = DPAD / 64;        // 32-column dQ chunks per half of the compute warps
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // All shared memory is dynamic so that the tiles start at the (1024-byte aligned) base of the CTA's window.
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
   uint8_t* sV = sK + kTileBytes;
-  uint8_t* sQ = sV + kTileBytes;                 // kQStages tiles
-  uint8_t* sDO = sQ + kQStages * kTileBytes;
-  uint8_t* sDS = sDO + kTileBytes;
-  __shared__ BwdShared sh;
+  uint8_t* sQ = sV + kTileBytes;                   // kStages tiles
+  uint8_t* sDO = sQ + kStages * kTileBytes;        // kStages tiles
+  uint8_t* sDS = sDO + kStages * kTileBytes;       // dS^T: 2 blocks of 128 key rows x 64 queries; also dQ staging
+  BwdShared& sh = *reinterpret_cast<BwdShared*>(sDS + 32768);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -77,6 +94,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   const int b = bh / p.N, h = bh % p.N;
   const int j = blockIdx.x;                      // K/V tile
   const ScoreMods& mods = p.mods;
+
+  if ((smem_u32(smem) & 1023u) != 0u) {          // the swizzled tiles need a 1024-byte aligned base
+    if (tid == 0) atomicMax(p.status, DEV_BAD_SMEM_BASE);
+    return;
+  }
 
   int kv_len = p.S_k;
   if (mods.seq_lens != nullptr) kv_len = min(p.S_k, max(0, mods.seq_lens[b]));
@@ -92,25 +114,26 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
 
   if (tid == 0) {
     mbar_init(&sh.kv_full, 1);
-    for (int s = 0; s < kQStages; ++s) mbar_init(&sh.q_full[s], 1);
-    mbar_init(&sh.do_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sh.q_full[s], 1); mbar_init(&sh.do_full[s], 1); mbar_init(&sh.qdo_empty[s], 1);
+    }
     mbar_init(&sh.st_full, 1);
     mbar_init(&sh.dp_full, 1);
-    mbar_init(&sh.pds_ready, 128);
-    mbar_init(&sh.tail_done, 1);
-    mbar_init(&sh.dq_read, 128);
-    mbar_init(&sh.stats_ready, 128);
+    mbar_init(&sh.pds_ready, kComputeThreads);
+    mbar_init(&sh.ds_done, 1);
+    mbar_init(&sh.dq_read, kComputeThreads);
+    mbar_init(&sh.stats_ready, kTile);
     sh.abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 4) { tmem_alloc(&sh.tmem_base, 512); tmem_relinquish(); }
+  if (warp == 8) { tmem_alloc(&sh.tmem_base, 512); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = sh.tmem_base;
   volatile uint32_t* abort_flag = &sh.abort_flag;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_iter > 0) {
       prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_do);
@@ -119,21 +142,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       for (int nb = 0; nb < NB; ++nb) tma_load_4d(sV + nb * 16384, &p.map_v, &sh.kv_full, nb * 64, j * kTile, h, b);
       for (int n = 0; n < n_iter; ++n) {
         const int i = i_lo + n;
-        const int st = n % kQStages;
-        // Q stage st was last read by the products of iteration n-2, whose completion this thread
-        // already observed before loading dO in iteration n-1; dO is read by those of iteration n-1.
+        const int st = n % kStages;
+        if (n >= kStages) mbar_wait(&sh.qdo_empty[st], ((n / kStages) - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         mbar_expect_tx(&sh.q_full[st], kTileBytes);
         for (int nb = 0; nb < NB; ++nb)
           tma_load_4d(sQ + st * kTileBytes + nb * 16384, &p.map_q, &sh.q_full[st], nb * 64, i * kTile, h, b);
-        if (n >= 1 && !mbar_wait(&sh.tail_done, (n - 1) & 1, abort_flag)) {
-          *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break;
-        }
-        mbar_expect_tx(&sh.do_full, kTileBytes);
+        mbar_expect_tx(&sh.do_full[st], kTileBytes);
         for (int nb = 0; nb < NB; ++nb)
-          tma_load_4d(sDO + nb * 16384, &p.map_do, &sh.do_full, nb * 64, i * kTile, h, b);
+          tma_load_4d(sDO + st * kTileBytes + nb * 16384, &p.map_do, &sh.do_full[st], nb * 64, i * kTile, h, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_iter > 0) {
       const uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);     // S^T, dP^T
@@ -141,30 +160,29 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       const uint32_t idesc_dq = make_idesc(BF16, 128, DPAD, true, true);     // dQ
       const uint64_t kmajor = make_sdesc_base(16, 1024);
       const uint64_t mnmajor = make_sdesc_base(16384, 1024);
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
-      bool ok = mbar_wait(&sh.kv_full, 0, abort_flag);
-      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); }
-      for (int n = 0; ok && n < n_iter; ++n) {
-        const int st = n % kQStages;
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
+
+      auto issue_st = [&](int st) {   // S^T = K Q^T
         const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
-        // S^T = K Q^T (its tensor-memory columns were last read by the dV product of iteration n-1,
-        // which the tensor pipe finishes first)
-        ok = mbar_wait(&sh.q_full[st], (n / kQStages) & 1, abort_flag);
-        if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); break; }
-        tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < DPAD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
           umma_ss(tmem + kColST, sdesc_at(kmajor, aK + off), sdesc_at(kmajor, aQ + off), idesc_s, kk > 0);
         }
         umma_commit(&sh.st_full);
+      };
+
+      mbar_wait(&sh.kv_full, 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
+      mbar_wait(&sh.q_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
+      tc_fence_after_sync();
+      issue_st(0);
+      for (int n = 0; n < n_iter; ++n) {
+        const int st = n % kStages;
+        const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
+        const uint32_t aDO = smem_u32(sDO + st * kTileBytes);
         // dP^T = V dO^T, once the previous dQ has been drained from those columns
-        ok = mbar_wait(&sh.do_full, n & 1, abort_flag);
-        if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); break; }
-        if (n > 0) {
-          ok = mbar_wait(&sh.dq_read, (n - 1) & 1, abort_flag);
-          if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break; }
-        }
+        mbar_wait(&sh.do_full[st], (n / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+        if (n > 0) mbar_wait(&sh.dq_read, (n - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < DPAD / 16; ++kk) {
@@ -172,13 +190,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
           umma_ss(tmem + kColDP, sdesc_at(kmajor, aV + off), sdesc_at(kmajor, aDO + off), idesc_s, kk > 0);
         }
         umma_commit(&sh.dp_full);
-        // the three products that consume P^T and dS^T
-        ok = mbar_wait(&sh.pds_ready, n & 1, abort_flag);
-        if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break; }
+        // the products that consume dS^T first, so that the compute warps can start draining dQ early
+        mbar_wait(&sh.pds_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)   // dV += P^T dO
-          umma_ts(tmem + kColDV, tmem + kColST + kk * 8, sdesc_at(mnmajor, aDO + kk * 2048u), idesc_kv, n > 0 || kk > 0);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)   // dK += dS^T Q
           umma_ss(tmem + kColDK, sdesc_at(kmajor, aDS + (kk >> 2) * 16384u + (kk & 3) * 32u),
@@ -186,168 +200,258 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)   // dQ = dS K
           umma_ss(tmem + kColDP, sdesc_at(mnmajor, aDS + kk * 2048u), sdesc_at(mnmajor, aK + kk * 2048u), idesc_dq, kk > 0);
-        umma_commit(&sh.tail_done);
+        umma_commit(&sh.ds_done);
+        // dV += P^T dO; P^T of query columns [64h, 64h+64) sits in S^T columns [64h, 64h+32)
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ts(tmem + kColDV, tmem + kColST + (kk >> 2) * 64 + (kk & 3) * 8, sdesc_at(mnmajor, aDO + kk * 2048u),
+                  idesc_kv, n > 0 || kk > 0);
+        umma_commit(&sh.qdo_empty[st]);
+        // S^T of the next Q tile right behind (the tensor pipe runs in order, so P^T has been consumed)
+        if (n + 1 < n_iter) {
+          mbar_wait(&sh.q_full[(n + 1) % kStages], ((n + 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+          tc_fence_after_sync();
+          issue_st((n + 1) % kStages);
+        }
       }
     }
   } else {
     // ------------------------------------------------------------------ compute warps
-    const int r = tid;                                   // key row inside the tile (and dQ row when draining)
+    const int hf = warp >> 2;                            // which half of the query columns / of head_dim
+    const int r = (warp & 3) * 32 + lane;                // key row inside the tile (and dQ row when draining)
     const int kv_idx = j * kTile + r;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_st = tmem + lane_base + kColST;
     const uint32_t t_dp = tmem + lane_base + kColDP;
     const bool kv_ok = kv_idx < kv_len;
-    float alibi_l2 = 0.f;
+    const bool elected = (tid == hf * 128);
+    uint8_t* my_ds = sDS + hf * 16384u;                  // this half's dS^T block, reused as its dQ staging
+    float bias = kNegInf;                                // alibi term in log2 units; -inf removes the key row
     if (kv_ok) {
-      if (mods.alibi != nullptr) alibi_l2 = load16<BF16>(mods.alibi, static_cast<int64_t>(bh) * p.S_k + kv_idx) * kLog2e;
-      else if (mods.alibi_slopes != nullptr) alibi_l2 = mods.alibi_slopes[h] * static_cast<float>(kv_idx) * kLog2e;
+      bias = 0.f;
+      if (mods.alibi != nullptr) bias = load16<BF16>(mods.alibi, static_cast<int64_t>(bh) * p.S_k + kv_idx) * kLog2e;
+      else if (mods.alibi_slopes != nullptr) bias = mods.alibi_slopes[h] * static_cast<float>(kv_idx) * kLog2e;
     }
-    bool ok = true;
+
+    // statistics of the first Q tile
+    float nxt_lse = 0.f, nxt_dlt = 0.f;
+    if (hf == 0 && n_iter > 0) {
+      const int q_row = i_lo * kTile + r;
+      const bool q_ok = q_row < p.S_q;
+      const int64_t idx = static_cast<int64_t>(bh) * p.S_q + q_row;
+      sh.lse2[0][r] = q_ok ? p.lse[idx] * kLog2e : INFINITY;
+      sh.delta[0][r] = q_ok ? p.delta[idx] : 0.f;
+      mbar_arrive(&sh.stats_ready);
+    }
+
     for (int n = 0; n < n_iter; ++n) {
       const int i = i_lo + n;
       const int q_base = i * kTile;
-      {
-        const int q_row = q_base + r;
+      // fetch the next tile's statistics now, park them in shared memory after this tile's math
+      if (hf == 0 && n + 1 < n_iter) {
+        const int q_row = q_base + kTile + r;
         const bool q_ok = q_row < p.S_q;
         const int64_t idx = static_cast<int64_t>(bh) * p.S_q + q_row;
-        sh.lse2[n & 1][r] = q_ok ? p.lse[idx] * kLog2e : INFINITY;
-        sh.delta[n & 1][r] = q_ok ? p.delta[idx] : 0.f;
-        sh.tri_end[n & 1][r] = mods.tri_block > 0 ? (min(q_row, p.S_q - 1) / mods.tri_block + 1) * mods.tri_block : 0x7fffffff;
+        nxt_lse = q_ok ? p.lse[idx] * kLog2e : INFINITY;
+        nxt_dlt = q_ok ? p.delta[idx] : 0.f;
       }
-      // an mbarrier rather than a named barrier, so that this hand-off is bounded like every other wait
-      mbar_arrive(&sh.stats_ready);
-      ok = mbar_wait(&sh.stats_ready, n & 1, abort_flag);
-      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break; }
+      mbar_wait(&sh.stats_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
       const float* lse2 = sh.lse2[n & 1];
       const float* dlt = sh.delta[n & 1];
-      const int* tri_end = sh.tri_end[n & 1];
-      ok = mbar_wait(&sh.st_full, n & 1, abort_flag);
-      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); break; }
-      ok = mbar_wait(&sh.dp_full, n & 1, abort_flag);
-      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); break; }
-      tc_fence_after_sync();
       const bool use_mask = (mods.mask_kind == 1) || (mods.mask_kind == 2 && i == j);
       const bool diag = mods.causal && (q_base < j * kTile + kTile - 1);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(t_st + c * 32, s);
-        tmem_ld32(t_dp + c * 32, dp);
-        tmem_wait_ld();
-        uint32_t pk[16], dk_[16];
-        float pd_prev = 0.f, ds_prev = 0.f;
+      const bool generic = use_mask || mods.drop != nullptr || mods.tri_block > 0;
+
+      mbar_wait(&sh.st_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      tc_fence_after_sync();
+      float pr[2][32];
+      if (!generic) {
+        // ---- P part: needs S^T only, runs while the tensor pipe still works on dP^T
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int q_row = q_base + c * 32 + e;
-          float x = fmaf(__uint_as_float(s[e]), p.scale_log2, alibi_l2);
-          if (use_mask && kv_ok && q_row < p.S_q) {
-            const float mv = mods.mask_kind == 1
-                                 ? load_mask_value(mods.mask, mods.mask_dtype,
-                                                   (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q + q_row) * p.S_k + kv_idx)
-                                 : load_mask_value(mods.mask, mods.mask_dtype, static_cast<int64_t>(c * 32 + e) * kTile + r);
-            x += mv * (-10000.0f * kLog2e);
-          }
-          float pr = ex2(x - lse2[c * 32 + e]);
-          if (!kv_ok || (diag && kv_idx > q_row) || kv_idx >= tri_end[c * 32 + e]) pr = 0.f;
-          float fac = 1.0f;
-          if (mods.drop != nullptr) {
-            fac = 0.f;
-            if (kv_ok && q_row < p.S_q)
-              fac = load_mask_value(mods.drop, mods.drop_dtype,
-                                    (static_cast<int64_t>(bh) * p.S_q + q_row) * p.S_k + kv_idx) * mods.drop_scale;
-          }
-          const float pd = pr * fac;
-          const float ds = pr * (__uint_as_float(dp[e]) * fac - dlt[c * 32 + e]);
-          if (e & 1) {
-            pk[e >> 1] = pack2<BF16>(pd_prev, pd);
-            dk_[e >> 1] = pack2<BF16>(ds_prev, ds);
-          } else {
-            pd_prev = pd;
-            ds_prev = ds;
-          }
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = hf * 2 + cc;
+          uint32_t s[32];
+          tmem_ld32(t_st + c * 32, s);
+          tmem_wait_ld();
+          if (diag) p_fast<true>(s, lse2 + c * 32, p.scale_log2, bias, kv_idx, q_base + c * 32, pr[cc]);
+          else p_fast<false>(s, lse2 + c * 32, p.scale_log2, bias, kv_idx, q_base + c * 32, pr[cc]);
         }
-        tmem_st16(t_st + c * 16, pk);
-        // dS^T row r, query columns [32c, 32c+32) -> 64 bytes = four 16-byte chunks of block c/2
-        uint8_t* blk = sDS + (c >> 1) * 16384u;
+        // P^T goes over the first 32 of this half's own 64 S^T columns, which it has finished reading
 #pragma unroll
-        for (int g = 0; g < 4; ++g)
-          *reinterpret_cast<uint4*>(blk + swz128(r, (c & 1) * 4 + g)) =
-              make_uint4(dk_[4 * g], dk_[4 * g + 1], dk_[4 * g + 2], dk_[4 * g + 3]);
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = pack2<BF16>(pr[cc][2 * e], pr[cc][2 * e + 1]);
+          tmem_st16(t_st + hf * 64 + cc * 16, pk);
+        }
+      }
+      mbar_wait(&sh.dp_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      tc_fence_after_sync();
+      // the dQ staging of the previous Q tile must have left this half's dS^T block
+      if (n > 0) {
+        if (elected) tma_store_wait_read();
+        named_barrier(1 + hf, 128);
+      }
+      if (!generic) {
+        // ---- dS part
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = hf * 2 + cc;
+          uint32_t dp[32];
+          tmem_ld32(t_dp + c * 32, dp);
+          tmem_wait_ld();
+          uint32_t dk_[16];
+#pragma unroll
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float4 Dl = *reinterpret_cast<const float4*>(dlt + c * 32 + 4 * e4);
+            const float d0 = pr[cc][4 * e4 + 0] * (__uint_as_float(dp[4 * e4 + 0]) - Dl.x);
+            const float d1 = pr[cc][4 * e4 + 1] * (__uint_as_float(dp[4 * e4 + 1]) - Dl.y);
+            const float d2 = pr[cc][4 * e4 + 2] * (__uint_as_float(dp[4 * e4 + 2]) - Dl.z);
+            const float d3 = pr[cc][4 * e4 + 3] * (__uint_as_float(dp[4 * e4 + 3]) - Dl.w);
+            dk_[2 * e4] = pack2<BF16>(d0, d1);
+            dk_[2 * e4 + 1] = pack2<BF16>(d2, d3);
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(my_ds + swz128(r, cc * 4 + g)) =
+                make_uint4(dk_[4 * g], dk_[4 * g + 1], dk_[4 * g + 2], dk_[4 * g + 3]);
+        }
+      } else {
+        // ---- general path: mask tensor, dropout mask, triangle row groups (per-element loads and branches)
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = hf * 2 + cc;
+          uint32_t s[32], dp[32];
+          tmem_ld32(t_st + c * 32, s);
+          tmem_ld32(t_dp + c * 32, dp);
+          tmem_wait_ld();
+          uint32_t pk[16], dk_[16];
+          float pd_prev = 0.f, ds_prev = 0.f;
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int q_row = q_base + c * 32 + e;
+            float x = fmaf(__uint_as_float(s[e]), p.scale_log2, bias);
+            if (use_mask && kv_ok && q_row < p.S_q) {
+              const float mv = mods.mask_kind == 1
+                                   ? load_mask_value(mods.mask, mods.mask_dtype,
+                                                     (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q + q_row) * p.S_k + kv_idx)
+                                   : load_mask_value(mods.mask, mods.mask_dtype, static_cast<int64_t>(c * 32 + e) * kTile + r);
+              x += mv * (-10000.0f * kLog2e);
+            }
+            float pv = ex2(x - lse2[c * 32 + e]);
+            if (diag && kv_idx > q_row) pv = 0.f;
+            if (mods.tri_block > 0 && kv_idx >= (min(q_row, p.S_q - 1) / mods.tri_block + 1) * mods.tri_block) pv = 0.f;
+            float fac = 1.0f;
+            if (mods.drop != nullptr) {
+              fac = 0.f;
+              if (kv_ok && q_row < p.S_q)
+                fac = load_mask_value(mods.drop, mods.drop_dtype,
+                                      (static_cast<int64_t>(bh) * p.S_q + q_row) * p.S_k + kv_idx) * mods.drop_scale;
+            }
+            const float pd = pv * fac;
+            const float ds = pv * (__uint_as_float(dp[e]) * fac - dlt[c * 32 + e]);
+            if (e & 1) {
+              pk[e >> 1] = pack2<BF16>(pd_prev, pd);
+              dk_[e >> 1] = pack2<BF16>(ds_prev, ds);
+            } else {
+              pd_prev = pd;
+              ds_prev = ds;
+            }
+          }
+          // lands inside this half's first S^T chunk, which it loaded at cc = 0
+          tmem_st16(t_st + hf * 64 + cc * 16, pk);
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(my_ds + swz128(r, cc * 4 + g)) =
+                make_uint4(dk_[4 * g], dk_[4 * g + 1], dk_[4 * g + 2], dk_[4 * g + 3]);
+        }
       }
       tmem_wait_st();
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&sh.pds_ready);
 
-      // drain dQ_i (thread t now owns query row t of the tile) into the fp32 accumulator
-      ok = mbar_wait(&sh.tail_done, n & 1, abort_flag);
-      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); break; }
-      tc_fence_after_sync();
-      {
-        const int q_row = q_base + r;
-        float* dst = p.dq_acc + (static_cast<int64_t>(bh) * p.S_q + q_row) * p.D;
-#pragma unroll 1
-        for (int c = 0; c < DPAD / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(t_dp + c * 32, v);
-          tmem_wait_ld();
-          if (q_row < p.S_q) {
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              const int col = c * 32 + g * 4;
-              if (col + 4 <= p.D)
-                red_add_v4(dst + col, __uint_as_float(v[4 * g]) * p.scale, __uint_as_float(v[4 * g + 1]) * p.scale,
-                           __uint_as_float(v[4 * g + 2]) * p.scale, __uint_as_float(v[4 * g + 3]) * p.scale);
-            }
-          }
-        }
+      // park the next tile's statistics
+      if (hf == 0 && n + 1 < n_iter) {
+        sh.lse2[(n + 1) & 1][r] = nxt_lse;
+        sh.delta[(n + 1) & 1][r] = nxt_dlt;
+        mbar_arrive(&sh.stats_ready);
       }
+
+      // ---- drain dQ_i: tensor memory -> registers -> swizzled staging (this half's dS^T block) -> TMA reduce
+      mbar_wait(&sh.ds_done, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      tc_fence_after_sync();
+      uint32_t dq[kDrainRounds][32];
+#pragma unroll
+      for (int rd = 0; rd < kDrainRounds; ++rd) tmem_ld32(t_dp + (hf * kDrainRounds + rd) * 32, dq[rd]);
+      tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(&sh.dq_read);
+#pragma unroll
+      for (int rd = 0; rd < kDrainRounds; ++rd) {
+        const int c = hf * kDrainRounds + rd;            // 32-column chunk of head_dim
+        if (rd > 0) {
+          if (elected) tma_store_wait_read();
+          named_barrier(1 + hf, 128);
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<float4*>(my_ds + swz128(r, g)) =
+              make_float4(__uint_as_float(dq[rd][4 * g]) * p.scale, __uint_as_float(dq[rd][4 * g + 1]) * p.scale,
+                          __uint_as_float(dq[rd][4 * g + 2]) * p.scale, __uint_as_float(dq[rd][4 * g + 3]) * p.scale);
+        fence_proxy_async_smem();
+        named_barrier(1 + hf, 128);
+        if (elected && c * 32 < p.D) {
+          tma_reduce_add_4d(&p.map_dq, my_ds, c * 32, q_base, h, b);
+          tma_store_commit();
+        }
+      }
     }
+    if (elected) tma_store_wait_all();
 
-    // epilogue: dK (scaled) and dV rows of this tile
+    // epilogue: dK (scaled) and dV rows of this tile; each half writes its half of head_dim
     // (the tensor-memory loads are warp-collective: every lane runs them, only the stores are guarded)
-    if (ok) {
-      tc_fence_after_sync();
-      const bool row_ok = kv_idx < p.S_k;
-      const int64_t row_off = (static_cast<int64_t>(bh) * p.S_k + kv_idx) * p.D;
+    if (n_iter > 0)
+      mbar_wait(&sh.qdo_empty[(n_iter - 1) % kStages], ((n_iter - 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+    tc_fence_after_sync();
+    const bool row_ok = kv_idx < p.S_k;
+    const int64_t row_off = (static_cast<int64_t>(bh) * p.S_k + kv_idx) * p.D;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t t_src = tmem + lane_base + (which == 0 ? kColDK : kColDV);
-        const float mul = which == 0 ? p.scale : 1.0f;
-        void* out = which == 0 ? p.dk : p.dv;
+    for (int which = 0; which < 2; ++which) {
+      const uint32_t t_src = tmem + lane_base + (which == 0 ? kColDK : kColDV);
+      const float mul = which == 0 ? p.scale : 1.0f;
+      void* out = which == 0 ? p.dk : p.dv;
 #pragma unroll 1
-        for (int c = 0; c < DPAD / 32; ++c) {
-          uint32_t v[32];
-          if (n_iter > 0) { tmem_ld32(t_src + c * 32, v); tmem_wait_ld(); }
-          else {
+      for (int cq = 0; cq < kDrainRounds; ++cq) {
+        const int c = hf * kDrainRounds + cq;
+        uint32_t v[32];
+        if (n_iter > 0) { tmem_ld32(t_src + c * 32, v); tmem_wait_ld(); }
+        else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = 0u;
+          for (int e = 0; e < 32; ++e) v[e] = 0u;
+        }
+        if (!row_ok) continue;
+        if (p.grads_f32) {
+          float* dst = reinterpret_cast<float*>(out) + row_off;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int col = c * 32 + g * 4;
+            if (col + 4 <= p.D)
+              *reinterpret_cast<float4*>(dst + col) =
+                  make_float4(__uint_as_float(v[4 * g]) * mul, __uint_as_float(v[4 * g + 1]) * mul,
+                              __uint_as_float(v[4 * g + 2]) * mul, __uint_as_float(v[4 * g + 3]) * mul);
           }
-          if (!row_ok) continue;
-          if (p.grads_f32) {
-            float* dst = reinterpret_cast<float*>(out) + row_off;
+        } else {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(out) + row_off * 2;
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              const int col = c * 32 + g * 4;
-              if (col + 4 <= p.D)
-                *reinterpret_cast<float4*>(dst + col) =
-                    make_float4(__uint_as_float(v[4 * g]) * mul, __uint_as_float(v[4 * g + 1]) * mul,
-                                __uint_as_float(v[4 * g + 2]) * mul, __uint_as_float(v[4 * g + 3]) * mul);
-            }
-          } else {
-            uint8_t* dst = reinterpret_cast<uint8_t*>(out) + row_off * 2;
+          for (int g = 0; g < 4; ++g) {
+            const int col = c * 32 + g * 8;
+            if (col + 8 <= p.D) {
+              uint32_t w[4];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int col = c * 32 + g * 8;
-              if (col + 8 <= p.D) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  w[e] = pack2<BF16>(__uint_as_float(v[8 * g + 2 * e]) * mul, __uint_as_float(v[8 * g + 2 * e + 1]) * mul);
-                *reinterpret_cast<uint4*>(dst + col * 2) = make_uint4(w[0], w[1], w[2], w[3]);
-              }
+              for (int e = 0; e < 4; ++e)
+                w[e] = pack2<BF16>(__uint_as_float(v[8 * g + 2 * e]) * mul, __uint_as_float(v[8 * g + 2 * e + 1]) * mul);
+              *reinterpret_cast<uint4*>(dst + col * 2) = make_uint4(w[0], w[1], w[2], w[3]);
             }
           }
         }
@@ -357,7 +461,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   }
 
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);
   }
@@ -413,7 +517,7 @@ __global__ void bwd_convert_kernel(const float* __restrict__ src, void* __restri
 
 cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : 128;
-  const size_t smem = static_cast<size_t>(3 + kQStages) * (dpad / 64) * 16384 + 32768 + 1024;
+  const size_t smem = static_cast<size_t>(2 + 2 * kStages) * (dpad / 64) * 16384 + 32768 + sizeof(BwdShared);
   dim3 grid((p.S_k + kTile - 1) / kTile, p.B * p.N);
   void (*kern)(const BwdParams) = nullptr;
   if (dpad == 64) kern = bf16 ? fa_bwd_kernel<64, true> : fa_bwd_kernel<64, false>;

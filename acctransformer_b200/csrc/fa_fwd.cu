@@ -130,15 +130,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       for (int j = cta_lo; j <= cta_hi; ++j, ++it) {
         const int st = it % kStages;
         const uint32_t reuse_parity = ((it / kStages) - 1) & 1;
-        if (it >= kStages && !mbar_wait(&sh.k_empty[st], reuse_parity, abort_flag)) {
-          *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break;
-        }
+        if (it >= kStages) mbar_wait(&sh.k_empty[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         mbar_expect_tx(&sh.k_full[st], kTileBytes);
         for (int nb = 0; nb < NB; ++nb)
           tma_load_4d(sK + st * kTileBytes + nb * 16384, &p.map_k, &sh.k_full[st], nb * 64, j * kTile, h, b);
-        if (it >= kStages && !mbar_wait(&sh.v_empty[st], reuse_parity, abort_flag)) {
-          *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break;
-        }
+        if (it >= kStages) mbar_wait(&sh.v_empty[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         mbar_expect_tx(&sh.v_full[st], kTileBytes);
         for (int nb = 0; nb < NB; ++nb)
           tma_load_4d(sV + st * kTileBytes + nb * 16384, &p.map_v, &sh.v_full[st], nb * 64, j * kTile, h, b);
@@ -153,8 +149,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       const uint64_t mnmajor = make_sdesc_base(16384, 1024);
       const TileRange rng[2] = {r0, r1};
       int n_done[2] = {0, 0};   // P tiles consumed so far per Q tile
-      bool ok = mbar_wait(&sh.q_full, 0, abort_flag);
-      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); }
+      mbar_wait(&sh.q_full, 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
 
       auto issue_s = [&](int qt, int st) {
         const uint32_t a0 = smem_u32(sQ + qt * kTileBytes);
@@ -167,29 +162,22 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         umma_commit(&sh.s_full[qt]);
       };
 
-      if (ok) {
-        // prologue: scores of the first K/V tile
-        ok = mbar_wait(&sh.k_full[0], 0, abort_flag);
-        if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); }
-        if (ok) {
-          tc_fence_after_sync();
-          for (int qt = 0; qt < 2; ++qt)
-            if (cta_lo >= rng[qt].lo && cta_lo <= rng[qt].hi) issue_s(qt, 0);
-          umma_commit(&sh.k_empty[0]);
-        }
-      }
+      // prologue: scores of the first K/V tile
+      mbar_wait(&sh.k_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
+      tc_fence_after_sync();
+      for (int qt = 0; qt < 2; ++qt)
+        if (cta_lo >= rng[qt].lo && cta_lo <= rng[qt].hi) issue_s(qt, 0);
+      umma_commit(&sh.k_empty[0]);
       int it = 0;
-      for (int j = cta_lo; ok && j <= cta_hi; ++j, ++it) {
+      for (int j = cta_lo; j <= cta_hi; ++j, ++it) {
         const int st = it % kStages;
         const int stn = (it + 1) % kStages;
         const uint32_t full_parity = (it / kStages) & 1;
         const uint32_t full_parity_n = ((it + 1) / kStages) & 1;
-        for (int qt = 0; ok && qt < 2; ++qt) {
+        for (int qt = 0; qt < 2; ++qt) {
           if (j >= rng[qt].lo && j <= rng[qt].hi) {
-            ok = mbar_wait(&sh.p_ready[qt], n_done[qt] & 1, abort_flag);
-            if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_SYNC); break; }
-            ok = mbar_wait(&sh.v_full[st], full_parity, abort_flag);
-            if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); break; }
+            mbar_wait(&sh.p_ready[qt], n_done[qt] & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+            mbar_wait(&sh.v_full[st], full_parity, abort_flag, p.status, DEV_TIMEOUT_TMA);
             tc_fence_after_sync();
             const uint32_t v0 = smem_u32(sV + st * kTileBytes);
 #pragma unroll
@@ -200,13 +188,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
             ++n_done[qt];
           }
           if (j + 1 <= cta_hi && j + 1 >= rng[qt].lo && j + 1 <= rng[qt].hi) {
-            ok = mbar_wait(&sh.k_full[stn], full_parity_n, abort_flag);
-            if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_TMA); break; }
+            mbar_wait(&sh.k_full[stn], full_parity_n, abort_flag, p.status, DEV_TIMEOUT_TMA);
             tc_fence_after_sync();
             issue_s(qt, stn);
           }
         }
-        if (!ok) break;
         umma_commit(&sh.v_empty[st]);
         if (j + 1 <= cta_hi) umma_commit(&sh.k_empty[stn]);
       }
@@ -234,10 +220,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
 
     float m_run = kNegInf, l_run = 0.f;
     int n = 0;
-    bool ok = true;
     for (int j = rng.lo; j <= rng.hi; ++j, ++n) {
-      ok = mbar_wait(&sh.s_full[qt], n & 1, abort_flag);
-      if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); break; }
+      mbar_wait(&sh.s_full[qt], n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
       const int col_base = j * kTile;
       const bool diag = mods.causal && (col_base + kTile - 1 > q_tile * kTile);
@@ -342,13 +326,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
     }
 
     // epilogue: O / l and L = m + ln l
-    if (ok && q_tile * kTile < p.S_q) {
+    if (q_tile * kTile < p.S_q) {
       if (n > 0) {
-        ok = mbar_wait(&sh.o_done[qt], (n - 1) & 1, abort_flag);
-        if (!ok) { *abort_flag = 1; atomicMax(p.status, DEV_TIMEOUT_MMA); }
+        mbar_wait(&sh.o_done[qt], (n - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
         tc_fence_after_sync();
       }
-      if (ok) {
+      {
         const float inv_l = (n > 0 && l_run > 0.f) ? 1.0f / l_run : 0.f;
         const bool row_ok = q_row < p.S_q;
         uint8_t* o_row = reinterpret_cast<uint8_t*>(p.o) +

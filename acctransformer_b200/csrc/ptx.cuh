@@ -2,9 +2,9 @@
 // (cp.async.bulk.tensor), tensor memory (tcgen05.alloc/ld/st) and the 5th-generation
 // tensor-core MMA (tcgen05.mma, kind::f16) with its shared-memory / instruction descriptors.
 //
-// Every wait in here is bounded: a wait that runs out returns false, and the caller is
-// expected to raise the CTA's abort flag, drain what it has in flight and leave through the
-// normal teardown (TMEM freed) so that the context stays usable.
+// Every wait in here is bounded: a wait that runs out raises the CTA's abort flag and records a
+// code in the device status word; the kernel then runs to its normal end without waiting any more
+// (TMEM freed), so that the context stays usable.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -20,6 +20,7 @@ enum : unsigned int {
   DEV_TIMEOUT_TMA = 1u,     // a wait on a TMA "full" barrier ran out
   DEV_TIMEOUT_MMA = 2u,     // a wait on a tcgen05.commit barrier ran out
   DEV_TIMEOUT_SYNC = 3u,    // a wait on a CTA-internal hand-off barrier ran out
+  DEV_BAD_SMEM_BASE = 4u,   // dynamic shared memory did not start on a 1024-byte boundary
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -57,17 +58,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Upper bound on one wait, in SM clock cycles (about one second at 2 GHz).
 constexpr long long kWaitCycleLimit = 2000000000LL;
 
-// Bounded wait.  `abort_flag` is a CTA-shared word: once any thread has raised it every other
-// wait in the CTA gives up on its next poll, so the whole CTA unwinds within microseconds.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+// Bounded wait.  `abort_flag` is a CTA-shared word.  A wait that runs out raises it, records `code`
+// in the device status word and returns false; from then on every wait of the CTA returns false at
+// once, so all roles run their loops to the end without waiting (their results are garbage and the
+// host learns of it through the status word), meet at the final barrier and free tensor memory.
+// Control flow therefore never depends on a wait's outcome, which keeps warp-collective
+// instructions and named barriers safe.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          unsigned int* status, unsigned int code) {
   if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag != 0u) return false;
   const long long t0 = clock64();
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++polls & 0xffu) == 0u) {
+    if ((++polls & 0x3fu) == 0u) {
       if (*abort_flag != 0u) return false;
-      if (clock64() - t0 > kWaitCycleLimit) return false;
+      if (clock64() - t0 > kWaitCycleLimit) {
+        *abort_flag = 1u;
+        atomicMax(status, code);
+        return false;
+      }
     }
   }
 }
@@ -113,6 +124,17 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void*
       "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
       ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+// shared -> global element-wise add (fp32 tensor map); out-of-range parts of the box are dropped
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1,
+                                                  int c2, int c3) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
