@@ -261,6 +261,13 @@ int acct_fa_fwd(const acct_fa_args* a, void* stream) {
   FwdParams p;
   memset(&p, 0, sizeof(p));
   if ((rc = make_qkv_maps(a, st, &p.map_q, &p.map_k, &p.map_v))) return rc;
+  {
+    TensorDesc4 t;
+    t.dtype = a->dtype; t.ptr = a->o;
+    t.dims[0] = a->D; t.dims[1] = a->S_q; t.dims[2] = a->N; t.dims[3] = a->B;
+    t.strides[0] = st.o[2]; t.strides[1] = st.o[1]; t.strides[2] = st.o[0];
+    if ((rc = make_tmap_4d(&p.map_o, t, kTile))) return rc;
+  }
   p.o = a->o;
   p.lse = a->lse;
   p.o_stride_b = st.o[0]; p.o_stride_h = st.o[1]; p.o_stride_s = st.o[2];

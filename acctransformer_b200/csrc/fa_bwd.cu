@@ -371,16 +371,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       tc_fence_before_sync();
       mbar_arrive(&sh.pds_ready);
 
-      // park the next tile's statistics
+      // ---- drain dQ_i: tensor memory -> registers -> swizzled staging (this half's dS^T block) -> TMA reduce
+      mbar_wait(&sh.ds_done, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      tc_fence_after_sync();
+      // Park the next tile's statistics.  ds_done implies that all 256 compute threads have arrived at
+      // pds_ready, hence have passed this tile's stats_ready wait: the barrier cannot run a phase ahead of
+      // a waiter, and nobody still reads the buffer being overwritten (it held the previous tile's values).
       if (hf == 0 && n + 1 < n_iter) {
         sh.lse2[(n + 1) & 1][r] = nxt_lse;
         sh.delta[(n + 1) & 1][r] = nxt_dlt;
         mbar_arrive(&sh.stats_ready);
       }
-
-      // ---- drain dQ_i: tensor memory -> registers -> swizzled staging (this half's dS^T block) -> TMA reduce
-      mbar_wait(&sh.ds_done, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
-      tc_fence_after_sync();
       uint32_t dq[kDrainRounds][32];
 #pragma unroll
       for (int rd = 0; rd < kDrainRounds; ++rd) tmem_ld32(t_dp + (hf * kDrainRounds + rd) * 32, dq[rd]);

@@ -9,7 +9,14 @@
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 columns each.  The 16-bit probabilities are
 // written back over the first 64 columns of their own S buffer and feed the second MMA straight
 // from tensor memory.  While one group runs softmax on its tile the tensor pipe works on the other
-// group's tile, so the two overlap.
+// group's tile, so the two overlap.  A softmax thread pulls its whole 128-entry score row into
+// registers with one wait, so the row maximum, the exponentials and the row sum need a single
+// pass over tensor memory.  O leaves through shared memory (the CTA's own Q tile, dead by then)
+// and a TMA store.
+//
+// CTAs are numbered so that, inside a group of kUnitGroup (batch, head) slices, the tile pairs
+// with the most K/V tiles (the latest rows under a causal mask) start first, while the slices that
+// run at the same time stay few enough for their K and V to sit in L2.
 //
 // Follows the reference's forward (train/acctransformer/flash_attention/ops/flash_attention/
 // flash_attention_fwd.py:308-457): per K/V tile  S -> (+alibi, +mask*-10000) -> running max ->
@@ -29,6 +36,7 @@ namespace {
 
 constexpr int kFwdThreads = 320;
 constexpr int kStages = 2;
+constexpr int kUnitGroup = 8;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
 struct TileRange {
@@ -36,7 +44,7 @@ struct TileRange {
 };
 
 // K/V tiles that Q tile `i` needs: the block band  j - next <= i <= j + prev, the causal triangle,
-// and the valid key length.
+// the TriangleAttention row groups and the valid key length.
 __device__ __forceinline__ TileRange kv_tile_range(int i, int s_q, int kv_len, const ScoreMods& m) {
   TileRange r;
   if (i * kTile >= s_q || kv_len <= 0) { r.lo = 0; r.hi = -1; return r; }
@@ -73,7 +81,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;                          // 2 tiles
+  uint8_t* sQ = smem;                          // 2 tiles; reused as the staging of O at the end
   uint8_t* sK = sQ + 2 * kTileBytes;           // kStages tiles
   uint8_t* sV = sK + kStages * kTileBytes;     // kStages tiles
   __shared__ FwdShared sh;
@@ -81,11 +89,21 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int bh = blockIdx.y;
-  const int b = bh / p.N, h = bh % p.N;
-  // heavier (later) tile pairs first: under a causal mask they have the most K/V tiles
-  const int pair = gridDim.x - 1 - blockIdx.x;
   const ScoreMods& mods = p.mods;
+
+  // linear CTA number -> ((batch, head) slice, tile pair): groups of kUnitGroup slices, heaviest pairs first
+  const int n_pairs = (p.S_q + 2 * kTile - 1) / (2 * kTile);
+  const int n_units = p.B * p.N;
+  int bh, pair;
+  {
+    const int per_group = n_pairs * kUnitGroup;
+    const int g = blockIdx.x / per_group;
+    const int within = blockIdx.x % per_group;
+    const int g_units = min(kUnitGroup, n_units - g * kUnitGroup);
+    pair = n_pairs - 1 - within / g_units;
+    bh = g * kUnitGroup + within % g_units;
+  }
+  const int b = bh / p.N, h = bh % p.N;
 
   int kv_len = p.S_k;
   if (mods.seq_lens != nullptr) kv_len = min(p.S_k, max(0, mods.seq_lens[b]));
@@ -120,7 +138,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && cta_hi >= cta_lo) {
-      prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v);
+      prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_o);
       mbar_expect_tx(&sh.q_full, 2 * kTileBytes);
       for (int qt = 0; qt < 2; ++qt)
         for (int nb = 0; nb < NB; ++nb)
@@ -214,9 +232,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q + min(q_row, p.S_q - 1)) * p.S_k;
     const int64_t drop_row = (static_cast<int64_t>(bh) * p.S_q + min(q_row, p.S_q - 1)) * p.S_k;
 
-    // keys at or past this index do not exist for this thread's row (TriangleAttention row groups)
+    // Keys at or past `bound` do not exist for this thread's row: valid length, TriangleAttention row
+    // group, causal triangle.  `bound_tile` is the smallest bound of any row of the tile.
     const int tri_end = mods.tri_block > 0 ? (min(q_row, p.S_q - 1) / mods.tri_block + 1) * mods.tri_block : 0x7fffffff;
     const int tri_end_tile = mods.tri_block > 0 ? ((q_tile * kTile) / mods.tri_block + 1) * mods.tri_block : 0x7fffffff;
+    const int bound = min(min(kv_len, tri_end), mods.causal ? q_row + 1 : 0x7fffffff);
+    const int bound_tile = min(min(kv_len, tri_end_tile), mods.causal ? q_tile * kTile + 1 : 0x7fffffff);
 
     float m_run = kNegInf, l_run = 0.f;
     int n = 0;
@@ -224,24 +245,26 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       mbar_wait(&sh.s_full[qt], n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
       const int col_base = j * kTile;
-      const bool diag = mods.causal && (col_base + kTile - 1 > q_tile * kTile);
-      const bool tail = col_base + kTile > kv_len;
       const bool use_mask = (mods.mask_kind == 1) || (mods.mask_kind == 2 && j == q_tile);
-      const bool tri_partial = col_base + kTile > tri_end_tile;
-      const bool transform = diag || tail || use_mask || has_alibi || tri_partial;
+      const bool generic = use_mask || has_alibi;
+      const bool partial = col_base + kTile > bound_tile;   // some (row, key) pairs of this tile do not exist
 
-      // pass 1: (transform and) row max
-      float m_tile = kNegInf;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_s + c * 32, r);
-        tmem_wait_ld();
-        if (transform) {
+      // the whole score row in registers, one wait
+      uint32_t s[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
+      tmem_wait_ld();
+
+      float mult = p.scale_log2;
+      if (generic) {
+        // general path: alibi and / or a mask tensor (per-element loads); values leave in log2 units
+        mult = 1.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {   // unrolled: the score row must stay in registers
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = col_base + c * 32 + i;
-            float x = __uint_as_float(r[i]) * p.scale_log2;
+            float x = __uint_as_float(s[c][i]) * p.scale_log2;
             if (col < kv_len) {
               if (mods.alibi != nullptr) x += load16<BF16>(mods.alibi, alibi_row + col) * kLog2e;
               else if (mods.alibi_slopes != nullptr) x += slope_l2 * static_cast<float>(col);
@@ -253,19 +276,27 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
                 x += mv * (-10000.0f * kLog2e);
               }
             }
-            if (col >= kv_len || col >= tri_end || (mods.causal && col > q_row)) x = kNegInf;
-            r[i] = __float_as_uint(x);
-            m_tile = fmaxf(m_tile, x);
+            s[c][i] = __float_as_uint(col >= bound ? kNegInf : x);
           }
-          tmem_st32(t_s + c * 32, r);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(r[i]));
         }
+      } else if (partial) {
+        // only positions that do not exist: one compare + select per element, no branches
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            s[c][i] = (col_base + c * 32 + i >= bound) ? __float_as_uint(kNegInf) : s[c][i];
       }
-      float mult = 1.0f;
-      if (transform) tmem_wait_st();
-      else { m_tile *= p.scale_log2; mult = p.scale_log2; }   // scale > 0: max commutes with the scaling
+
+      // row maximum (four independent chains)
+      float mx[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        mx[c] = __uint_as_float(s[c][0]);
+#pragma unroll
+        for (int i = 1; i < 32; ++i) mx[c] = fmaxf(mx[c], __uint_as_float(s[c][i]));
+      }
+      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * mult;   // scale > 0
 
       // running max, refreshed only when it grows by more than the threshold
       const float m_new = fmaxf(m_run, m_tile);
@@ -287,22 +318,18 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
           tmem_st32(t_o + c * 32, r);
         }
-        tmem_wait_st();
       }
       const float m_use = (m_run == kNegInf) ? 0.f : m_run;
 
-      // pass 2: P = exp2(x - m), row sum before dropout, 16-bit P over the S buffer
-      float l_tile = 0.f;
-#pragma unroll 1
+      // P = exp2(x - m), row sum before dropout, 16-bit P over the S buffer
+      float l_part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_s + c * 32, r);
-        tmem_wait_ld();
         float pr[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          pr[i] = ex2(fmaf(__uint_as_float(r[i]), mult, -m_use));
-          l_tile += pr[i];
+          pr[i] = ex2(fmaf(__uint_as_float(s[c][i]), mult, -m_use));
+          l_part[i & 3] += pr[i];
         }
         if (mods.drop != nullptr) {
           const int col0 = col_base + c * 32;
@@ -319,48 +346,53 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         for (int i = 0; i < 16; ++i) pk[i] = pack2<BF16>(pr[2 * i], pr[2 * i + 1]);
         tmem_st16(t_s + c * 16, pk);
       }
-      l_run += l_tile;
+      l_run += (l_part[0] + l_part[1]) + (l_part[2] + l_part[3]);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&sh.p_ready[qt]);
     }
 
-    // epilogue: O / l and L = m + ln l
+    // epilogue: O / l through this group's (now dead) Q tile in shared memory and a TMA store, which
+    // clips rows past S_q and columns past D; L = m + ln l straight to global memory
     if (q_tile * kTile < p.S_q) {
       if (n > 0) {
         mbar_wait(&sh.o_done[qt], (n - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
         tc_fence_after_sync();
+      } else if (cta_hi >= cta_lo) {
+        // no K/V tile for this Q tile, but its TMA load was issued: let it land before the tile is reused
+        mbar_wait(&sh.q_full, 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
       }
-      {
-        const float inv_l = (n > 0 && l_run > 0.f) ? 1.0f / l_run : 0.f;
-        const bool row_ok = q_row < p.S_q;
-        uint8_t* o_row = reinterpret_cast<uint8_t*>(p.o) +
-                         2 * (b * p.o_stride_b + h * p.o_stride_h + static_cast<int64_t>(q_row) * p.o_stride_s);
+      const float inv_l = (n > 0 && l_run > 0.f) ? 1.0f / l_run : 0.f;
+      uint8_t* stage = sQ + qt * kTileBytes;
 #pragma unroll 1
-        for (int c = 0; c < DPAD / 32; ++c) {
-          uint32_t r[32];
-          if (n > 0) { tmem_ld32(t_o + c * 32, r); tmem_wait_ld(); }
-          else {
+      for (int c = 0; c < DPAD / 32; ++c) {
+        uint32_t r[32];
+        if (n > 0) { tmem_ld32(t_o + c * 32, r); tmem_wait_ld(); }
+        else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0u;
-          }
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            pk[i] = pack2<BF16>(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
-          if (row_ok) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int col = c * 32 + g * 8;
-              if (col + 8 <= p.D)
-                *reinterpret_cast<uint4*>(o_row + col * 2) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
-            }
-          }
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
-        if (row_ok && p.lse != nullptr)
-          p.lse[static_cast<int64_t>(bh) * p.S_q + q_row] =
-              (n > 0 && l_run > 0.f) ? m_run * kLn2 + logf(l_run) : kNegInf;
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          pk[i] = pack2<BF16>(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
+        uint8_t* blk = stage + (c >> 1) * 16384u;
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          *reinterpret_cast<uint4*>(blk + swz128(row_in_tile, (c & 1) * 4 + g)) =
+              make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
       }
+      fence_proxy_async_smem();
+      named_barrier(1 + qt, 128);
+      if (row_in_tile == 0) {
+        for (int nb = 0; nb < NB; ++nb)
+          if (nb * 64 < p.D) tma_store_4d(&p.map_o, stage + nb * 16384, nb * 64, q_tile * kTile, h, b);
+        tma_store_commit();
+        tma_store_wait_read();
+      }
+      if (q_row < p.S_q && p.lse != nullptr)
+        p.lse[static_cast<int64_t>(bh) * p.S_q + q_row] =
+            (n > 0 && l_run > 0.f) ? m_run * kLn2 + logf(l_run) : kNegInf;
     }
     tc_fence_before_sync();
   }
@@ -375,7 +407,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
 cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : 128;
   const size_t smem = static_cast<size_t>(2 + 2 * kStages) * (dpad / 64) * 16384 + 1024;
-  dim3 grid((p.S_q + 2 * kTile - 1) / (2 * kTile), p.B * p.N);
+  const int n_pairs = (p.S_q + 2 * kTile - 1) / (2 * kTile);
+  dim3 grid(static_cast<unsigned>(n_pairs) * static_cast<unsigned>(p.B * p.N));
   void (*kern)(const FwdParams) = nullptr;
   if (dpad == 64) kern = bf16 ? fa_fwd_kernel<64, true> : fa_fwd_kernel<64, false>;
   else kern = bf16 ? fa_fwd_kernel<128, true> : fa_fwd_kernel<128, false>;

@@ -26,7 +26,7 @@ struct ScoreMods {
 };
 
 struct alignas(64) FwdParams {
-  CUtensorMap map_q, map_k, map_v;
+  CUtensorMap map_q, map_k, map_v, map_o;
   void* o;
   float* lse;
   int64_t o_stride_b, o_stride_h, o_stride_s;
