@@ -12,9 +12,11 @@
 //   dV  += (P^T*M) dO_i       (A from tensor memory, written over S^T; B = dO_i, MN-major)
 // Warp roles: warps 0-7 compute (thread = one key row x one half of the query columns), warp 8 =
 // TMA producer (K/V once, Q and dO in two-stage rings), warp 9 = MMA issuer.  Tensor memory:
-// S^T/P^T | dP^T/dQ | dK | dV, 128 columns each.  The MMA issuer runs one step ahead: S^T of the
-// next Q tile is issued right behind the products of the current one, so the tensor pipe works
-// while the compute warps drain dQ and form the next P^T.
+// S^T/P^T | dP^T/dQ | dK | dV, 128 columns each.  Per Q tile n the tensor pipe runs
+// dV(n), S^T(n+1), dK(n), dQ(n), dP^T(n+1): dV starts as soon as P^T is written (the compute warps go
+// on to dS^T meanwhile), S^T of the next tile follows at once, and dP^T of the next tile waits only
+// for dQ to be pulled out of its columns.  dQ leaves through shared memory that is dead at that
+// moment (the dS^T block and the dO stage of the tile) and a TMA reduce-add.
 //
 // Follows the reference's backward (train/acctransformer/flash_attention/ops/flash_attention/
 // flash_attention_bwd.py:259-415): K/V tile outer, Q tile inner, P recomputed from L, D = rowsum(dO*O)
@@ -38,16 +40,18 @@ constexpr int kStages = 2;
 struct BwdShared {
   uint64_t kv_full;
   uint64_t q_full[kStages], do_full[kStages];
-  uint64_t qdo_empty[kStages];   // MMA -> producer: every product reading this Q / dO stage has finished
-  uint64_t st_full, dp_full;     // MMA -> compute
-  uint64_t pds_ready;            // compute -> MMA: P^T in tensor memory, dS^T in shared memory
-  uint64_t ds_done;              // MMA -> compute: dK and dQ products finished (dS^T free, dQ in tensor memory)
-  uint64_t dq_read;              // compute -> MMA: dQ drained, the dP^T columns are free again
+  uint64_t q_empty[kStages];     // MMA -> producer: the dK product reading this Q stage has finished
+  uint64_t stage_free[kStages];  // compute -> producer: the dQ staging borrowed from this dO stage has been read
+  uint64_t st_full, dp_full;     // MMA -> compute: S^T / dP^T are in tensor memory
+  uint64_t p_ready;              // compute -> MMA: P^T is in tensor memory
+  uint64_t ds_ready;             // compute -> MMA: dS^T is in shared memory
+  uint64_t dq_full;              // MMA -> compute: dV, dK and dQ products of this Q tile have finished
+  uint64_t dq_read;              // compute -> MMA: dQ is in registers, the dP^T columns are free again
   uint64_t stats_ready;          // compute -> compute: lse2 / delta of this Q tile are in shared memory
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
-  float lse2[2][kTile];          // L * log2(e) per query of the tile (+inf for rows past S_q)
-  float delta[2][kTile];
+  alignas(16) float lse2[2][kTile];   // L * log2(e) per query of the tile (+inf for rows past S_q); read as float4
+  alignas(16) float delta[2][kTile];
 };
 
 // P = exp2(s*scale + bias - L) for 32 consecutive queries of one key row; `bias` is -inf for key rows
@@ -115,12 +119,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   if (tid == 0) {
     mbar_init(&sh.kv_full, 1);
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&sh.q_full[s], 1); mbar_init(&sh.do_full[s], 1); mbar_init(&sh.qdo_empty[s], 1);
+      mbar_init(&sh.q_full[s], 1); mbar_init(&sh.do_full[s], 1);
+      mbar_init(&sh.q_empty[s], 1); mbar_init(&sh.stage_free[s], 2);
     }
     mbar_init(&sh.st_full, 1);
     mbar_init(&sh.dp_full, 1);
-    mbar_init(&sh.pds_ready, kComputeThreads);
-    mbar_init(&sh.ds_done, 1);
+    mbar_init(&sh.p_ready, kComputeThreads);
+    mbar_init(&sh.ds_ready, kComputeThreads);
+    mbar_init(&sh.dq_full, 1);
     mbar_init(&sh.dq_read, kComputeThreads);
     mbar_init(&sh.stats_ready, kTile);
     sh.abort_flag = 0;
@@ -137,16 +143,21 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_iter > 0) {
       prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_do);
+      prefetch_tmap(&p.map_dq);
       mbar_expect_tx(&sh.kv_full, 2 * kTileBytes);
       for (int nb = 0; nb < NB; ++nb) tma_load_4d(sK + nb * 16384, &p.map_k, &sh.kv_full, nb * 64, j * kTile, h, b);
       for (int nb = 0; nb < NB; ++nb) tma_load_4d(sV + nb * 16384, &p.map_v, &sh.kv_full, nb * 64, j * kTile, h, b);
       for (int n = 0; n < n_iter; ++n) {
         const int i = i_lo + n;
         const int st = n % kStages;
-        if (n >= kStages) mbar_wait(&sh.qdo_empty[st], ((n / kStages) - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+        const uint32_t reuse_parity = ((n / kStages) - 1) & 1;
+        // the Q stage is free once the dK product of two tiles ago has finished
+        if (n >= kStages) mbar_wait(&sh.q_empty[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         mbar_expect_tx(&sh.q_full[st], kTileBytes);
         for (int nb = 0; nb < NB; ++nb)
           tma_load_4d(sQ + st * kTileBytes + nb * 16384, &p.map_q, &sh.q_full[st], nb * 64, i * kTile, h, b);
+        // the dO stage doubles as dQ staging: it is free once that staging has been read by the TMA reduce
+        if (n >= kStages) mbar_wait(&sh.stage_free[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         mbar_expect_tx(&sh.do_full[st], kTileBytes);
         for (int nb = 0; nb < NB; ++nb)
           tma_load_4d(sDO + st * kTileBytes + nb * 16384, &p.map_do, &sh.do_full[st], nb * 64, i * kTile, h, b);
@@ -154,6 +165,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
+    // Tensor-pipe order per Q tile n:  dV(n), S^T(n+1), dK(n), dQ(n), dP^T(n+1).
     if (lane == 0 && n_iter > 0) {
       const uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);     // S^T, dP^T
       const uint32_t idesc_kv = make_idesc(BF16, 128, DPAD, false, true);    // dV, dK
@@ -171,47 +183,60 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         }
         umma_commit(&sh.st_full);
       };
-
-      mbar_wait(&sh.kv_full, 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
-      mbar_wait(&sh.q_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
-      tc_fence_after_sync();
-      issue_st(0);
-      for (int n = 0; n < n_iter; ++n) {
-        const int st = n % kStages;
-        const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
+      auto issue_dp = [&](int st) {   // dP^T = V dO^T
         const uint32_t aDO = smem_u32(sDO + st * kTileBytes);
-        // dP^T = V dO^T, once the previous dQ has been drained from those columns
-        mbar_wait(&sh.do_full[st], (n / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
-        if (n > 0) mbar_wait(&sh.dq_read, (n - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-        tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < DPAD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
           umma_ss(tmem + kColDP, sdesc_at(kmajor, aV + off), sdesc_at(kmajor, aDO + off), idesc_s, kk > 0);
         }
         umma_commit(&sh.dp_full);
-        // the products that consume dS^T first, so that the compute warps can start draining dQ early
-        mbar_wait(&sh.pds_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+      };
+
+      mbar_wait(&sh.kv_full, 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
+      mbar_wait(&sh.q_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
+      tc_fence_after_sync();
+      issue_st(0);
+      mbar_wait(&sh.do_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
+      tc_fence_after_sync();
+      issue_dp(0);
+      for (int n = 0; n < n_iter; ++n) {
+        const int st = n % kStages;
+        const int stn = (n + 1) % kStages;
+        const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
+        const uint32_t aDO = smem_u32(sDO + st * kTileBytes);
+        // dV += P^T dO as soon as P^T is in tensor memory (the compute warps go on to dS meanwhile);
+        // P^T of query columns [64h, 64h+64) sits in S^T columns [64h, 64h+32)
+        mbar_wait(&sh.p_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)   // dK += dS^T Q
-          umma_ss(tmem + kColDK, sdesc_at(kmajor, aDS + (kk >> 2) * 16384u + (kk & 3) * 32u),
-                  sdesc_at(mnmajor, aQ + kk * 2048u), idesc_kv, n > 0 || kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)   // dQ = dS K
-          umma_ss(tmem + kColDP, sdesc_at(mnmajor, aDS + kk * 2048u), sdesc_at(mnmajor, aK + kk * 2048u), idesc_dq, kk > 0);
-        umma_commit(&sh.ds_done);
-        // dV += P^T dO; P^T of query columns [64h, 64h+64) sits in S^T columns [64h, 64h+32)
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
           umma_ts(tmem + kColDV, tmem + kColST + (kk >> 2) * 64 + (kk & 3) * 8, sdesc_at(mnmajor, aDO + kk * 2048u),
                   idesc_kv, n > 0 || kk > 0);
-        umma_commit(&sh.qdo_empty[st]);
-        // S^T of the next Q tile right behind (the tensor pipe runs in order, so P^T has been consumed)
+        // S^T of the next Q tile right behind it (the tensor pipe runs in order, so P^T has been consumed)
         if (n + 1 < n_iter) {
-          mbar_wait(&sh.q_full[(n + 1) % kStages], ((n + 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+          mbar_wait(&sh.q_full[stn], ((n + 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
           tc_fence_after_sync();
-          issue_st((n + 1) % kStages);
+          issue_st(stn);
+        }
+        // dK += dS^T Q and dQ = dS K once dS^T is in shared memory
+        mbar_wait(&sh.ds_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ss(tmem + kColDK, sdesc_at(kmajor, aDS + (kk >> 2) * 16384u + (kk & 3) * 32u),
+                  sdesc_at(mnmajor, aQ + kk * 2048u), idesc_kv, n > 0 || kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ss(tmem + kColDP, sdesc_at(mnmajor, aDS + kk * 2048u), sdesc_at(mnmajor, aK + kk * 2048u), idesc_dq, kk > 0);
+        umma_commit(&sh.dq_full);
+        umma_commit(&sh.q_empty[st]);
+        // dP^T of the next Q tile into the columns dQ is being drained from
+        if (n + 1 < n_iter) {
+          mbar_wait(&sh.do_full[stn], ((n + 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+          mbar_wait(&sh.dq_read, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+          tc_fence_after_sync();
+          issue_dp(stn);
         }
       }
     }
@@ -225,7 +250,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     const uint32_t t_dp = tmem + lane_base + kColDP;
     const bool kv_ok = kv_idx < kv_len;
     const bool elected = (tid == hf * 128);
-    uint8_t* my_ds = sDS + hf * 16384u;                  // this half's dS^T block, reused as its dQ staging
+    uint8_t* my_ds = sDS + hf * 16384u;                  // this half's dS^T block; also staging of its first dQ chunk
     float bias = kNegInf;                                // alibi term in log2 units; -inf removes the key row
     if (kv_ok) {
       bias = 0.f;
@@ -247,7 +272,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     for (int n = 0; n < n_iter; ++n) {
       const int i = i_lo + n;
       const int q_base = i * kTile;
-      // fetch the next tile's statistics now, park them in shared memory after this tile's math
+      const int st = n % kStages;
+      // fetch the next tile's statistics now, park them in shared memory later in this iteration
       if (hf == 0 && n + 1 < n_iter) {
         const int q_row = q_base + kTile + r;
         const bool q_ok = q_row < p.S_q;
@@ -262,121 +288,131 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       const bool diag = mods.causal && (q_base < j * kTile + kTile - 1);
       const bool generic = use_mask || mods.drop != nullptr || mods.tri_block > 0;
 
+      // ---- P part: needs S^T only.  P^T (dropped) goes over the first 32 of this half's own 64 S^T
+      // columns, which the half has finished reading by then.
       mbar_wait(&sh.st_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
       float pr[2][32];
-      if (!generic) {
-        // ---- P part: needs S^T only, runs while the tensor pipe still works on dP^T
+      {
+        uint32_t s[2][32];
+        tmem_ld32(t_st + (hf * 2) * 32, s[0]);
+        tmem_ld32(t_st + (hf * 2 + 1) * 32, s[1]);
+        tmem_wait_ld();
+        if (!generic) {
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = hf * 2 + cc;
-          uint32_t s[32];
-          tmem_ld32(t_st + c * 32, s);
-          tmem_wait_ld();
-          if (diag) p_fast<true>(s, lse2 + c * 32, p.scale_log2, bias, kv_idx, q_base + c * 32, pr[cc]);
-          else p_fast<false>(s, lse2 + c * 32, p.scale_log2, bias, kv_idx, q_base + c * 32, pr[cc]);
-        }
-        // P^T goes over the first 32 of this half's own 64 S^T columns, which it has finished reading
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = hf * 2 + cc;
+            if (diag) p_fast<true>(s[cc], lse2 + c * 32, p.scale_log2, bias, kv_idx, q_base + c * 32, pr[cc]);
+            else p_fast<false>(s[cc], lse2 + c * 32, p.scale_log2, bias, kv_idx, q_base + c * 32, pr[cc]);
+            uint32_t pk[16];
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) pk[e] = pack2<BF16>(pr[cc][2 * e], pr[cc][2 * e + 1]);
-          tmem_st16(t_st + hf * 64 + cc * 16, pk);
-        }
-      }
-      mbar_wait(&sh.dp_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
-      tc_fence_after_sync();
-      // the dQ staging of the previous Q tile must have left this half's dS^T block
-      if (n > 0) {
-        if (elected) tma_store_wait_read();
-        named_barrier(1 + hf, 128);
-      }
-      if (!generic) {
-        // ---- dS part
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = hf * 2 + cc;
-          uint32_t dp[32];
-          tmem_ld32(t_dp + c * 32, dp);
-          tmem_wait_ld();
-          uint32_t dk_[16];
-#pragma unroll
-          for (int e4 = 0; e4 < 8; ++e4) {
-            const float4 Dl = *reinterpret_cast<const float4*>(dlt + c * 32 + 4 * e4);
-            const float d0 = pr[cc][4 * e4 + 0] * (__uint_as_float(dp[4 * e4 + 0]) - Dl.x);
-            const float d1 = pr[cc][4 * e4 + 1] * (__uint_as_float(dp[4 * e4 + 1]) - Dl.y);
-            const float d2 = pr[cc][4 * e4 + 2] * (__uint_as_float(dp[4 * e4 + 2]) - Dl.z);
-            const float d3 = pr[cc][4 * e4 + 3] * (__uint_as_float(dp[4 * e4 + 3]) - Dl.w);
-            dk_[2 * e4] = pack2<BF16>(d0, d1);
-            dk_[2 * e4 + 1] = pack2<BF16>(d2, d3);
+            for (int e = 0; e < 16; ++e) pk[e] = pack2<BF16>(pr[cc][2 * e], pr[cc][2 * e + 1]);
+            tmem_st16(t_st + hf * 64 + cc * 16, pk);
           }
+        } else {
+          // general path: mask tensor, dropout mask, triangle row groups (per-element loads and branches)
 #pragma unroll
-          for (int g = 0; g < 4; ++g)
-            *reinterpret_cast<uint4*>(my_ds + swz128(r, cc * 4 + g)) =
-                make_uint4(dk_[4 * g], dk_[4 * g + 1], dk_[4 * g + 2], dk_[4 * g + 3]);
-        }
-      } else {
-        // ---- general path: mask tensor, dropout mask, triangle row groups (per-element loads and branches)
-#pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = hf * 2 + cc;
-          uint32_t s[32], dp[32];
-          tmem_ld32(t_st + c * 32, s);
-          tmem_ld32(t_dp + c * 32, dp);
-          tmem_wait_ld();
-          uint32_t pk[16], dk_[16];
-          float pd_prev = 0.f, ds_prev = 0.f;
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = hf * 2 + cc;
+            uint32_t pk[16];
+            float pd_prev = 0.f;
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int q_row = q_base + c * 32 + e;
-            float x = fmaf(__uint_as_float(s[e]), p.scale_log2, bias);
-            if (use_mask && kv_ok && q_row < p.S_q) {
-              const float mv = mods.mask_kind == 1
-                                   ? load_mask_value(mods.mask, mods.mask_dtype,
-                                                     (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q + q_row) * p.S_k + kv_idx)
-                                   : load_mask_value(mods.mask, mods.mask_dtype, static_cast<int64_t>(c * 32 + e) * kTile + r);
-              x += mv * (-10000.0f * kLog2e);
+            for (int e = 0; e < 32; ++e) {
+              const int q_row = q_base + c * 32 + e;
+              float x = fmaf(__uint_as_float(s[cc][e]), p.scale_log2, bias);
+              if (use_mask && kv_ok && q_row < p.S_q) {
+                const float mv = mods.mask_kind == 1
+                                     ? load_mask_value(mods.mask, mods.mask_dtype,
+                                                       (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q + q_row) * p.S_k + kv_idx)
+                                     : load_mask_value(mods.mask, mods.mask_dtype, static_cast<int64_t>(c * 32 + e) * kTile + r);
+                x += mv * (-10000.0f * kLog2e);
+              }
+              float pv = ex2(x - lse2[c * 32 + e]);
+              if (diag && kv_idx > q_row) pv = 0.f;
+              if (mods.tri_block > 0 && kv_idx >= (min(q_row, p.S_q - 1) / mods.tri_block + 1) * mods.tri_block) pv = 0.f;
+              pr[cc][e] = pv;
+              float pd = pv;
+              if (mods.drop != nullptr) {
+                float fac = 0.f;
+                if (kv_ok && q_row < p.S_q)
+                  fac = load_mask_value(mods.drop, mods.drop_dtype,
+                                        (static_cast<int64_t>(bh) * p.S_q + q_row) * p.S_k + kv_idx) * mods.drop_scale;
+                pd = pv * fac;
+              }
+              if (e & 1) pk[e >> 1] = pack2<BF16>(pd_prev, pd);
+              else pd_prev = pd;
             }
-            float pv = ex2(x - lse2[c * 32 + e]);
-            if (diag && kv_idx > q_row) pv = 0.f;
-            if (mods.tri_block > 0 && kv_idx >= (min(q_row, p.S_q - 1) / mods.tri_block + 1) * mods.tri_block) pv = 0.f;
-            float fac = 1.0f;
-            if (mods.drop != nullptr) {
-              fac = 0.f;
-              if (kv_ok && q_row < p.S_q)
-                fac = load_mask_value(mods.drop, mods.drop_dtype,
-                                      (static_cast<int64_t>(bh) * p.S_q + q_row) * p.S_k + kv_idx) * mods.drop_scale;
-            }
-            const float pd = pv * fac;
-            const float ds = pv * (__uint_as_float(dp[e]) * fac - dlt[c * 32 + e]);
-            if (e & 1) {
-              pk[e >> 1] = pack2<BF16>(pd_prev, pd);
-              dk_[e >> 1] = pack2<BF16>(ds_prev, ds);
-            } else {
-              pd_prev = pd;
-              ds_prev = ds;
-            }
+            tmem_st16(t_st + hf * 64 + cc * 16, pk);
           }
-          // lands inside this half's first S^T chunk, which it loaded at cc = 0
-          tmem_st16(t_st + hf * 64 + cc * 16, pk);
-#pragma unroll
-          for (int g = 0; g < 4; ++g)
-            *reinterpret_cast<uint4*>(my_ds + swz128(r, cc * 4 + g)) =
-                make_uint4(dk_[4 * g], dk_[4 * g + 1], dk_[4 * g + 2], dk_[4 * g + 3]);
         }
       }
       tmem_wait_st();
-      fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(&sh.pds_ready);
+      mbar_arrive(&sh.p_ready);
 
-      // ---- drain dQ_i: tensor memory -> registers -> swizzled staging (this half's dS^T block) -> TMA reduce
-      mbar_wait(&sh.ds_done, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      // ---- dS part: dS^T = P^T * (dP^T * M - D) into this half's shared-memory block
+      mbar_wait(&sh.dp_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
-      // Park the next tile's statistics.  ds_done implies that all 256 compute threads have arrived at
-      // pds_ready, hence have passed this tile's stats_ready wait: the barrier cannot run a phase ahead of
-      // a waiter, and nobody still reads the buffer being overwritten (it held the previous tile's values).
+      {
+        uint32_t dp[2][32];
+        tmem_ld32(t_dp + (hf * 2) * 32, dp[0]);
+        tmem_ld32(t_dp + (hf * 2 + 1) * 32, dp[1]);
+        // the previous tile's dQ staging must have left this half's block (and the dO stage it borrowed)
+        if (n > 0) {
+          if (elected) {
+            tma_store_wait_read();
+            mbar_arrive(&sh.stage_free[(n - 1) % kStages]);
+          }
+          named_barrier(1 + hf, 128);
+        }
+        tmem_wait_ld();
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = hf * 2 + cc;
+          uint32_t dk_[16];
+          if (mods.drop == nullptr) {
+#pragma unroll
+            for (int e4 = 0; e4 < 8; ++e4) {
+              const float4 Dl = *reinterpret_cast<const float4*>(dlt + c * 32 + 4 * e4);
+              const float d0 = pr[cc][4 * e4 + 0] * (__uint_as_float(dp[cc][4 * e4 + 0]) - Dl.x);
+              const float d1 = pr[cc][4 * e4 + 1] * (__uint_as_float(dp[cc][4 * e4 + 1]) - Dl.y);
+              const float d2 = pr[cc][4 * e4 + 2] * (__uint_as_float(dp[cc][4 * e4 + 2]) - Dl.z);
+              const float d3 = pr[cc][4 * e4 + 3] * (__uint_as_float(dp[cc][4 * e4 + 3]) - Dl.w);
+              dk_[2 * e4] = pack2<BF16>(d0, d1);
+              dk_[2 * e4 + 1] = pack2<BF16>(d2, d3);
+            }
+          } else {
+            float ds_prev = 0.f;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int q_row = q_base + c * 32 + e;
+              float fac = 0.f;
+              if (kv_ok && q_row < p.S_q)
+                fac = load_mask_value(mods.drop, mods.drop_dtype,
+                                      (static_cast<int64_t>(bh) * p.S_q + q_row) * p.S_k + kv_idx) * mods.drop_scale;
+              const float ds = pr[cc][e] * (__uint_as_float(dp[cc][e]) * fac - dlt[c * 32 + e]);
+              if (e & 1) dk_[e >> 1] = pack2<BF16>(ds_prev, ds);
+              else ds_prev = ds;
+            }
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(my_ds + swz128(r, cc * 4 + g)) =
+                make_uint4(dk_[4 * g], dk_[4 * g + 1], dk_[4 * g + 2], dk_[4 * g + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&sh.ds_ready);
+
+      // ---- drain dQ_i: tensor memory -> registers -> swizzled staging -> TMA reduce-add.  Staging of this
+      // half's first 32-column chunk is its dS^T block, of its second chunk the matching block of the dO
+      // stage of this tile; both are dead once dq_full has fired (every product of this tile but none of
+      // the next reads them).
+      mbar_wait(&sh.dq_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      tc_fence_after_sync();
+      // Park the next tile's statistics.  dq_full implies that all 256 compute threads have arrived at
+      // ds_ready, hence have passed this tile's stats_ready wait and finished reading the buffer being
+      // overwritten (it held the previous tile's values).
       if (hf == 0 && n + 1 < n_iter) {
         sh.lse2[(n + 1) & 1][r] = nxt_lse;
         sh.delta[(n + 1) & 1][r] = nxt_dlt;
@@ -390,30 +426,30 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       mbar_arrive(&sh.dq_read);
 #pragma unroll
       for (int rd = 0; rd < kDrainRounds; ++rd) {
-        const int c = hf * kDrainRounds + rd;            // 32-column chunk of head_dim
-        if (rd > 0) {
-          if (elected) tma_store_wait_read();
-          named_barrier(1 + hf, 128);
-        }
+        uint8_t* stage = rd == 0 ? my_ds : sDO + st * kTileBytes + hf * 16384u;
 #pragma unroll
         for (int g = 0; g < 8; ++g)
-          *reinterpret_cast<float4*>(my_ds + swz128(r, g)) =
+          *reinterpret_cast<float4*>(stage + swz128(r, g)) =
               make_float4(__uint_as_float(dq[rd][4 * g]) * p.scale, __uint_as_float(dq[rd][4 * g + 1]) * p.scale,
                           __uint_as_float(dq[rd][4 * g + 2]) * p.scale, __uint_as_float(dq[rd][4 * g + 3]) * p.scale);
-        fence_proxy_async_smem();
-        named_barrier(1 + hf, 128);
-        if (elected && c * 32 < p.D) {
-          tma_reduce_add_4d(&p.map_dq, my_ds, c * 32, q_base, h, b);
-          tma_store_commit();
+      }
+      fence_proxy_async_smem();
+      named_barrier(1 + hf, 128);
+      if (elected) {
+#pragma unroll
+        for (int rd = 0; rd < kDrainRounds; ++rd) {
+          const int c = hf * kDrainRounds + rd;          // 32-column chunk of head_dim
+          const uint8_t* stage = rd == 0 ? my_ds : sDO + st * kTileBytes + hf * 16384u;
+          if (c * 32 < p.D) tma_reduce_add_4d(&p.map_dq, stage, c * 32, q_base, h, b);
         }
+        tma_store_commit();
       }
     }
     if (elected) tma_store_wait_all();
 
-    // epilogue: dK (scaled) and dV rows of this tile; each half writes its half of head_dim
+    // epilogue: dK (scaled) and dV rows of this tile; each half writes its half of head_dim.  The last
+    // dq_full wait above covered every product.
     // (the tensor-memory loads are warp-collective: every lane runs them, only the stores are guarded)
-    if (n_iter > 0)
-      mbar_wait(&sh.qdo_empty[(n_iter - 1) % kStages], ((n_iter - 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
     tc_fence_after_sync();
     const bool row_ok = kv_idx < p.S_k;
     const int64_t row_off = (static_cast<int64_t>(bh) * p.S_k + kv_idx) * p.D;
