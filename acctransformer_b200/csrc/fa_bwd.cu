@@ -10,13 +10,15 @@
 //   dK  += dS^T Q_i           (A = dS^T from shared memory, K-major; B = Q_i, MN-major)
 //   dQ_i = dS K_j             (A = the same dS^T tile read MN-major; B = K_j, MN-major) -> over dP^T
 //   dV  += (P^T*M) dO_i       (A from tensor memory, written over S^T; B = dO_i, MN-major)
-// Warp roles: warps 0-7 compute (thread = one key row x one half of the query columns), warp 8 =
-// TMA producer (K/V once, Q and dO in two-stage rings), warp 9 = MMA issuer.  Tensor memory:
+// Warp roles (four warpgroups, registers re-split between them with setmaxnreg): warps 0-7 compute
+// (thread = one key row x one half of the query columns), warps 8-11 drain dQ (thread = one query
+// row), warp 12 = TMA producer (K/V once, Q in a two-stage ring, dO single-buffered), warp 13 = MMA
+// issuer.  Tensor memory:
 // S^T/P^T | dP^T/dQ | dK | dV, 128 columns each.  Per Q tile n the tensor pipe runs
-// dV(n), S^T(n+1), dK(n), dQ(n), dP^T(n+1): dV starts as soon as P^T is written (the compute warps go
-// on to dS^T meanwhile), S^T of the next tile follows at once, and dP^T of the next tile waits only
-// for dQ to be pulled out of its columns.  dQ leaves through shared memory that is dead at that
-// moment (the dS^T block and the dO stage of the tile) and a TMA reduce-add.
+// dP^T(n) | dV(n), S^T(n+1) | dK(n), dQ(n): dP^T starts as soon as the previous dQ has been pulled
+// out of its columns, dV as soon as P^T is written (the compute warps go on to dS^T meanwhile), S^T
+// of the next tile right behind it.  The compute warps never wait for dQ: the drain warpgroup takes
+// it through a staging area in shared memory into the fp32 accumulator with TMA reduce-add.
 //
 // Follows the reference's backward (train/acctransformer/flash_attention/ops/flash_attention/
 // flash_attention_bwd.py:259-415): K/V tile outer, Q tile inner, P recomputed from L, D = rowsum(dO*O)
@@ -33,20 +35,27 @@ namespace acct {
 
 namespace {
 
-constexpr int kBwdThreads = 320;
+constexpr int kBwdThreads = 512;        // four warpgroups: compute x2, drain, control
 constexpr int kComputeThreads = 256;
-constexpr int kStages = 2;
+constexpr int kDrainWarp0 = 8;
+constexpr int kProducerWarp = 12;
+constexpr int kMmaWarp = 13;
+constexpr int kStages = 2;              // Q stages (dO has one)
+// Register budget per thread after the warpgroups re-split the register file (512 x 128 at launch):
+// 256 x 152 + 128 x 152 + 128 x 56 = 65536.
+constexpr int kRegsCompute = 152, kRegsDrain = 152, kRegsControl = 56;
 
 struct BwdShared {
   uint64_t kv_full;
-  uint64_t q_full[kStages], do_full[kStages];
+  uint64_t q_full[kStages];
   uint64_t q_empty[kStages];     // MMA -> producer: the dK product reading this Q stage has finished
-  uint64_t stage_free[kStages];  // compute -> producer: the dQ staging borrowed from this dO stage has been read
+  uint64_t do_full;
+  uint64_t do_empty;             // MMA -> producer: the dV product reading dO has finished
   uint64_t st_full, dp_full;     // MMA -> compute: S^T / dP^T are in tensor memory
   uint64_t p_ready;              // compute -> MMA: P^T is in tensor memory
   uint64_t ds_ready;             // compute -> MMA: dS^T is in shared memory
-  uint64_t dq_full;              // MMA -> compute: dV, dK and dQ products of this Q tile have finished
-  uint64_t dq_read;              // compute -> MMA: dQ is in registers, the dP^T columns are free again
+  uint64_t dq_full;              // MMA -> drain: dV, dK and dQ products of this Q tile have finished
+  uint64_t dq_read;              // drain -> MMA: dQ is in registers, the dP^T columns are free again
   uint64_t stats_ready;          // compute -> compute: lse2 / delta of this Q tile are in shared memory
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
@@ -80,16 +89,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   constexpr int NB = DPAD / 64;
   constexpr uint32_t kTileBytes = NB * 16384u;   // 128 rows x DPAD 16-bit elements
   constexpr uint32_t kColST = 0, kColDP = 128, kColDK = 256, kColDV = 384;
-  constexpr int kDrainRounds = DPAD / 64;        // 32-column dQ chunks per half of the compute warps
+  constexpr int kChunks = DPAD / 32;             // 32-column fp32 chunks of a dQ / dK / dV row
 
   // All shared memory is dynamic so that the tiles start at the (1024-byte aligned) base of the CTA's window.
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
   uint8_t* sV = sK + kTileBytes;
   uint8_t* sQ = sV + kTileBytes;                   // kStages tiles
-  uint8_t* sDO = sQ + kStages * kTileBytes;        // kStages tiles
-  uint8_t* sDS = sDO + kStages * kTileBytes;       // dS^T: 2 blocks of 128 key rows x 64 queries; also dQ staging
-  BwdShared& sh = *reinterpret_cast<BwdShared*>(sDS + 32768);
+  uint8_t* sDO = sQ + kStages * kTileBytes;        // one tile
+  uint8_t* sDS = sDO + kTileBytes;                 // dS^T: 2 blocks of 128 key rows x 64 queries
+  uint8_t* sStage = sDS + 32768;                   // dQ staging: 2 chunks of 128 rows x 32 fp32
+  BwdShared& sh = *reinterpret_cast<BwdShared*>(sStage + 32768);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -118,130 +128,169 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
 
   if (tid == 0) {
     mbar_init(&sh.kv_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&sh.q_full[s], 1); mbar_init(&sh.do_full[s], 1);
-      mbar_init(&sh.q_empty[s], 1); mbar_init(&sh.stage_free[s], 2);
-    }
+    for (int s = 0; s < kStages; ++s) { mbar_init(&sh.q_full[s], 1); mbar_init(&sh.q_empty[s], 1); }
+    mbar_init(&sh.do_full, 1);
+    mbar_init(&sh.do_empty, 1);
     mbar_init(&sh.st_full, 1);
     mbar_init(&sh.dp_full, 1);
     mbar_init(&sh.p_ready, kComputeThreads);
     mbar_init(&sh.ds_ready, kComputeThreads);
     mbar_init(&sh.dq_full, 1);
-    mbar_init(&sh.dq_read, kComputeThreads);
+    mbar_init(&sh.dq_read, kTile);
     mbar_init(&sh.stats_ready, kTile);
     sh.abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 8) { tmem_alloc(&sh.tmem_base, 512); tmem_relinquish(); }
+  if (warp == kProducerWarp) { tmem_alloc(&sh.tmem_base, 512); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = sh.tmem_base;
   volatile uint32_t* abort_flag = &sh.abort_flag;
 
-  if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_iter > 0) {
-      prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_do);
-      prefetch_tmap(&p.map_dq);
-      mbar_expect_tx(&sh.kv_full, 2 * kTileBytes);
-      for (int nb = 0; nb < NB; ++nb) tma_load_4d(sK + nb * 16384, &p.map_k, &sh.kv_full, nb * 64, j * kTile, h, b);
-      for (int nb = 0; nb < NB; ++nb) tma_load_4d(sV + nb * 16384, &p.map_v, &sh.kv_full, nb * 64, j * kTile, h, b);
-      for (int n = 0; n < n_iter; ++n) {
-        const int i = i_lo + n;
-        const int st = n % kStages;
-        const uint32_t reuse_parity = ((n / kStages) - 1) & 1;
-        // the Q stage is free once the dK product of two tiles ago has finished
-        if (n >= kStages) mbar_wait(&sh.q_empty[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-        mbar_expect_tx(&sh.q_full[st], kTileBytes);
-        for (int nb = 0; nb < NB; ++nb)
-          tma_load_4d(sQ + st * kTileBytes + nb * 16384, &p.map_q, &sh.q_full[st], nb * 64, i * kTile, h, b);
-        // the dO stage doubles as dQ staging: it is free once that staging has been read by the TMA reduce
-        if (n >= kStages) mbar_wait(&sh.stage_free[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-        mbar_expect_tx(&sh.do_full[st], kTileBytes);
-        for (int nb = 0; nb < NB; ++nb)
-          tma_load_4d(sDO + st * kTileBytes + nb * 16384, &p.map_do, &sh.do_full[st], nb * 64, i * kTile, h, b);
+  if (warp >= kProducerWarp) {
+    // ------------------------------------------------------------------ control warpgroup
+    reg_dealloc<kRegsControl>();
+    if (warp == kProducerWarp) {
+      // ---------------------------------------------------------------- TMA producer
+      if (lane == 0 && n_iter > 0) {
+        prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_do);
+        prefetch_tmap(&p.map_dq);
+        mbar_expect_tx(&sh.kv_full, 2 * kTileBytes);
+        for (int nb = 0; nb < NB; ++nb) tma_load_4d(sK + nb * 16384, &p.map_k, &sh.kv_full, nb * 64, j * kTile, h, b);
+        for (int nb = 0; nb < NB; ++nb) tma_load_4d(sV + nb * 16384, &p.map_v, &sh.kv_full, nb * 64, j * kTile, h, b);
+        for (int n = 0; n < n_iter; ++n) {
+          const int i = i_lo + n;
+          const int st = n % kStages;
+          // the Q stage is free once the dK product of two tiles ago has finished
+          if (n >= kStages) mbar_wait(&sh.q_empty[st], ((n / kStages) - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+          mbar_expect_tx(&sh.q_full[st], kTileBytes);
+          for (int nb = 0; nb < NB; ++nb)
+            tma_load_4d(sQ + st * kTileBytes + nb * 16384, &p.map_q, &sh.q_full[st], nb * 64, i * kTile, h, b);
+          // dO has one buffer: it is free once the dV product of the previous tile has finished, and is not
+          // needed again before the dP^T product of this tile, most of an iteration later
+          if (n >= 1) mbar_wait(&sh.do_empty, (n - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+          mbar_expect_tx(&sh.do_full, kTileBytes);
+          for (int nb = 0; nb < NB; ++nb)
+            tma_load_4d(sDO + nb * 16384, &p.map_do, &sh.do_full, nb * 64, i * kTile, h, b);
+        }
       }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    // Tensor-pipe order per Q tile n:  dV(n), S^T(n+1), dK(n), dQ(n), dP^T(n+1).
-    if (lane == 0 && n_iter > 0) {
-      const uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);     // S^T, dP^T
-      const uint32_t idesc_kv = make_idesc(BF16, 128, DPAD, false, true);    // dV, dK
-      const uint32_t idesc_dq = make_idesc(BF16, 128, DPAD, true, true);     // dQ
-      const uint64_t kmajor = make_sdesc_base(16, 1024);
-      const uint64_t mnmajor = make_sdesc_base(16384, 1024);
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
+    } else if (warp == kMmaWarp) {
+      // ---------------------------------------------------------------- MMA issuer
+      // Tensor-pipe order per Q tile n:  dP^T(n) | dV(n), S^T(n+1) | dK(n), dQ(n).
+      if (lane == 0 && n_iter > 0) {
+        const uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);     // S^T, dP^T
+        const uint32_t idesc_kv = make_idesc(BF16, 128, DPAD, false, true);    // dV, dK
+        const uint32_t idesc_dq = make_idesc(BF16, 128, DPAD, true, true);     // dQ
+        const uint64_t kmajor = make_sdesc_base(16, 1024);
+        const uint64_t mnmajor = make_sdesc_base(16384, 1024);
+        const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS), aDO = smem_u32(sDO);
 
-      auto issue_st = [&](int st) {   // S^T = K Q^T
-        const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
+        auto issue_st = [&](int st) {   // S^T = K Q^T
+          const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
 #pragma unroll
-        for (int kk = 0; kk < DPAD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
-          umma_ss(tmem + kColST, sdesc_at(kmajor, aK + off), sdesc_at(kmajor, aQ + off), idesc_s, kk > 0);
-        }
-        umma_commit(&sh.st_full);
-      };
-      auto issue_dp = [&](int st) {   // dP^T = V dO^T
-        const uint32_t aDO = smem_u32(sDO + st * kTileBytes);
-#pragma unroll
-        for (int kk = 0; kk < DPAD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
-          umma_ss(tmem + kColDP, sdesc_at(kmajor, aV + off), sdesc_at(kmajor, aDO + off), idesc_s, kk > 0);
-        }
-        umma_commit(&sh.dp_full);
-      };
+          for (int kk = 0; kk < DPAD / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
+            umma_ss(tmem + kColST, sdesc_at(kmajor, aK + off), sdesc_at(kmajor, aQ + off), idesc_s, kk > 0);
+          }
+          umma_commit(&sh.st_full);
+        };
 
-      mbar_wait(&sh.kv_full, 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
-      mbar_wait(&sh.q_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
-      tc_fence_after_sync();
-      issue_st(0);
-      mbar_wait(&sh.do_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
-      tc_fence_after_sync();
-      issue_dp(0);
-      for (int n = 0; n < n_iter; ++n) {
-        const int st = n % kStages;
-        const int stn = (n + 1) % kStages;
-        const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
-        const uint32_t aDO = smem_u32(sDO + st * kTileBytes);
-        // dV += P^T dO as soon as P^T is in tensor memory (the compute warps go on to dS meanwhile);
-        // P^T of query columns [64h, 64h+64) sits in S^T columns [64h, 64h+32)
-        mbar_wait(&sh.p_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+        mbar_wait(&sh.kv_full, 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
+        mbar_wait(&sh.q_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
         tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ts(tmem + kColDV, tmem + kColST + (kk >> 2) * 64 + (kk & 3) * 8, sdesc_at(mnmajor, aDO + kk * 2048u),
-                  idesc_kv, n > 0 || kk > 0);
-        // S^T of the next Q tile right behind it (the tensor pipe runs in order, so P^T has been consumed)
-        if (n + 1 < n_iter) {
-          mbar_wait(&sh.q_full[stn], ((n + 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+        issue_st(0);
+        for (int n = 0; n < n_iter; ++n) {
+          const int st = n % kStages;
+          const int stn = (n + 1) % kStages;
+          const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
+          // dP^T = V dO^T as early as possible: it only needs dO and the previous dQ out of its columns
+          mbar_wait(&sh.do_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+          if (n > 0) mbar_wait(&sh.dq_read, (n - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
           tc_fence_after_sync();
-          issue_st(stn);
-        }
-        // dK += dS^T Q and dQ = dS K once dS^T is in shared memory
-        mbar_wait(&sh.ds_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-        tc_fence_after_sync();
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ss(tmem + kColDK, sdesc_at(kmajor, aDS + (kk >> 2) * 16384u + (kk & 3) * 32u),
-                  sdesc_at(mnmajor, aQ + kk * 2048u), idesc_kv, n > 0 || kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ss(tmem + kColDP, sdesc_at(mnmajor, aDS + kk * 2048u), sdesc_at(mnmajor, aK + kk * 2048u), idesc_dq, kk > 0);
-        umma_commit(&sh.dq_full);
-        umma_commit(&sh.q_empty[st]);
-        // dP^T of the next Q tile into the columns dQ is being drained from
-        if (n + 1 < n_iter) {
-          mbar_wait(&sh.do_full[stn], ((n + 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
-          mbar_wait(&sh.dq_read, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+          for (int kk = 0; kk < DPAD / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
+            umma_ss(tmem + kColDP, sdesc_at(kmajor, aV + off), sdesc_at(kmajor, aDO + off), idesc_s, kk > 0);
+          }
+          umma_commit(&sh.dp_full);
+          // dV += P^T dO as soon as P^T is in tensor memory (the compute warps go on to dS meanwhile);
+          // P^T of query columns [64h, 64h+64) sits in S^T columns [64h, 64h+32)
+          mbar_wait(&sh.p_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
           tc_fence_after_sync();
-          issue_dp(stn);
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ts(tmem + kColDV, tmem + kColST + (kk >> 2) * 64 + (kk & 3) * 8, sdesc_at(mnmajor, aDO + kk * 2048u),
+                    idesc_kv, n > 0 || kk > 0);
+          umma_commit(&sh.do_empty);
+          // S^T of the next Q tile right behind it (the tensor pipe runs in order, so P^T has been consumed)
+          if (n + 1 < n_iter) {
+            mbar_wait(&sh.q_full[stn], ((n + 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+            tc_fence_after_sync();
+            issue_st(stn);
+          }
+          // dK += dS^T Q and dQ = dS K once dS^T is in shared memory
+          mbar_wait(&sh.ds_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+          tc_fence_after_sync();
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ss(tmem + kColDK, sdesc_at(kmajor, aDS + (kk >> 2) * 16384u + (kk & 3) * 32u),
+                    sdesc_at(mnmajor, aQ + kk * 2048u), idesc_kv, n > 0 || kk > 0);
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ss(tmem + kColDP, sdesc_at(mnmajor, aDS + kk * 2048u), sdesc_at(mnmajor, aK + kk * 2048u), idesc_dq, kk > 0);
+          umma_commit(&sh.dq_full);
+          umma_commit(&sh.q_empty[st]);
         }
       }
     }
+  } else if (warp >= kDrainWarp0) {
+    // ------------------------------------------------------------------ drain warpgroup: dQ_i out of tensor
+    // memory, through a 32 KB swizzled staging area (two 32-column chunks at a time), into the fp32
+    // accumulator by TMA reduce-add.  Thread t owns query row t of the tile.
+    reg_alloc<kRegsDrain>();
+    const int r = tid - kDrainWarp0 * 32;
+    const uint32_t t_dq = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kColDP;
+    const bool elected = (r == 0);
+    for (int n = 0; n < n_iter; ++n) {
+      const int q_base = (i_lo + n) * kTile;
+      mbar_wait(&sh.dq_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      tc_fence_after_sync();
+      uint32_t dq[kChunks][32];
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) tmem_ld32(t_dq + c * 32, dq[c]);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(&sh.dq_read);
+#pragma unroll
+      for (int rd = 0; rd < kChunks / 2; ++rd) {
+        // the staging area is free once the previous round's reduce has read it
+        if (elected) tma_store_wait_read();
+        named_barrier(3, kTile);
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            *reinterpret_cast<float4*>(sStage + cc * 16384u + swz128(r, g)) =
+                make_float4(__uint_as_float(dq[rd * 2 + cc][4 * g]) * p.scale, __uint_as_float(dq[rd * 2 + cc][4 * g + 1]) * p.scale,
+                            __uint_as_float(dq[rd * 2 + cc][4 * g + 2]) * p.scale, __uint_as_float(dq[rd * 2 + cc][4 * g + 3]) * p.scale);
+        }
+        fence_proxy_async_smem();
+        named_barrier(3, kTile);
+        if (elected) {
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = rd * 2 + cc;
+            if (c * 32 < p.D) tma_reduce_add_4d(&p.map_dq, sStage + cc * 16384u, c * 32, q_base, h, b);
+          }
+          tma_store_commit();
+        }
+      }
+    }
+    if (elected) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ compute warps
+    reg_alloc<kRegsCompute>();
     const int hf = warp >> 2;                            // which half of the query columns / of head_dim
     const int r = (warp & 3) * 32 + lane;                // key row inside the tile (and dQ row when draining)
     const int kv_idx = j * kTile + r;
@@ -249,8 +298,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     const uint32_t t_st = tmem + lane_base + kColST;
     const uint32_t t_dp = tmem + lane_base + kColDP;
     const bool kv_ok = kv_idx < kv_len;
-    const bool elected = (tid == hf * 128);
-    uint8_t* my_ds = sDS + hf * 16384u;                  // this half's dS^T block; also staging of its first dQ chunk
+    uint8_t* my_ds = sDS + hf * 16384u;                  // this half's dS^T block
     float bias = kNegInf;                                // alibi term in log2 units; -inf removes the key row
     if (kv_ok) {
       bias = 0.f;
@@ -272,8 +320,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     for (int n = 0; n < n_iter; ++n) {
       const int i = i_lo + n;
       const int q_base = i * kTile;
-      const int st = n % kStages;
-      // fetch the next tile's statistics now, park them in shared memory later in this iteration
+      // ---- P part: needs S^T only
+      mbar_wait(&sh.st_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      tc_fence_after_sync();
+      // Park this tile's statistics (fetched during the previous tile).  S^T(n) was issued after all 256
+      // compute threads arrived at p_ready(n-1), i.e. after they passed the previous stats_ready wait and
+      // finished the dS part that read the buffer being overwritten.
+      if (hf == 0 && n > 0) {
+        sh.lse2[n & 1][r] = nxt_lse;
+        sh.delta[n & 1][r] = nxt_dlt;
+        mbar_arrive(&sh.stats_ready);
+      }
+      // fetch the next tile's statistics now
       if (hf == 0 && n + 1 < n_iter) {
         const int q_row = q_base + kTile + r;
         const bool q_ok = q_row < p.S_q;
@@ -288,10 +346,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       const bool diag = mods.causal && (q_base < j * kTile + kTile - 1);
       const bool generic = use_mask || mods.drop != nullptr || mods.tri_block > 0;
 
-      // ---- P part: needs S^T only.  P^T (dropped) goes over the first 32 of this half's own 64 S^T
-      // columns, which the half has finished reading by then.
-      mbar_wait(&sh.st_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
-      tc_fence_after_sync();
+      // P^T (dropped) goes over the first 32 of this half's own 64 S^T columns, which the half has
+      // finished reading by then.
       float pr[2][32];
       {
         uint32_t s[2][32];
@@ -357,14 +413,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         uint32_t dp[2][32];
         tmem_ld32(t_dp + (hf * 2) * 32, dp[0]);
         tmem_ld32(t_dp + (hf * 2 + 1) * 32, dp[1]);
-        // the previous tile's dQ staging must have left this half's block (and the dO stage it borrowed)
-        if (n > 0) {
-          if (elected) {
-            tma_store_wait_read();
-            mbar_arrive(&sh.stage_free[(n - 1) % kStages]);
-          }
-          named_barrier(1 + hf, 128);
-        }
         tmem_wait_ld();
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
@@ -404,52 +452,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       fence_proxy_async_smem();
       mbar_arrive(&sh.ds_ready);
 
-      // ---- drain dQ_i: tensor memory -> registers -> swizzled staging -> TMA reduce-add.  Staging of this
-      // half's first 32-column chunk is its dS^T block, of its second chunk the matching block of the dO
-      // stage of this tile; both are dead once dq_full has fired (every product of this tile but none of
-      // the next reads them).
-      mbar_wait(&sh.dq_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
-      tc_fence_after_sync();
-      // Park the next tile's statistics.  dq_full implies that all 256 compute threads have arrived at
-      // ds_ready, hence have passed this tile's stats_ready wait and finished reading the buffer being
-      // overwritten (it held the previous tile's values).
-      if (hf == 0 && n + 1 < n_iter) {
-        sh.lse2[(n + 1) & 1][r] = nxt_lse;
-        sh.delta[(n + 1) & 1][r] = nxt_dlt;
-        mbar_arrive(&sh.stats_ready);
-      }
-      uint32_t dq[kDrainRounds][32];
-#pragma unroll
-      for (int rd = 0; rd < kDrainRounds; ++rd) tmem_ld32(t_dp + (hf * kDrainRounds + rd) * 32, dq[rd]);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(&sh.dq_read);
-#pragma unroll
-      for (int rd = 0; rd < kDrainRounds; ++rd) {
-        uint8_t* stage = rd == 0 ? my_ds : sDO + st * kTileBytes + hf * 16384u;
-#pragma unroll
-        for (int g = 0; g < 8; ++g)
-          *reinterpret_cast<float4*>(stage + swz128(r, g)) =
-              make_float4(__uint_as_float(dq[rd][4 * g]) * p.scale, __uint_as_float(dq[rd][4 * g + 1]) * p.scale,
-                          __uint_as_float(dq[rd][4 * g + 2]) * p.scale, __uint_as_float(dq[rd][4 * g + 3]) * p.scale);
-      }
-      fence_proxy_async_smem();
-      named_barrier(1 + hf, 128);
-      if (elected) {
-#pragma unroll
-        for (int rd = 0; rd < kDrainRounds; ++rd) {
-          const int c = hf * kDrainRounds + rd;          // 32-column chunk of head_dim
-          const uint8_t* stage = rd == 0 ? my_ds : sDO + st * kTileBytes + hf * 16384u;
-          if (c * 32 < p.D) tma_reduce_add_4d(&p.map_dq, stage, c * 32, q_base, h, b);
-        }
-        tma_store_commit();
-      }
     }
-    if (elected) tma_store_wait_all();
 
-    // epilogue: dK (scaled) and dV rows of this tile; each half writes its half of head_dim.  The last
-    // dq_full wait above covered every product.
+    // epilogue: dK (scaled) and dV rows of this tile; each half writes its half of head_dim.
     // (the tensor-memory loads are warp-collective: every lane runs them, only the stores are guarded)
+    if (n_iter > 0) mbar_wait(&sh.dq_full, (n_iter - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
     tc_fence_after_sync();
     const bool row_ok = kv_idx < p.S_k;
     const int64_t row_off = (static_cast<int64_t>(bh) * p.S_k + kv_idx) * p.D;
@@ -459,8 +466,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       const float mul = which == 0 ? p.scale : 1.0f;
       void* out = which == 0 ? p.dk : p.dv;
 #pragma unroll 1
-      for (int cq = 0; cq < kDrainRounds; ++cq) {
-        const int c = hf * kDrainRounds + cq;
+      for (int cq = 0; cq < kChunks / 2; ++cq) {
+        const int c = hf * (kChunks / 2) + cq;
         uint32_t v[32];
         if (n_iter > 0) { tmem_ld32(t_src + c * 32, v); tmem_wait_ld(); }
         else {
@@ -498,7 +505,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   }
 
   __syncthreads();
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);
   }
@@ -554,7 +561,7 @@ __global__ void bwd_convert_kernel(const float* __restrict__ src, void* __restri
 
 cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : 128;
-  const size_t smem = static_cast<size_t>(2 + 2 * kStages) * (dpad / 64) * 16384 + 32768 + sizeof(BwdShared);
+  const size_t smem = static_cast<size_t>(3 + kStages) * (dpad / 64) * 16384 + 2 * 32768 + sizeof(BwdShared);
   dim3 grid((p.S_k + kTile - 1) / kTile, p.B * p.N);
   void (*kern)(const BwdParams) = nullptr;
   if (dpad == 64) kern = bf16 ? fa_bwd_kernel<64, true> : fa_bwd_kernel<64, false>;

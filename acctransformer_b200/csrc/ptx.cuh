@@ -84,6 +84,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ------------------------------------------------------------------------------------------
+// register file re-split between warpgroups (all four warps of a warpgroup must execute the same one)
+// ------------------------------------------------------------------------------------------
+template <int kRegs>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
+// ------------------------------------------------------------------------------------------
 // fences
 // ------------------------------------------------------------------------------------------
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA / tcgen05.mma reads)
