@@ -84,7 +84,9 @@ __device__ __forceinline__ void p_fast(const uint32_t (&s)[32], const float* lse
 
 }  // namespace
 
-template <int DPAD, bool BF16>
+// GENERIC = mask tensor, dropout mask or triangle row groups may be present; the plain instantiation carries
+// none of that code, so its register allocation is not disturbed by it.
+template <int DPAD, bool BF16, bool GENERIC>
 __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_constant__ BwdParams p) {
   constexpr int NB = DPAD / 64;
   constexpr uint32_t kTileBytes = NB * 16384u;   // 128 rows x DPAD 16-bit elements
@@ -344,7 +346,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       const float* dlt = sh.delta[n & 1];
       const bool use_mask = (mods.mask_kind == 1) || (mods.mask_kind == 2 && i == j);
       const bool diag = mods.causal && (q_base < j * kTile + kTile - 1);
-      const bool generic = use_mask || mods.drop != nullptr || mods.tri_block > 0;
+      const bool generic = GENERIC && (use_mask || mods.drop != nullptr || mods.tri_block > 0);
 
       // P^T (dropped) goes over the first 32 of this half's own 64 S^T columns, which the half has
       // finished reading by then.
@@ -365,38 +367,62 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
             for (int e = 0; e < 16; ++e) pk[e] = pack2<BF16>(pr[cc][2 * e], pr[cc][2 * e + 1]);
             tmem_st16(t_st + hf * 64 + cc * 16, pk);
           }
-        } else {
-          // general path: mask tensor, dropout mask, triangle row groups (per-element loads and branches)
+        } else if constexpr (GENERIC) {
+          // general path: mask tensor, dropout mask, triangle row groups.  Loads use clamped (always valid)
+          // addresses so that they carry no branches: whatever they fetch for a key or query that does not
+          // exist is multiplied by a P that is exactly 0 there (bias = -inf / L = +inf).
+          const int kv_c = min(kv_idx, p.S_k - 1);
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
             const int c = hf * 2 + cc;
-            uint32_t pk[16];
-            float pd_prev = 0.f;
+            const int q0 = q_base + c * 32;
+            float add[32];
+            if (use_mask) {
+              if (mods.mask_kind == 1)
+                load_col32(mods.mask, mods.mask_dtype, static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q, q0,
+                           p.S_q - 1, p.S_k, kv_c, -10000.0f * kLog2e, add);
+              else   // the 128 x 128 tile: element (query in tile, key in tile)
+                load_col32(mods.mask, mods.mask_dtype, 0, c * 32, kTile - 1, kTile, r, -10000.0f * kLog2e, add);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) add[e] = 0.f;
+            }
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
-              const int q_row = q_base + c * 32 + e;
-              float x = fmaf(__uint_as_float(s[cc][e]), p.scale_log2, bias);
-              if (use_mask && kv_ok && q_row < p.S_q) {
-                const float mv = mods.mask_kind == 1
-                                     ? load_mask_value(mods.mask, mods.mask_dtype,
-                                                       (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q + q_row) * p.S_k + kv_idx)
-                                     : load_mask_value(mods.mask, mods.mask_dtype, static_cast<int64_t>(c * 32 + e) * kTile + r);
-                x += mv * (-10000.0f * kLog2e);
-              }
-              float pv = ex2(x - lse2[c * 32 + e]);
-              if (diag && kv_idx > q_row) pv = 0.f;
-              if (mods.tri_block > 0 && kv_idx >= (min(q_row, p.S_q - 1) / mods.tri_block + 1) * mods.tri_block) pv = 0.f;
+              float pv = ex2(fmaf(__uint_as_float(s[cc][e]), p.scale_log2, bias) + add[e] - lse2[c * 32 + e]);
+              if (diag) pv = (kv_idx > q0 + e) ? 0.f : pv;
               pr[cc][e] = pv;
-              float pd = pv;
-              if (mods.drop != nullptr) {
-                float fac = 0.f;
-                if (kv_ok && q_row < p.S_q)
-                  fac = load_mask_value(mods.drop, mods.drop_dtype,
-                                        (static_cast<int64_t>(bh) * p.S_q + q_row) * p.S_k + kv_idx) * mods.drop_scale;
-                pd = pv * fac;
+            }
+            if (mods.tri_block > 0) {
+              // first key that does not exist for query q0 + e: end of its row group
+              const int g0 = q0 / mods.tri_block;
+              const int rem0 = q0 - g0 * mods.tri_block;
+              const int end0 = (g0 + 1) * mods.tri_block;
+              if (mods.tri_block >= 32) {      // at most one group boundary inside the 32 queries
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                  const int lim = rem0 + e < mods.tri_block ? end0 : end0 + mods.tri_block;
+                  pr[cc][e] = kv_idx >= lim ? 0.f : pr[cc][e];
+                }
+              } else {
+#pragma unroll   // (static indices keep the probabilities in registers)
+                for (int e = 0; e < 32; ++e) {
+                  const int lim = ((q0 + e) / mods.tri_block + 1) * mods.tri_block;
+                  pr[cc][e] = kv_idx >= lim ? 0.f : pr[cc][e];
+                }
               }
-              if (e & 1) pk[e >> 1] = pack2<BF16>(pd_prev, pd);
-              else pd_prev = pd;
+            }
+            uint32_t pk[16];
+            if (mods.drop != nullptr) {
+              float fac[32];
+              load_col32(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q0, p.S_q - 1, p.S_k, kv_c,
+                         mods.drop_scale, fac);
+#pragma unroll
+              for (int e = 0; e < 16; ++e)
+                pk[e] = pack2<BF16>(pr[cc][2 * e] * fac[2 * e], pr[cc][2 * e + 1] * fac[2 * e + 1]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) pk[e] = pack2<BF16>(pr[cc][2 * e], pr[cc][2 * e + 1]);
             }
             tmem_st16(t_st + hf * 64 + cc * 16, pk);
           }
@@ -418,7 +444,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         for (int cc = 0; cc < 2; ++cc) {
           const int c = hf * 2 + cc;
           uint32_t dk_[16];
-          if (mods.drop == nullptr) {
+          if (!GENERIC || mods.drop == nullptr) {
 #pragma unroll
             for (int e4 = 0; e4 < 8; ++e4) {
               const float4 Dl = *reinterpret_cast<const float4*>(dlt + c * 32 + 4 * e4);
@@ -429,18 +455,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
               dk_[2 * e4] = pack2<BF16>(d0, d1);
               dk_[2 * e4 + 1] = pack2<BF16>(d2, d3);
             }
-          } else {
-            float ds_prev = 0.f;
+          } else if constexpr (GENERIC) {
+            float fac[32];
+            load_col32(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q_base + c * 32, p.S_q - 1, p.S_k,
+                       min(kv_idx, p.S_k - 1), mods.drop_scale, fac);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int q_row = q_base + c * 32 + e;
-              float fac = 0.f;
-              if (kv_ok && q_row < p.S_q)
-                fac = load_mask_value(mods.drop, mods.drop_dtype,
-                                      (static_cast<int64_t>(bh) * p.S_q + q_row) * p.S_k + kv_idx) * mods.drop_scale;
-              const float ds = pr[cc][e] * (__uint_as_float(dp[cc][e]) * fac - dlt[c * 32 + e]);
-              if (e & 1) dk_[e >> 1] = pack2<BF16>(ds_prev, ds);
-              else ds_prev = ds;
+            for (int e = 0; e < 16; ++e) {
+              const float d0 = pr[cc][2 * e] * (__uint_as_float(dp[cc][2 * e]) * fac[2 * e] - dlt[c * 32 + 2 * e]);
+              const float d1 = pr[cc][2 * e + 1] * (__uint_as_float(dp[cc][2 * e + 1]) * fac[2 * e + 1] - dlt[c * 32 + 2 * e + 1]);
+              dk_[e] = pack2<BF16>(d0, d1);
             }
           }
 #pragma unroll
@@ -563,9 +586,15 @@ cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : 128;
   const size_t smem = static_cast<size_t>(3 + kStages) * (dpad / 64) * 16384 + 2 * 32768 + sizeof(BwdShared);
   dim3 grid((p.S_k + kTile - 1) / kTile, p.B * p.N);
+  const bool generic = p.mods.mask_kind != 0 || p.mods.drop != nullptr || p.mods.tri_block > 0;
   void (*kern)(const BwdParams) = nullptr;
-  if (dpad == 64) kern = bf16 ? fa_bwd_kernel<64, true> : fa_bwd_kernel<64, false>;
-  else kern = bf16 ? fa_bwd_kernel<128, true> : fa_bwd_kernel<128, false>;
+  if (dpad == 64) {
+    if (generic) kern = bf16 ? fa_bwd_kernel<64, true, true> : fa_bwd_kernel<64, false, true>;
+    else kern = bf16 ? fa_bwd_kernel<64, true, false> : fa_bwd_kernel<64, false, false>;
+  } else {
+    if (generic) kern = bf16 ? fa_bwd_kernel<128, true, true> : fa_bwd_kernel<128, false, true>;
+    else kern = bf16 ? fa_bwd_kernel<128, true, false> : fa_bwd_kernel<128, false, false>;
+  }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   kern<<<grid, kBwdThreads, smem, stream>>>(p);

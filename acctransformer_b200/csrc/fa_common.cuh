@@ -37,4 +37,107 @@ __device__ __forceinline__ float load_mask_value(const void* base, int dtype, in
   return __half2float(reinterpret_cast<const __half*>(base)[idx]);
 }
 
+// 32 consecutive values (elements idx0 .. idx0+31 of a u8 / f16 / bf16 array) as floats, times `mul`.
+// `vec` (uniform): idx0 is a multiple of 16 elements and all 32 elements exist, so 128-bit loads are used;
+// otherwise element loads, with elements at or past `n_valid` read as 0.
+__device__ __forceinline__ void load_row32(const void* base, int dtype, int64_t idx0, int n_valid, bool vec, float mul,
+                                           float (&out)[32]) {
+  if (vec) {
+    if (dtype == 2 /*U8*/) {
+      const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(base) + idx0);
+#pragma unroll
+      for (int v = 0; v < 2; ++v) {
+        const uint4 u = p[v];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+          for (int bb = 0; bb < 4; ++bb) out[v * 16 + k * 4 + bb] = static_cast<float>((w[k] >> (8 * bb)) & 0xffu) * mul;
+      }
+    } else {
+      const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + idx0);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const uint4 u = p[v];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float lo, hi;
+          if (dtype == 1 /*BF16*/) {
+            lo = __uint_as_float(w[k] << 16);
+            hi = __uint_as_float(w[k] & 0xffff0000u);
+          } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+            lo = f.x;
+            hi = f.y;
+          }
+          out[v * 8 + k * 2] = lo * mul;
+          out[v * 8 + k * 2 + 1] = hi * mul;
+        }
+      }
+    }
+  } else {
+    // element loads from clamped (always valid) addresses, all issued before the first conversion
+    const int last = max(n_valid, 1) - 1;
+    if (dtype == 2 /*U8*/) {
+      const uint8_t* p = reinterpret_cast<const uint8_t*>(base) + idx0;
+      uint8_t raw[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) raw[i] = p[min(i, last)];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) out[i] = i < n_valid ? static_cast<float>(raw[i]) * mul : 0.f;
+    } else {
+      const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + idx0;
+      uint16_t raw[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) raw[i] = p[min(i, last)];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float f = dtype == 1 ? __uint_as_float(static_cast<uint32_t>(raw[i]) << 16) : __half2float(__ushort_as_half(raw[i]));
+        out[i] = i < n_valid ? f * mul : 0.f;
+      }
+    }
+  }
+}
+
+// 32 values taken down a column of a row-major u8 / f16 / bf16 matrix: element (row_base + min(row0 + e, row_max),
+// col) for e = 0..31, as floats times `mul`.  The element-type switch sits outside the loops and all 32 loads
+// are issued before the first conversion, so that their latencies overlap.
+__device__ __forceinline__ void load_col32(const void* base, int dtype, int64_t row_base, int row0, int row_max,
+                                           int64_t row_stride, int col, float mul, float (&out)[32]) {
+  if (dtype == 2 /*U8*/) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(base) + col;
+    uint8_t raw[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) raw[e] = p[(row_base + min(row0 + e, row_max)) * row_stride];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) out[e] = static_cast<float>(raw[e]) * mul;
+  } else {
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + col;
+    uint16_t raw[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) raw[e] = p[(row_base + min(row0 + e, row_max)) * row_stride];
+    if (dtype == 1 /*BF16*/) {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) out[e] = __uint_as_float(static_cast<uint32_t>(raw[e]) << 16) * mul;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) out[e] = __half2float(__ushort_as_half(raw[e])) * mul;
+    }
+  }
+}
+
+// 2^x on the FMA pipe (for x <= ~1): round-to-nearest split x = n + f, degree-3 minimax polynomial for 2^f on
+// [-0.5, 0.5] (relative error 7.5e-5, far below the 16-bit rounding P gets afterwards), then n added to the
+// exponent field.  Takes load off the 16-lane transcendental unit.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float t = x + 12582912.0f;                 // 1.5 * 2^23: n lands in the low mantissa bits
+  const float f = x - (t - 12582912.0f);
+  float p = fmaf(0.0551716648f, f, 0.2426111251f);
+  p = fmaf(p, f, 0.6932609677f);
+  p = fmaf(p, f, 0.9999280572f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 }  // namespace acct

@@ -69,11 +69,14 @@ struct FwdShared {
   uint64_t s_full[2], p_ready[2], o_done[2];
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
+  alignas(16) float alibi[2][2][kTile];   // [softmax group][tile parity]: alibi row of the K/V tile, log2 units
 };
 
 }  // namespace
 
-template <int DPAD, bool BF16>
+// GENERIC = a mask tensor, alibi or a dropout mask may be present; the plain instantiation carries none of
+// that code, so its register allocation is not disturbed by it.
+template <int DPAD, bool BF16, bool GENERIC>
 __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_constant__ FwdParams p) {
   constexpr int NB = DPAD / 64;                 // 64-column (128-byte) blocks per row
   constexpr uint32_t kTileBytes = NB * 16384u;  // one 128-row tile
@@ -246,8 +249,62 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       tc_fence_after_sync();
       const int col_base = j * kTile;
       const bool use_mask = (mods.mask_kind == 1) || (mods.mask_kind == 2 && j == q_tile);
-      const bool generic = use_mask || has_alibi;
+      const bool generic = GENERIC && (use_mask || has_alibi);
       const bool partial = col_base + kTile > bound_tile;   // some (row, key) pairs of this tile do not exist
+
+      float mult = p.scale_log2;
+      if constexpr (GENERIC) if (generic) {
+        // general path: alibi and / or a mask tensor; values leave in log2 units
+        mult = 1.0f;
+        // the alibi row of this K/V tile goes through shared memory: one value per thread of the group,
+        // double-buffered by tile parity so that one barrier per tile is enough
+        float* al = sh.alibi[qt][n & 1];
+        if (mods.alibi != nullptr) {
+          const int col = col_base + row_in_tile;
+          al[row_in_tile] = col < p.S_k ? load16<BF16>(mods.alibi, alibi_row + col) * kLog2e : 0.f;
+          named_barrier(1 + qt, 128);
+        }
+        // mask values are read 32 at a time (128-bit loads when the row segment is aligned and complete)
+        const bool mask_vec = col_base + kTile <= p.S_k && (p.S_k & 15) == 0 &&
+                              (reinterpret_cast<uintptr_t>(mods.mask) & 15u) == 0;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {   // one 32-column chunk at a time, rewritten in place in tensor memory
+          uint32_t sc[32];
+          tmem_ld32(t_s + c * 32, sc);
+          float add[32];
+          if (use_mask) {
+            if (mods.mask_kind == 1)
+              load_row32(mods.mask, mods.mask_dtype, mask_row + col_base + c * 32, p.S_k - (col_base + c * 32), mask_vec,
+                         -10000.0f * kLog2e, add);
+            else
+              load_row32(mods.mask, mods.mask_dtype, static_cast<int64_t>(row_in_tile) * kTile + c * 32, 32,
+                         (reinterpret_cast<uintptr_t>(mods.mask) & 15u) == 0, -10000.0f * kLog2e, add);
+          }
+          else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) add[i] = 0.f;
+          }
+          // the branches are on tile-uniform conditions and sit outside the element loops
+          if (mods.alibi != nullptr) {
+#pragma unroll
+            for (int i4 = 0; i4 < 8; ++i4) {
+              const float4 a4 = *reinterpret_cast<const float4*>(al + c * 32 + 4 * i4);
+              add[4 * i4] += a4.x; add[4 * i4 + 1] += a4.y; add[4 * i4 + 2] += a4.z; add[4 * i4 + 3] += a4.w;
+            }
+          } else if (mods.alibi_slopes != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) add[i] = fmaf(slope_l2, static_cast<float>(col_base + c * 32 + i), add[i]);
+          }
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float x = fmaf(__uint_as_float(sc[i]), p.scale_log2, add[i]);
+            sc[i] = __float_as_uint(col_base + c * 32 + i >= bound ? kNegInf : x);
+          }
+          tmem_st32(t_s + c * 32, sc);
+        }
+        tmem_wait_st();
+      }
 
       // the whole score row in registers, one wait
       uint32_t s[4][32];
@@ -255,31 +312,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
       tmem_wait_ld();
 
-      float mult = p.scale_log2;
-      if (generic) {
-        // general path: alibi and / or a mask tensor (per-element loads); values leave in log2 units
-        mult = 1.0f;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {   // unrolled: the score row must stay in registers
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = col_base + c * 32 + i;
-            float x = __uint_as_float(s[c][i]) * p.scale_log2;
-            if (col < kv_len) {
-              if (mods.alibi != nullptr) x += load16<BF16>(mods.alibi, alibi_row + col) * kLog2e;
-              else if (mods.alibi_slopes != nullptr) x += slope_l2 * static_cast<float>(col);
-              if (use_mask) {
-                const float mv = mods.mask_kind == 1
-                                     ? load_mask_value(mods.mask, mods.mask_dtype, mask_row + col)
-                                     : load_mask_value(mods.mask, mods.mask_dtype,
-                                                       static_cast<int64_t>(row_in_tile) * kTile + (col - col_base));
-                x += mv * (-10000.0f * kLog2e);
-              }
-            }
-            s[c][i] = __float_as_uint(col >= bound ? kNegInf : x);
-          }
-        }
-      } else if (partial) {
+      if (!generic && partial) {
         // only positions that do not exist: one compare + select per element, no branches
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -331,15 +364,14 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
           pr[i] = ex2(fmaf(__uint_as_float(s[c][i]), mult, -m_use));
           l_part[i & 3] += pr[i];
         }
-        if (mods.drop != nullptr) {
+        if constexpr (GENERIC) if (mods.drop != nullptr) {
           const int col0 = col_base + c * 32;
+          const bool drop_vec = col_base + kTile <= p.S_k && (p.S_k & 15) == 0 &&
+                                (reinterpret_cast<uintptr_t>(mods.drop) & 15u) == 0;
+          float f[32];
+          load_row32(mods.drop, mods.drop_dtype, drop_row + col0, p.S_k - col0, drop_vec, mods.drop_scale, f);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = col0 + i;
-            float f = 0.f;
-            if (col < p.S_k) f = load_mask_value(mods.drop, mods.drop_dtype, drop_row + col) * mods.drop_scale;
-            pr[i] *= f;
-          }
+          for (int i = 0; i < 32; ++i) pr[i] *= f[i];
         }
         uint32_t pk[16];
 #pragma unroll
@@ -409,9 +441,16 @@ cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(2 + 2 * kStages) * (dpad / 64) * 16384 + 1024;
   const int n_pairs = (p.S_q + 2 * kTile - 1) / (2 * kTile);
   dim3 grid(static_cast<unsigned>(n_pairs) * static_cast<unsigned>(p.B * p.N));
+  const bool generic = p.mods.mask_kind != 0 || p.mods.alibi != nullptr || p.mods.alibi_slopes != nullptr ||
+                       p.mods.drop != nullptr;
   void (*kern)(const FwdParams) = nullptr;
-  if (dpad == 64) kern = bf16 ? fa_fwd_kernel<64, true> : fa_fwd_kernel<64, false>;
-  else kern = bf16 ? fa_fwd_kernel<128, true> : fa_fwd_kernel<128, false>;
+  if (dpad == 64) {
+    if (generic) kern = bf16 ? fa_fwd_kernel<64, true, true> : fa_fwd_kernel<64, false, true>;
+    else kern = bf16 ? fa_fwd_kernel<64, true, false> : fa_fwd_kernel<64, false, false>;
+  } else {
+    if (generic) kern = bf16 ? fa_fwd_kernel<128, true, true> : fa_fwd_kernel<128, false, true>;
+    else kern = bf16 ? fa_fwd_kernel<128, true, false> : fa_fwd_kernel<128, false, false>;
+  }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   kern<<<grid, kFwdThreads, smem, stream>>>(p);

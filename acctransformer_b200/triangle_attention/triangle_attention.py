@@ -61,8 +61,9 @@ class TriangleAttention(torch.nn.Module):
                                     generator=self.generator) < self.keep_prob).to(torch.uint8)
         # tri_block: a query row in group g sees keys [0, (g+1)*block_size) only, as in the reference's slices;
         # inside that range the mask tensor decides (or the in-kernel triangle when assume_causal).
+        # (under the in-kernel triangle the group bound excludes nothing more, so it is not passed)
         cfg = dict(prev_block_num=65536, next_block_num=65536, scale=1.0, causal=self.assume_causal,
-                   keep_prob=self.keep_prob, tri_block=self.block_size)
+                   keep_prob=self.keep_prob, tri_block=0 if self.assume_causal else self.block_size)
         mask = None if self.assume_causal else attention_mask
         out, _ = _FlashAttentionFunction.apply(query, key, value, mask, drop_mask, None, cfg)
         return out
