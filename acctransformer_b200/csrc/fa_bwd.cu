@@ -7,7 +7,7 @@
 //   S^T  = K_j Q_i^T          (tcgen05, both operands K-major from shared memory)
 //   dP^T = V_j dO_i^T
 //   P^T  = exp2(S^T*scale*log2e - L_i*log2e);  dS^T = P^T * (dP^T * M - D_i)        (registers)
-//   dK  += dS^T Q_i           (A = dS^T from shared memory, K-major; B = Q_i, MN-major)
+//   dK  += dS^T Q_i           (A = dS^T from tensor memory, written over dP^T; B = Q_i, MN-major)
 //   dQ_i = dS K_j             (A = the same dS^T tile read MN-major; B = K_j, MN-major) -> over dP^T
 //   dV  += (P^T*M) dO_i       (A from tensor memory, written over S^T; B = dO_i, MN-major)
 // Warp roles (four warpgroups, registers re-split between them with setmaxnreg): warps 0-7 compute
@@ -235,9 +235,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
           mbar_wait(&sh.ds_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
           tc_fence_after_sync();
 #pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ss(tmem + kColDK, sdesc_at(kmajor, aDS + (kk >> 2) * 16384u + (kk & 3) * 32u),
-                    sdesc_at(mnmajor, aQ + kk * 2048u), idesc_kv, n > 0 || kk > 0);
+          for (int kk = 0; kk < kTile / 16; ++kk)   // dK: A = dS^T packed over the dP^T columns, like P^T over S^T
+            umma_ts(tmem + kColDK, tmem + kColDP + (kk >> 2) * 64 + (kk & 3) * 8, sdesc_at(mnmajor, aQ + kk * 2048u),
+                    idesc_kv, n > 0 || kk > 0);
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk)
             umma_ss(tmem + kColDP, sdesc_at(mnmajor, aDS + kk * 2048u), sdesc_at(mnmajor, aK + kk * 2048u), idesc_dq, kk > 0);
@@ -466,13 +466,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
               dk_[e] = pack2<BF16>(d0, d1);
             }
           }
+          // dS^T goes to two places: over the first 32 of this half's own 64 dP^T columns (both chunks of which
+          // are in registers by now), as the A operand of the dK product, and into shared memory, from where the
+          // dQ product reads it transposed.  (An A operand in tensor memory runs about a third faster than one in
+          // shared memory next to an MN-major B operand.)
+          tmem_st16(t_dp + hf * 64 + cc * 16, dk_);
 #pragma unroll
           for (int g = 0; g < 4; ++g)
             *reinterpret_cast<uint4*>(my_ds + swz128(r, cc * 4 + g)) =
                 make_uint4(dk_[4 * g], dk_[4 * g + 1], dk_[4 * g + 2], dk_[4 * g + 3]);
         }
       }
+      tmem_wait_st();
       fence_proxy_async_smem();
+      tc_fence_before_sync();
       mbar_arrive(&sh.ds_ready);
 
     }

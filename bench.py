@@ -18,7 +18,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -41,6 +40,7 @@ def parse_args():
     ap.add_argument("--no-decode", action="store_true", help="skip the decode HBM measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-aux", action="store_true", help="skip the other configurations (2, 3, 4, 5a)")
     return ap.parse_args()
 
 
@@ -108,51 +108,60 @@ def run_reference(args):
 # clocks
 # ----------------------------------------------------------------------------------------------
 class ClockSampler:
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) every few milliseconds in a
+    thread, so that even a timed region of tens of milliseconds gets samples taken under load."""
 
-    def __init__(self, index):
+    def __init__(self, index, period_s=0.004):
         self.rows = []
-        self.proc = None
+        self.stop_flag = False
+        self.err = None
+        self.thread = None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.period = period_s
+            self.thread = threading.Thread(target=self._run, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception as e:      # no NVML: report that instead of a number
+            self.err = f"NVML unavailable: {e}"
 
-    def _read(self):
-        for ln in self.proc.stdout:
-            self.rows.append((time.perf_counter(), ln.strip()))
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.rows.append((time.perf_counter(), mhz, reasons))
+            except Exception as e:
+                self.err = str(e)
+                return
+            time.sleep(self.period)
 
     def stop(self, t0, t1):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], None, set()
-        rows = [r for (t, r) in self.rows if t0 <= t <= t1] or [r for (_, r) in self.rows[-3:]]
-        for r in rows:
-            f = [x.strip() for x in r.split(",")]
-            if len(f) < 7:
-                continue
-            try:
-                sm.append(float(f[0]))
-                mx = float(f[1])
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        if self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.err or "no samples"]}
+        self.stop_flag = True
+        self.thread.join(timeout=2)
+        nv = self.nv
+        rows = [r for r in self.rows if t0 <= r[0] <= t1]
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        seen = set()
+        for _, _, bits in rows:
+            for name, bit in names.items():
+                if bits & bit:
+                    seen.add(name)
+        mhz = [r[1] for r in rows]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_min_mhz": min(mhz) if mhz else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(seen), "samples": len(mhz)}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -217,17 +226,19 @@ def run_ours(args):
 
     for _ in range(max(3, args.warmup)):
         step()
+    # clocks are sampled over the timed steps and the two per-kernel legs that follow them (same kernels, same
+    # inputs), so that a run of a few tens of milliseconds still yields several samples under load
     sampler = ClockSampler(local_rank) if rank == 0 else None
     t0 = time.perf_counter()
     ms_step = timed(step, args.steps)
-    t1 = time.perf_counter()
-    clocks = sampler.stop(t0, t1) if sampler else None
     _lib.device_status()
 
     # per-kernel legs for the roofline (same inputs, same stream)
     ms_fwd = timed(fwd, args.steps)
     o, lse = fwd()
     ms_bwd = timed(lambda: bwd(o, lse), args.steps)
+    t1 = time.perf_counter()
+    clocks = sampler.stop(t0, t1) if sampler else None
 
     if world > 1:
         t = torch.tensor([ms_step, ms_fwd, ms_bwd], device=dev, dtype=torch.float64)
@@ -284,11 +295,15 @@ def run_ours(args):
     decode = None
     if not args.no_decode and rank == 0:
         decode = bench_decode(torch, ops, dev, peaks)
+    other = None
+    if not args.no_aux and rank == 0 and world == 1 and args.workload == "H":
+        other = bench_other_configs(torch, ops, dev, peaks)
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp16", "data": "synthetic", "config": workload_config(args.workload),
-            "roofline": roofline, "e2e": e2e, "gpu_launches": 4 * args.steps, "clocks": clocks, "decode": decode}
+            "roofline": roofline, "e2e": e2e, "gpu_launches": 4 * args.steps, "clocks": clocks, "decode": decode,
+            "other_configs": other}
     if rank == 0:
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"], _ = cpu_baseline(args.workload)
@@ -297,6 +312,54 @@ def run_ours(args):
         dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+def bench_other_configs(torch, ops, dev, peaks):
+    """The remaining benchmark configurations at full size, forward and backward, as algorithmic TFLOP/s
+    (informational: the headline metric is quoted on workload H)."""
+    from acctransformer_b200.workloads import CONFIGS, fwd_flops, make_inputs
+
+    def t(fn, iters):
+        for _ in range(2):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    out = {}
+    for name in ("cfg2", "cfg3", "cfg4", "cfg5a"):
+        inp = make_inputs(name, dev)
+        cfg = inp["cfg"]
+        q, k, v = inp["q"], inp["k"], inp["v"]
+        kw, mask, what = dict(scale=inp["scale"]), None, ""
+        if name == "cfg2":
+            kw.update(causal=True, alibi=inp["alibi"]); what = "fp16 causal + alibi tensor B=4 N=16 S=2048"
+        elif name == "cfg3":
+            kw.update(dropout_mask=inp["dropout_mask"], keep_prob=0.9, prev_block_num=4, next_block_num=4)
+            what = "bf16 band prev=next=4 + uint8 dropout mask B=2 N=32 S=8192"
+        elif name == "cfg4":
+            mask = inp["attn_mask"]; kw.update(tri_block=cfg["block_size"], scale=1.0)
+            what = "fp16 TriangleAttention block 512, [B,S,S] fp16 mask tensor read, B=8 N=32 S=4096"
+        else:
+            kw.update(causal=True); what = "fp16 causal prefill B=8 N=32 S=4096 (forward only)"
+        fl = fwd_flops(cfg)
+        o, lse = ops.fa_forward(q, k, v, mask, **kw)
+        ms_f = t(lambda: ops.fa_forward(q, k, v, mask, **kw), 5)
+        rec = {"workload": what, "fwd_ms": ms_f, "fwd_tflops": fl / ms_f / 1e9}
+        if "do" in inp:
+            do = inp["do"]
+            ms_b = t(lambda: ops.fa_backward(q, k, v, o, lse, do, mask, **kw), 3)
+            rec.update(bwd_ms=ms_b, bwd_tflops=2.5 * fl / ms_b / 1e9, fwd_bwd_tflops=3.5 * fl / (ms_f + ms_b) / 1e9,
+                       frac_of_sustained=3.5 * fl / (ms_f + ms_b) / 1e9 / peaks["tflops"])
+        out[name] = rec
+        del inp, q, k, v, o, lse
+        torch.cuda.empty_cache()
+    return out
 
 
 def bench_decode(torch, ops, dev, peaks):
