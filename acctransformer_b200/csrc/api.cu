@@ -283,8 +283,10 @@ int acct_fa_fwd(const acct_fa_args* a, void* stream) {
 size_t acct_fa_bwd_workspace_bytes(const acct_fa_args* a) {
   if (a == nullptr || a->B <= 0 || a->N <= 0 || a->S_q <= 0 || a->D <= 0) return 0;
   const size_t rows = static_cast<size_t>(a->B) * a->N * a->S_q;
-  // delta [rows] fp32 (padded to 256 bytes) + dQ accumulator [rows, D] fp32
-  return ((rows * 4 + 255) / 256) * 256 + rows * static_cast<size_t>(a->D) * 4;
+  const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile);
+  // delta [rows] fp32 | turn counters of the ordered dQ reduction [B*N*ceil(S_q/128)] u32 | dQ accumulator
+  // [rows, D] fp32; the first two padded to 256 bytes
+  return ((rows * 4 + 255) / 256) * 256 + ((q_tiles * 4 + 255) / 256) * 256 + rows * static_cast<size_t>(a->D) * 4;
 }
 
 int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
@@ -305,7 +307,10 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   const bool bf16 = a->dtype == ACCT_BF16;
   const size_t rows = static_cast<size_t>(a->B) * a->N * a->S_q;
   float* delta = static_cast<float*>(g->workspace);
-  float* dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(g->workspace) + ((rows * 4 + 255) / 256) * 256);
+  const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile);
+  const size_t order_bytes = ((q_tiles * 4 + 255) / 256) * 256;
+  unsigned int* dq_order = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(g->workspace) + ((rows * 4 + 255) / 256) * 256);
+  float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dq_order) + order_bytes);
 
   BwdParams p;
   memset(&p, 0, sizeof(p));
@@ -321,11 +326,13 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   t.strides[2] = static_cast<int64_t>(a->N) * a->S_q * a->D;
   if ((rc = make_tmap_4d(&p.map_dq, t, kTile))) return rc;
 
-  cudaError_t e = cudaMemsetAsync(dq_acc, 0, rows * static_cast<size_t>(a->D) * 4, s);
+  // one zero-fill covers the turn counters and the accumulator behind them
+  cudaError_t e = cudaMemsetAsync(dq_order, 0, order_bytes + rows * static_cast<size_t>(a->D) * 4, s);
   if (e != cudaSuccess) return fail_cuda(e, "zero-filling the dQ accumulator");
   e = launch_bwd_delta(a->o, g->d_o, delta, static_cast<int64_t>(rows), a->D, st.o[0], st.o[1], st.o[2], a->N, a->S_q, bf16, s);
   if (e != cudaSuccess) return fail_cuda(e, "launching the row-sum kernel");
   p.lse = a->lse; p.delta = delta; p.dq_acc = dq_acc;
+  p.dq_order = (a->flags & ACCT_FLAG_DETERMINISTIC) ? dq_order : nullptr;
   p.dk = g->dk; p.dv = g->dv;
   p.grads_f32 = (a->flags & ACCT_FLAG_GRAD_F32) ? 1 : 0;
   p.B = a->B; p.N = a->N; p.S_q = a->S_q; p.S_k = a->S_k; p.D = a->D;

@@ -280,12 +280,37 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         fence_proxy_async_smem();
         named_barrier(3, kTile);
         if (elected) {
+          if (p.dq_order != nullptr && rd == 0) {
+            // Fixed summation order for dQ (opt-in): the K/V tiles that touch Q tile i add their parts in
+            // descending tile order, which is the order in which they naturally reach tile i under a causal
+            // mask.  j_top is the last K/V tile that touches tile i: it inverts the Q-tile range above.
+            const int i = i_lo + n;
+            int j_top = (kv_len + kTile - 1) / kTile - 1;
+            if (mods.next_block_num < 65536) j_top = min(j_top, i + mods.next_block_num);
+            if (mods.causal) j_top = min(j_top, i);
+            if (mods.tri_block > 0) j_top = min(j_top, (((i * kTile + kTile - 1) / mods.tri_block + 1) * mods.tri_block - 1) / kTile);
+            const unsigned int my_turn = static_cast<unsigned int>(j_top - j);
+            const unsigned int* slot = p.dq_order + static_cast<int64_t>(bh) * ((p.S_q + kTile - 1) / kTile) + i;
+            const long long t0 = clock64();
+            unsigned int seen;
+            while (true) {
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(slot) : "memory");
+              if (seen >= my_turn || *abort_flag != 0u) break;
+              if (clock64() - t0 > kWaitCycleLimit) { *abort_flag = 1u; atomicMax(p.status, DEV_TIMEOUT_SYNC); break; }
+            }
+          }
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
             const int c = rd * 2 + cc;
             if (c * 32 < p.D) tma_reduce_add_4d(&p.map_dq, sStage + cc * 16384u, c * 32, q_base, h, b);
           }
           tma_store_commit();
+          if (p.dq_order != nullptr && rd == kChunks / 2 - 1) {
+            // pass the turn on once this tile's additions have been performed
+            tma_store_wait_all();
+            unsigned int* slot = p.dq_order + static_cast<int64_t>(bh) * ((p.S_q + kTile - 1) / kTile) + (i_lo + n);
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(slot) : "memory");
+          }
         }
       }
     }

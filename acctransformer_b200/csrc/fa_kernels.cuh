@@ -42,6 +42,7 @@ struct alignas(64) BwdParams {
   const float* lse;                 // [B,N,S_q]
   const float* delta;               // [B,N,S_q]  rowsum(dO * O)
   float* dq_acc;                    // [B,N,S_q,D] fp32, zeroed before launch
+  unsigned int* dq_order;           // [B,N,ceil(S_q/128)] turn counters, zeroed before launch; nullptr = any order
   void* dk;
   void* dv;
   int grads_f32;

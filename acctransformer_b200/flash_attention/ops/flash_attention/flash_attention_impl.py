@@ -37,8 +37,10 @@ def _is_tile_mask(attn_mask):
 
 
 def get_flash_attention_grad(prev_block_num=65536, next_block_num=65536, tiling_stgy_name='sparse',
-                             scale=1.0, causal=False):
-    """Returns the grad primitive (fp32 dq, dk, dv)."""
+                             scale=1.0, causal=False, deterministic=False):
+    """Returns the grad primitive (fp32 dq, dk, dv).  ``deterministic`` makes dq bit-reproducible from run to
+    run (the reference's tests require that of its gradients, tests/train/flash_attention/st/test_sharding.py:91-115)
+    at some cost in speed; dk and dv always are."""
 
     def fa_grad(query, key, value, output, do, rowsum, attn_mask=None, dropout_mask=None, alibi_mask=None,
                 keep_prob=1.0, grads_fp32=True):
@@ -46,7 +48,7 @@ def get_flash_attention_grad(prev_block_num=65536, next_block_num=65536, tiling_
                                 mask_tile128=_is_tile_mask(attn_mask), causal=causal,
                                 dropout_mask=dropout_mask, keep_prob=keep_prob, alibi=alibi_mask,
                                 prev_block_num=prev_block_num, next_block_num=next_block_num, scale=scale,
-                                grads_fp32=grads_fp32)
+                                grads_fp32=grads_fp32, deterministic=deterministic)
 
     fa_grad.prev_block_num = prev_block_num
     fa_grad.next_block_num = next_block_num
@@ -84,18 +86,18 @@ class _FlashAttentionFunction(torch.autograd.Function):
             mask_tile128=_is_tile_mask(attn_mask), causal=cfg["causal"], dropout_mask=dropout_mask,
             keep_prob=cfg["keep_prob"], alibi=alibi_mask, prev_block_num=cfg["prev_block_num"],
             next_block_num=cfg["next_block_num"], scale=cfg["scale"], grads_fp32=False,
-            tri_block=cfg.get("tri_block", 0))
+            tri_block=cfg.get("tri_block", 0), deterministic=cfg.get("deterministic", False))
         return dq, dk, dv, None, None, None, None
 
 
 def get_flash_attention(prev_block_num=65536, next_block_num=65536, tiling_stgy_name='sparse',
-                        scale=1.0, causal=False):
+                        scale=1.0, causal=False, deterministic=False):
     """Returns the forward primitive.  ``scale`` (default 1: the raw primitive) and ``causal``
     (an in-kernel triangle that needs no mask tensor) are this library's additions."""
 
     def fa_forward(query, key, value, attn_mask=None, dropout_mask=None, alibi_mask=None, keep_prob=1.0):
         cfg = dict(prev_block_num=prev_block_num, next_block_num=next_block_num, scale=scale, causal=causal,
-                   keep_prob=keep_prob)
+                   keep_prob=keep_prob, deterministic=deterministic)
         return _FlashAttentionFunction.apply(query, key, value, attn_mask, dropout_mask, alibi_mask, cfg)
 
     fa_forward.prev_block_num = prev_block_num

@@ -9,7 +9,7 @@ import math
 import torch
 
 from . import _lib
-from ._lib import (ACCT_BF16, ACCT_F16, ACCT_U8, BAND_UNBOUNDED, FLAG_GRAD_F32, MASK_FULL, MASK_NONE,
+from ._lib import (ACCT_BF16, ACCT_F16, ACCT_U8, BAND_UNBOUNDED, FLAG_DETERMINISTIC, FLAG_GRAD_F32, MASK_FULL, MASK_NONE,
                    MASK_TILE128, DecodeArgs, FaArgs, FaBwdIO, InferArgs, check, load)
 
 _DTYPES = {torch.float16: ACCT_F16, torch.bfloat16: ACCT_BF16, torch.uint8: ACCT_U8, torch.bool: ACCT_U8}
@@ -127,7 +127,7 @@ def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dro
 def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, causal=False,
                 dropout_mask=None, keep_prob=1.0, alibi=None, alibi_slopes=None,
                 prev_block_num=BAND_UNBOUNDED, next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None,
-                grads_fp32=False, tri_block=0):
+                grads_fp32=False, tri_block=0, deterministic=False):
     """Grad primitive: returns (dq, dk, dv), fp32 when ``grads_fp32`` (what the reference primitive
     returns) else in q's dtype (what its bprop hands back after the cast)."""
     lib = load()
@@ -144,7 +144,8 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
     lse = lse.contiguous()
     a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
                             alibi_slopes, prev_block_num, next_block_num, scale, seq_lens,
-                            flags=FLAG_GRAD_F32 if grads_fp32 else 0, tri_block=tri_block)
+                            flags=(FLAG_GRAD_F32 if grads_fp32 else 0) | (FLAG_DETERMINISTIC if deterministic else 0),
+                            tri_block=tri_block)
     nbytes = lib.acct_fa_bwd_workspace_bytes(C.byref(a))
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     g = FaBwdIO()

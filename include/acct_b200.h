@@ -67,7 +67,8 @@ extern "C" {
 
 /* flags */
 #define ACCT_FLAG_GRAD_F32 1u      /* acct_fa_bwd writes dq/dk/dv as fp32 (what the reference primitive returns) */
-#define ACCT_FLAG_DETERMINISTIC 2u /* acct_fa_bwd reduces dq in a fixed order */
+#define ACCT_FLAG_DETERMINISTIC 2u /* acct_fa_bwd adds the dq contributions of the K/V tiles in a fixed order, so that
+                                      dq is bit-identical from run to run (dk, dv and the forward always are) */
 
 /* Arguments shared by the training forward and backward.
  *
@@ -141,7 +142,7 @@ typedef struct acct_fa_bwd_io {
 /* Forward: writes o and (if non-NULL) lse. */
 ACCT_API int acct_fa_fwd(const acct_fa_args* a, void* stream);
 
-/* Bytes of scratch acct_fa_bwd needs for `a` (row sums Dl and an fp32 dQ accumulator).
+/* Bytes of scratch acct_fa_bwd needs for `a` (row sums Dl, turn counters and an fp32 dQ accumulator).
  * The reference declares its fp32 gradient outputs "atomic add" buffers that the runtime zero-fills
  * (flash_attention_bwd.py:55-57); here the library zero-fills its own accumulator on `stream`. */
 ACCT_API size_t acct_fa_bwd_workspace_bytes(const acct_fa_args* a);

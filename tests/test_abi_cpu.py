@@ -109,7 +109,8 @@ def test_null_struct_pointers(lib):
 def test_backward_workspace_size_and_rejection(lib):
     a = _args(B=2, N=3, S_q=200, S_k=300, D=128, lse=0x2000)
     rows = 2 * 3 * 200
-    need = ((rows * 4 + 255) // 256) * 256 + rows * 128 * 4
+    q_tiles = 2 * 3 * 2          # ceil(200 / 128) Q tiles per (batch, head) slice
+    need = ((rows * 4 + 255) // 256) * 256 + ((q_tiles * 4 + 255) // 256) * 256 + rows * 128 * 4
     assert lib.acct_fa_bwd_workspace_bytes(C.byref(a)) == need
     g = _lib.FaBwdIO()
     g.d_o = g.dq = g.dk = g.dv = 0x3000

@@ -314,6 +314,24 @@ def test_seq_lens_zero_and_full(dev):
     _check_o(y[1:], y_ref)
 
 
+@pytest.mark.parametrize("kw", [dict(causal=True), dict(), dict(prev_block_num=2, next_block_num=1), dict(tri_block=384)])
+def test_deterministic_backward_is_bit_reproducible(dev, kw):
+    # the reference requires run-to-run equality of its gradients (tests/train/flash_attention/st/test_sharding.py:91-115)
+    ops = _ops()
+    B, N, S, D = 2, 3, 1024 + 72, 128
+    q, k, v, do = (_rand((B, N, S, D), 130 + i).to(dev) for i in range(4))
+    o, lse = ops.fa_forward(q, k, v, scale=0.09, **kw)
+    runs = [ops.fa_backward(q, k, v, o, lse, do, scale=0.09, deterministic=True, **kw) for _ in range(3)]
+    _status()
+    for other in runs[1:]:
+        for a, b_ in zip(runs[0], other):
+            assert torch.equal(a, b_)
+    loose = ops.fa_backward(q, k, v, o, lse, do, scale=0.09, **kw)
+    _status()
+    for a, b_ in zip(runs[0], loose):
+        assert float((a.float() - b_.float()).abs().max()) <= 1e-2 * float(a.float().abs().max())
+
+
 # ---------------------------------------------------------------------------------------------
 # size-independent properties at the benchmark's full sizes
 # ---------------------------------------------------------------------------------------------
