@@ -124,7 +124,8 @@ int make_tmap_4d(CUtensorMap* out, const TensorDesc4& t, int box_rows) {
 namespace {
 
 constexpr int kMaxHeadDimCell = 256;   // the reference cell's limit (nn/layer/flash_attention.py:26,105-106)
-constexpr int kMaxHeadDimKernel = 128; // what the tcgen05 kernels here are instantiated for
+constexpr int kMaxHeadDimFwd = 256;    // forward / prefill kernels: tiles padded to 64, 128 or 256 columns
+constexpr int kMaxHeadDimBwd = 128;    // backward kernel: dK and dV accumulators fill tensor memory at 128
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -140,10 +141,10 @@ int check_strides(const char* name, const int64_t s[3], int64_t S, int64_t N, in
   return 0;
 }
 
-int check_head_dim(int D) {
+int check_head_dim(int D, int kernel_max, const char* what) {
   if (D <= 0 || D > kMaxHeadDimCell) return fail(ACCT_ERR_UNSUPPORTED_D, "head_dim %d outside (0, %d]", D, kMaxHeadDimCell);
   if (D % 8 != 0) return fail(ACCT_ERR_UNSUPPORTED_D, "head_dim %d is not a multiple of 8", D);
-  if (D > kMaxHeadDimKernel) return fail(ACCT_ERR_UNSUPPORTED_D, "head_dim %d > %d is not built in this library", D, kMaxHeadDimKernel);
+  if (D > kernel_max) return fail(ACCT_ERR_UNSUPPORTED_D, "head_dim %d > %d is not built for the %s", D, kernel_max, what);
   return 0;
 }
 
@@ -151,12 +152,12 @@ struct Strides {
   int64_t q[3], k[3], v[3], o[3];
 };
 
-int validate_fa(const acct_fa_args* a, Strides* st) {
+int validate_fa(const acct_fa_args* a, Strides* st, bool backward = false) {
   if (a == nullptr) return fail(ACCT_ERR_NULL, "args is NULL");
   if (a->dtype != ACCT_F16 && a->dtype != ACCT_BF16) return fail(ACCT_ERR_DTYPE, "dtype must be ACCT_F16 or ACCT_BF16");
   if (a->B <= 0 || a->N <= 0 || a->S_q <= 0 || a->S_k <= 0) return fail(ACCT_ERR_SHAPE, "B, N, S_q, S_k must be positive");
   if (static_cast<int64_t>(a->B) * a->N > 65535) return fail(ACCT_ERR_SHAPE, "B*N = %lld exceeds 65535", (long long)a->B * a->N);
-  int rc = check_head_dim(a->D);
+  int rc = backward ? check_head_dim(a->D, kMaxHeadDimBwd, "backward") : check_head_dim(a->D, kMaxHeadDimFwd, "forward");
   if (rc) return rc;
   if (!a->q || !a->k || !a->v || !a->o) return fail(ACCT_ERR_NULL, "q, k, v, o must be non-NULL");
   if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o))
@@ -291,7 +292,7 @@ size_t acct_fa_bwd_workspace_bytes(const acct_fa_args* a) {
 
 int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   Strides st;
-  int rc = validate_fa(a, &st);
+  int rc = validate_fa(a, &st, true);
   if (rc) return rc;
   if (g == nullptr) return fail(ACCT_ERR_NULL, "backward io is NULL");
   if (!g->d_o || !g->dq || !g->dk || !g->dv || !a->lse) return fail(ACCT_ERR_NULL, "d_o, dq, dk, dv and lse must be non-NULL");

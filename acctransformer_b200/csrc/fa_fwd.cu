@@ -35,7 +35,7 @@ namespace acct {
 namespace {
 
 constexpr int kFwdThreads = 320;
-constexpr int kStages = 2;
+constexpr int kStages = 2;   // K/V ring depth for head_dim <= 128 (one stage above that)
 constexpr int kUnitGroup = 8;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
@@ -80,13 +80,17 @@ template <int DPAD, bool BF16, bool GENERIC>
 __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_constant__ FwdParams p) {
   constexpr int NB = DPAD / 64;                 // 64-column (128-byte) blocks per row
   constexpr uint32_t kTileBytes = NB * 16384u;  // one 128-row tile
-  constexpr uint32_t kColS = 0, kColO = 256;
+  // head_dim in (128, 256]: O takes 256 columns of tensor memory and a K or V tile 64 KB of shared memory, so a
+  // CTA then owns ONE Q tile (softmax group 1 idles) and K and V have one stage each.
+  constexpr int NQ = DPAD > 128 ? 1 : 2;        // Q tiles per CTA
+  constexpr int kSt = DPAD > 128 ? 1 : kStages;  // K/V stages
+  constexpr uint32_t kColS = 0, kColO = NQ * 128;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                          // 2 tiles; reused as the staging of O at the end
-  uint8_t* sK = sQ + 2 * kTileBytes;           // kStages tiles
-  uint8_t* sV = sK + kStages * kTileBytes;     // kStages tiles
+  uint8_t* sK = sQ + NQ * kTileBytes;          // kSt tiles
+  uint8_t* sV = sK + kSt * kTileBytes;         // kSt tiles
   __shared__ FwdShared sh;
 
   const int tid = threadIdx.x;
@@ -95,7 +99,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
   const ScoreMods& mods = p.mods;
 
   // linear CTA number -> ((batch, head) slice, tile pair): groups of kUnitGroup slices, heaviest pairs first
-  const int n_pairs = (p.S_q + 2 * kTile - 1) / (2 * kTile);
+  const int n_pairs = (p.S_q + NQ * kTile - 1) / (NQ * kTile);
   const int n_units = p.B * p.N;
   int bh, pair;
   {
@@ -111,8 +115,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
   int kv_len = p.S_k;
   if (mods.seq_lens != nullptr) kv_len = min(p.S_k, max(0, mods.seq_lens[b]));
 
-  const TileRange r0 = kv_tile_range(2 * pair, p.S_q, kv_len, mods);
-  const TileRange r1 = kv_tile_range(2 * pair + 1, p.S_q, kv_len, mods);
+  const TileRange r0 = kv_tile_range(NQ * pair, p.S_q, kv_len, mods);
+  TileRange r1 = kv_tile_range(NQ * pair + 1, p.S_q, kv_len, mods);
+  if (NQ == 1) { r1.lo = 0; r1.hi = -1; }
   const bool any0 = r0.lo <= r0.hi, any1 = r1.lo <= r1.hi;
   int cta_lo = 0, cta_hi = -1;
   if (any0 && any1) { cta_lo = min(r0.lo, r1.lo); cta_hi = max(r0.hi, r1.hi); }
@@ -121,7 +126,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
 
   if (tid == 0) {
     mbar_init(&sh.q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kSt; ++s) {
       mbar_init(&sh.k_full[s], 1); mbar_init(&sh.k_empty[s], 1);
       mbar_init(&sh.v_full[s], 1); mbar_init(&sh.v_empty[s], 1);
     }
@@ -142,20 +147,20 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && cta_hi >= cta_lo) {
       prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_o);
-      mbar_expect_tx(&sh.q_full, 2 * kTileBytes);
-      for (int qt = 0; qt < 2; ++qt)
+      mbar_expect_tx(&sh.q_full, NQ * kTileBytes);
+      for (int qt = 0; qt < NQ; ++qt)
         for (int nb = 0; nb < NB; ++nb)
           tma_load_4d(sQ + qt * kTileBytes + nb * 16384, &p.map_q, &sh.q_full, nb * 64,
-                      (2 * pair + qt) * kTile, h, b);
+                      (NQ * pair + qt) * kTile, h, b);
       int it = 0;
       for (int j = cta_lo; j <= cta_hi; ++j, ++it) {
-        const int st = it % kStages;
-        const uint32_t reuse_parity = ((it / kStages) - 1) & 1;
-        if (it >= kStages) mbar_wait(&sh.k_empty[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+        const int st = it % kSt;
+        const uint32_t reuse_parity = ((it / kSt) - 1) & 1;
+        if (it >= kSt) mbar_wait(&sh.k_empty[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         mbar_expect_tx(&sh.k_full[st], kTileBytes);
         for (int nb = 0; nb < NB; ++nb)
           tma_load_4d(sK + st * kTileBytes + nb * 16384, &p.map_k, &sh.k_full[st], nb * 64, j * kTile, h, b);
-        if (it >= kStages) mbar_wait(&sh.v_empty[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+        if (it >= kSt) mbar_wait(&sh.v_empty[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         mbar_expect_tx(&sh.v_full[st], kTileBytes);
         for (int nb = 0; nb < NB; ++nb)
           tma_load_4d(sV + st * kTileBytes + nb * 16384, &p.map_v, &sh.v_full[st], nb * 64, j * kTile, h, b);
@@ -191,10 +196,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       umma_commit(&sh.k_empty[0]);
       int it = 0;
       for (int j = cta_lo; j <= cta_hi; ++j, ++it) {
-        const int st = it % kStages;
-        const int stn = (it + 1) % kStages;
-        const uint32_t full_parity = (it / kStages) & 1;
-        const uint32_t full_parity_n = ((it + 1) / kStages) & 1;
+        const int st = it % kSt;
+        const int stn = (it + 1) % kSt;
+        const uint32_t full_parity = (it / kSt) & 1;
+        const uint32_t full_parity_n = ((it + 1) / kSt) & 1;
         for (int qt = 0; qt < 2; ++qt) {
           if (j >= rng[qt].lo && j <= rng[qt].hi) {
             mbar_wait(&sh.p_ready[qt], n_done[qt] & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
@@ -222,7 +227,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
     // ------------------------------------------------------------------ softmax groups
     const int qt = warp >> 2;
     const TileRange rng = qt == 0 ? r0 : r1;
-    const int q_tile = 2 * pair + qt;
+    const int q_tile = NQ * pair + qt;
     const int row_in_tile = tid & 127;
     const int q_row = q_tile * kTile + row_in_tile;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -386,7 +391,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
 
     // epilogue: O / l through this group's (now dead) Q tile in shared memory and a TMA store, which
     // clips rows past S_q and columns past D; L = m + ln l straight to global memory
-    if (q_tile * kTile < p.S_q) {
+    if (qt < NQ && q_tile * kTile < p.S_q) {
       if (n > 0) {
         mbar_wait(&sh.o_done[qt], (n - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
         tc_fence_after_sync();
@@ -437,9 +442,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
 }
 
 cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
-  const int dpad = p.D <= 64 ? 64 : 128;
-  const size_t smem = static_cast<size_t>(2 + 2 * kStages) * (dpad / 64) * 16384 + 1024;
-  const int n_pairs = (p.S_q + 2 * kTile - 1) / (2 * kTile);
+  const int dpad = p.D <= 64 ? 64 : (p.D <= 128 ? 128 : 256);
+  const int nq = dpad > 128 ? 1 : 2, stages = dpad > 128 ? 1 : kStages;
+  const size_t smem = static_cast<size_t>(nq + 2 * stages) * (dpad / 64) * 16384 + 1024;
+  const int n_pairs = (p.S_q + nq * kTile - 1) / (nq * kTile);
   dim3 grid(static_cast<unsigned>(n_pairs) * static_cast<unsigned>(p.B * p.N));
   const bool generic = p.mods.mask_kind != 0 || p.mods.alibi != nullptr || p.mods.alibi_slopes != nullptr ||
                        p.mods.drop != nullptr;
@@ -447,9 +453,12 @@ cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
   if (dpad == 64) {
     if (generic) kern = bf16 ? fa_fwd_kernel<64, true, true> : fa_fwd_kernel<64, false, true>;
     else kern = bf16 ? fa_fwd_kernel<64, true, false> : fa_fwd_kernel<64, false, false>;
-  } else {
+  } else if (dpad == 128) {
     if (generic) kern = bf16 ? fa_fwd_kernel<128, true, true> : fa_fwd_kernel<128, false, true>;
     else kern = bf16 ? fa_fwd_kernel<128, true, false> : fa_fwd_kernel<128, false, false>;
+  } else {
+    if (generic) kern = bf16 ? fa_fwd_kernel<256, true, true> : fa_fwd_kernel<256, false, true>;
+    else kern = bf16 ? fa_fwd_kernel<256, true, false> : fa_fwd_kernel<256, false, false>;
   }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;

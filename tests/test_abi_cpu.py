@@ -82,7 +82,6 @@ def _args(**kw):
     (dict(S_q=0), 2),                        # ACCT_ERR_SHAPE
     (dict(dtype=7), 3),                      # ACCT_ERR_DTYPE
     (dict(D=300), 4),                        # beyond the reference cell's 256 limit
-    (dict(D=160), 4),                        # within it, but not built here
     (dict(D=60), 4),                         # not a multiple of 8
     (dict(q=0x1008), 5),                     # ACCT_ERR_ALIGN
     (dict(scale=0.0), 2),
@@ -95,6 +94,18 @@ def test_forward_validation_codes(lib, kw, code):
     rc = lib.acct_fa_fwd(C.byref(a), None)
     assert rc == code, lib.acct_last_error()
     assert lib.acct_last_error() != b""
+
+
+def test_head_dim_limits_differ_for_forward_and_backward(lib):
+    # forward / prefill take head_dim up to 256 (the reference cell's limit); the backward stops at 128
+    a = _args(D=160, lse=0x2000)
+    rc = lib.acct_fa_fwd(C.byref(a), None)
+    assert rc in (0, 9)          # passes validation; 9 = no sm_100 device on this machine
+    g = _lib.FaBwdIO()
+    g.d_o = g.dq = g.dk = g.dv = 0x3000
+    g.workspace, g.workspace_bytes = 0x4000, 1 << 30
+    assert lib.acct_fa_bwd(C.byref(a), C.byref(g), None) == 4
+    assert b"backward" in lib.acct_last_error()
 
 
 def test_null_struct_pointers(lib):

@@ -233,6 +233,28 @@ def test_config5_prefill_causal_and_decode(dev):
         _check_o(yd, ref.decode_ref(qd.numpy(), kc.numpy(), vc.numpy(), lens.numpy(), scale))
 
 
+@pytest.mark.parametrize("D, S_q, S_k, causal", [(160, 512, 512, False), (160, 300, 700, False), (256, 384, 384, True),
+                                                    (192, 1024, 1024, True)])
+def test_forward_head_dims_above_128(dev, D, S_q, S_k, causal):
+    # the inference op's envelope includes head_dim 160 (infer/flash_attention/tik/tbe/impl/flash_attention_fwd.py:34-40),
+    # the cell's goes up to 256 (nn/layer/flash_attention.py:26)
+    from acctransformer_b200 import flash_attention_tik
+    B, N = 1, 2
+    q = _rand((B, N, S_q, D), 140, std=0.5)
+    k, v = _rand((B, N, S_k, D), 141, std=0.5), _rand((B, N, S_k, D), 142, std=0.5)
+    y = flash_attention_tik(q.to(dev), k.to(dev), v.to(dev), scale=1.0 / math.sqrt(D), causal=causal)
+    _status()
+    _check_o(y, ref.infer_fwd(q.numpy(), k.numpy(), v.numpy(), scale=1.0 / math.sqrt(D), causal=causal))
+    ops = _ops()
+    o, lse = ops.fa_forward(q.to(dev), k.to(dev), v.to(dev), causal=causal, scale=1.0 / math.sqrt(D))
+    _status()
+    _, l_ref = ref.sa_fwd(q.numpy(), k.numpy(), v.numpy(), causal=causal, scale=1.0 / math.sqrt(D))
+    assert float(np.max(np.abs(_np(lse) - l_ref))) <= O_TOL
+    from acctransformer_b200._lib import AcctError
+    with pytest.raises(AcctError, match="UNSUPPORTED_D"):
+        ops.fa_backward(q.to(dev), k.to(dev), v.to(dev), o, lse, o, causal=causal)
+
+
 # ---------------------------------------------------------------------------------------------
 # edge cases taken from the reference tests' shape lists, and ragged / mixed-option cases
 # ---------------------------------------------------------------------------------------------
