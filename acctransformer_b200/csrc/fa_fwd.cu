@@ -34,7 +34,8 @@ namespace acct {
 
 namespace {
 
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 384;   // warps 10 and 11 only complete the third warpgroup (register re-split)
+constexpr int kRegsSoftmax = 208, kRegsControl = 88;
 constexpr int kStages = 2;   // K/V ring depth for head_dim <= 128 (one stage above that)
 constexpr int kUnitGroup = 8;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
@@ -66,7 +67,7 @@ struct FwdShared {
   uint64_t q_full;
   uint64_t k_full[kStages], k_empty[kStages];
   uint64_t v_full[kStages], v_empty[kStages];
-  uint64_t s_full[2], p_ready[2], o_done[2];
+  uint64_t s_full[2], p_half[2], p_ready[2], o_done[2];
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   alignas(16) float alibi[2][2][kTile];   // [softmax group][tile parity]: alibi row of the K/V tile, log2 units
@@ -131,7 +132,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       mbar_init(&sh.v_full[s], 1); mbar_init(&sh.v_empty[s], 1);
     }
     for (int q = 0; q < 2; ++q) {
-      mbar_init(&sh.s_full[q], 1); mbar_init(&sh.p_ready[q], 128); mbar_init(&sh.o_done[q], 1);
+      mbar_init(&sh.s_full[q], 1); mbar_init(&sh.p_half[q], 128); mbar_init(&sh.p_ready[q], 128);
+      mbar_init(&sh.o_done[q], 1);
     }
     sh.abort_flag = 0;
     mbar_fence_init();
@@ -145,6 +147,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
+    reg_dealloc<kRegsControl>();
     if (lane == 0 && cta_hi >= cta_lo) {
       prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_o);
       mbar_expect_tx(&sh.q_full, NQ * kTileBytes);
@@ -168,63 +171,92 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
+    // The tensor pipe takes the MMAs at the rate it executes them and holds only a couple in its queue, so
+    // whatever this thread does between two MMAs is time the pipe may idle.  Hence: descriptors are stepped
+    // with one 32-bit add, the waits on the K/V ring (long satisfied when they are reached) are placed right
+    // behind a burst of MMAs that is still executing, and each hand-off from the softmax groups is waited
+    // for once.
+    reg_dealloc<kRegsControl>();
     if (lane == 0 && cta_hi >= cta_lo) {
       const uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);
       const uint32_t idesc_o = make_idesc(BF16, 128, DPAD, false, true);
       const uint64_t kmajor = make_sdesc_base(16, 1024);
       const uint64_t mnmajor = make_sdesc_base(16384, 1024);
+      const uint32_t k_hi = static_cast<uint32_t>(kmajor >> 32), k_lo = static_cast<uint32_t>(kmajor);
+      const uint32_t mn_hi = static_cast<uint32_t>(mnmajor >> 32), mn_lo = static_cast<uint32_t>(mnmajor);
       const TileRange rng[2] = {r0, r1};
       int n_done[2] = {0, 0};   // P tiles consumed so far per Q tile
+      // low descriptor words of the tile bases (all tiles are 1024-byte aligned, so offsets simply add)
+      const uint32_t q_lo = k_lo | ((smem_u32(sQ) >> 4) & 0x3fffu);
+      const uint32_t kt_lo = k_lo | ((smem_u32(sK) >> 4) & 0x3fffu);
+      const uint32_t vt_lo = mn_lo | ((smem_u32(sV) >> 4) & 0x3fffu);
+      constexpr uint32_t kTileUnits = kTileBytes >> 4;
       mbar_wait(&sh.q_full, 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
 
       auto issue_s = [&](int qt, int st) {
-        const uint32_t a0 = smem_u32(sQ + qt * kTileBytes);
-        const uint32_t b0 = smem_u32(sK + st * kTileBytes);
+        const uint32_t a0 = q_lo + qt * kTileUnits, b0 = kt_lo + st * kTileUnits;
 #pragma unroll
         for (int kk = 0; kk < DPAD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
-          umma_ss(tmem + kColS + qt * 128, sdesc_at(kmajor, a0 + off), sdesc_at(kmajor, b0 + off), idesc_s, kk > 0);
+          const uint32_t off = (kk >> 2) * 1024u + (kk & 3) * 2u;   // 16-byte units
+          umma_ss_lohi(tmem + kColS + qt * 128, a0 + off, k_hi, b0 + off, k_hi, idesc_s, kk > 0);
         }
         umma_commit(&sh.s_full[qt]);
       };
 
       // prologue: scores of the first K/V tile
       mbar_wait(&sh.k_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
-      tc_fence_after_sync();
       for (int qt = 0; qt < 2; ++qt)
         if (cta_lo >= rng[qt].lo && cta_lo <= rng[qt].hi) issue_s(qt, 0);
       umma_commit(&sh.k_empty[0]);
+      mbar_wait(&sh.v_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
       int it = 0;
       for (int j = cta_lo; j <= cta_hi; ++j, ++it) {
         const int st = it % kSt;
         const int stn = (it + 1) % kSt;
-        const uint32_t full_parity = (it / kSt) & 1;
         const uint32_t full_parity_n = ((it + 1) / kSt) & 1;
+        const bool more = j + 1 <= cta_hi;
+        bool k_seen = false;   // K tile j+1 seen full
         for (int qt = 0; qt < 2; ++qt) {
-          if (j >= rng[qt].lo && j <= rng[qt].hi) {
-            mbar_wait(&sh.p_ready[qt], n_done[qt] & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-            mbar_wait(&sh.v_full[st], full_parity, abort_flag, p.status, DEV_TIMEOUT_TMA);
+          const bool pv = j >= rng[qt].lo && j <= rng[qt].hi;
+          const bool sn = more && j + 1 >= rng[qt].lo && j + 1 <= rng[qt].hi;
+          const uint32_t t_s = tmem + kColS + qt * 128, t_o = tmem + kColO + qt * DPAD;
+          const uint32_t v0 = vt_lo + st * kTileUnits;
+          if (pv) {
+            // P arrives in two halves (key rows 0-63, then 64-127 of the V tile, which was seen full before)
+            mbar_wait(&sh.p_half[qt], n_done[qt] & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
             tc_fence_after_sync();
-            const uint32_t v0 = smem_u32(sV + st * kTileBytes);
 #pragma unroll
-            for (int kk = 0; kk < kTile / 16; ++kk)
-              umma_ts(tmem + kColO + qt * DPAD, tmem + kColS + qt * 128 + kk * 8,
-                      sdesc_at(mnmajor, v0 + kk * 2048u), idesc_o, n_done[qt] > 0 || kk > 0);
+            for (int kk = 0; kk < kTile / 32; ++kk)
+              umma_ts_lohi(t_o, t_s + kk * 8, v0 + kk * 128u, mn_hi, idesc_o, n_done[qt] > 0 || kk > 0);
+          }
+          if (sn && !k_seen) {
+            mbar_wait(&sh.k_full[stn], full_parity_n, abort_flag, p.status, DEV_TIMEOUT_TMA);
+            k_seen = true;
+          }
+          if (pv) {
+            mbar_wait(&sh.p_ready[qt], n_done[qt] & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+            tc_fence_after_sync();
+#pragma unroll
+            for (int kk = kTile / 32; kk < kTile / 16; ++kk)
+              umma_ts_lohi(t_o, t_s + kk * 8, v0 + kk * 128u, mn_hi, idesc_o, true);
             umma_commit(&sh.o_done[qt]);
             ++n_done[qt];
           }
-          if (j + 1 <= cta_hi && j + 1 >= rng[qt].lo && j + 1 <= rng[qt].hi) {
-            mbar_wait(&sh.k_full[stn], full_parity_n, abort_flag, p.status, DEV_TIMEOUT_TMA);
-            tc_fence_after_sync();
-            issue_s(qt, stn);
-          }
+          if (sn) issue_s(qt, stn);
         }
         umma_commit(&sh.v_empty[st]);
-        if (j + 1 <= cta_hi) umma_commit(&sh.k_empty[stn]);
+        if (more) {
+          umma_commit(&sh.k_empty[stn]);
+          // the next V tile, waited for while the MMAs just issued still execute
+          mbar_wait(&sh.v_full[stn], full_parity_n, abort_flag, p.status, DEV_TIMEOUT_TMA);
+        }
       }
     }
+  } else if (warp >= 10) {
+    reg_dealloc<kRegsControl>();
   } else {
     // ------------------------------------------------------------------ softmax groups
+    reg_alloc<kRegsSoftmax>();
     const int qt = warp >> 2;
     const TileRange rng = qt == 0 ? r0 : r1;
     const int q_tile = NQ * pair + qt;
@@ -326,26 +358,70 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
             s[c][i] = (col_base + c * 32 + i >= bound) ? __float_as_uint(kNegInf) : s[c][i];
       }
 
-      // row maximum (four independent chains)
+      // One 32-column chunk: P = exp2(x * mult - m) packed to 16 bits, row sum (before dropout) into `l4`.
+      // Two-wide fp32 instructions do the scaling and the sum in half the issue slots.
+      const uint64_t mult2 = f2_pack(mult, mult);
+      auto exp_chunk = [&](int c, uint64_t negm2, uint64_t (&l4)[4], uint32_t (&pk)[16]) {
+        bool dropped = false;
+        if constexpr (GENERIC) if (mods.drop != nullptr) {
+          dropped = true;
+          const int col0 = col_base + c * 32;
+          const bool drop_vec = col_base + kTile <= p.S_k && (p.S_k & 15) == 0 &&
+                                (reinterpret_cast<uintptr_t>(mods.drop) & 15u) == 0;
+          float f[32];
+          load_row32(mods.drop, mods.drop_dtype, drop_row + col0, p.S_k - col0, drop_vec, mods.drop_scale, f);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])), mult2, negm2), x0, x1);
+            const float p0 = ex2(x0), p1 = ex2(x1);
+            l4[i & 3] = f2_add(l4[i & 3], f2_pack(p0, p1));
+            pk[i] = pack2<BF16>(p0 * f[2 * i], p1 * f[2 * i + 1]);
+          }
+        }
+        if (!dropped) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])), mult2, negm2), x0, x1);
+            const float p0 = ex2(x0), p1 = ex2(x1);
+            l4[i & 3] = f2_add(l4[i & 3], f2_pack(p0, p1));
+            pk[i] = pack2<BF16>(p0, p1);
+          }
+        }
+      };
+
+      // The running maximum rarely moves after the first tiles (it is only refreshed when it grows by more than
+      // the threshold), so from the second tile on the exponentials of chunk 0 are started with the old maximum
+      // while the row maximum of the tile is still being formed (four independent chains of three-input maxima,
+      // which fill the gaps the exponential unit leaves).  If some row of the warp does need a new maximum, that
+      // chunk is simply computed again.
+      uint64_t l_part[4] = {0ull, 0ull, 0ull, 0ull};
+      uint32_t pk0[16];
+      const bool speculate = n > 0;
+      if (speculate) {
+        const float m_old = (m_run == kNegInf) ? 0.f : m_run;
+        exp_chunk(0, f2_pack(-m_old, -m_old), l_part, pk0);
+      }
       float mx[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        mx[c] = __uint_as_float(s[c][0]);
+        mx[c] = fmaxf(__uint_as_float(s[c][0]), __uint_as_float(s[c][31]));
 #pragma unroll
-        for (int i = 1; i < 32; ++i) mx[c] = fmaxf(mx[c], __uint_as_float(s[c][i]));
+        for (int i = 1; i < 31; i += 2) mx[c] = fmax3(mx[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
       }
       const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * mult;   // scale > 0
 
-      // running max, refreshed only when it grows by more than the threshold
       const float m_new = fmaxf(m_run, m_tile);
       const bool grow = (m_new > m_run + kRescaleThreshold) || (m_run == kNegInf && m_new != kNegInf);
+      const bool any_grow = __any_sync(0xffffffffu, grow);
       float alpha = 1.0f;
       if (grow) {
         alpha = (m_run == kNegInf) ? 0.f : ex2(m_run - m_new);
         m_run = m_new;
         l_run *= alpha;
       }
-      if (n > 0 && __any_sync(0xffffffffu, grow)) {
+      if (n > 0 && any_grow) {
         // O of the previous tiles is complete (the S MMA just waited for was issued after their P V)
 #pragma unroll 1
         for (int c = 0; c < DPAD / 32; ++c) {
@@ -358,32 +434,30 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         }
       }
       const float m_use = (m_run == kNegInf) ? 0.f : m_run;
-
-      // P = exp2(x - m), row sum before dropout, 16-bit P over the S buffer
-      float l_part[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint64_t negm2 = f2_pack(-m_use, -m_use);
+      if (!speculate || any_grow) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float pr[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          pr[i] = ex2(fmaf(__uint_as_float(s[c][i]), mult, -m_use));
-          l_part[i & 3] += pr[i];
-        }
-        if constexpr (GENERIC) if (mods.drop != nullptr) {
-          const int col0 = col_base + c * 32;
-          const bool drop_vec = col_base + kTile <= p.S_k && (p.S_k & 15) == 0 &&
-                                (reinterpret_cast<uintptr_t>(mods.drop) & 15u) == 0;
-          float f[32];
-          load_row32(mods.drop, mods.drop_dtype, drop_row + col0, p.S_k - col0, drop_vec, mods.drop_scale, f);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) pr[i] *= f[i];
-        }
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) pk[i] = pack2<BF16>(pr[2 * i], pr[2 * i + 1]);
-        tmem_st16(t_s + c * 16, pk);
+        for (int i = 0; i < 4; ++i) l_part[i] = 0ull;
+        exp_chunk(0, negm2, l_part, pk0);
       }
-      l_run += (l_part[0] + l_part[1]) + (l_part[2] + l_part[3]);
+      tmem_st16(t_s, pk0);
+      // 16-bit P goes back over the S buffer; the first half is handed to the MMA warp as soon as it is stored
+#pragma unroll
+      for (int c = 1; c < 4; ++c) {
+        uint32_t pk[16];
+        exp_chunk(c, negm2, l_part, pk);
+        tmem_st16(t_s + c * 16, pk);
+        if (c == 1) {
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(&sh.p_half[qt]);
+        }
+      }
+      {
+        float a0, a1;
+        f2_unpack(f2_add(f2_add(l_part[0], l_part[1]), f2_add(l_part[2], l_part[3])), a0, a1);
+        l_run += a0 + a1;
+      }
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&sh.p_ready[qt]);
