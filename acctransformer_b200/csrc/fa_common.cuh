@@ -159,17 +159,4 @@ __device__ __forceinline__ void load_col32(const void* base, int dtype, int64_t 
   }
 }
 
-// 2^x on the FMA pipe (for x <= ~1): round-to-nearest split x = n + f, degree-3 minimax polynomial for 2^f on
-// [-0.5, 0.5] (relative error 7.5e-5, far below the 16-bit rounding P gets afterwards), then n added to the
-// exponent field.  Takes load off the 16-lane transcendental unit.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.0f);
-  const float t = x + 12582912.0f;                 // 1.5 * 2^23: n lands in the low mantissa bits
-  const float f = x - (t - 12582912.0f);
-  float p = fmaf(0.0551716648f, f, 0.2426111251f);
-  p = fmaf(p, f, 0.6932609677f);
-  p = fmaf(p, f, 0.9999280572f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
 }  // namespace acct

@@ -64,23 +64,27 @@ constexpr long long kWaitCycleLimit = 2000000000LL;
 // host learns of it through the status word), meet at the final barrier and free tensor memory.
 // Control flow therefore never depends on a wait's outcome, which keeps warp-collective
 // instructions and named barriers safe.
+// The limit counts polls, not clock cycles: that keeps the loop to a handful of instructions (the callers, above
+// all the single MMA-issuing thread, must stay small enough to sit in the instruction cache beside the softmax
+// loop), and time during which the CTA is not running does not count against it.  An unsatisfied try_wait
+// takes from tens of cycles to a hardware-defined suspend time, so 2^24 polls are between a fraction of a
+// second and some tens of seconds.
+constexpr uint32_t kWaitPollLimit = 1u << 24;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned int* status, unsigned int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  if (*abort_flag != 0u) return false;
-  const long long t0 = clock64();
   uint32_t polls = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+  do {
     if ((++polls & 0x3fu) == 0u) {
       if (*abort_flag != 0u) return false;
-      if (clock64() - t0 > kWaitCycleLimit) {
+      if (polls >= kWaitPollLimit) {
         *abort_flag = 1u;
         atomicMax(status, code);
         return false;
       }
     }
-  }
+  } while (!mbar_try_wait(bar, parity));
+  return true;
 }
 
 // ------------------------------------------------------------------------------------------
