@@ -27,6 +27,7 @@ EXPORTS = [
     "acct_fa_fwd", "acct_fa_bwd_workspace_bytes", "acct_fa_bwd", "acct_infer_prefill",
     "acct_infer_decode_workspace_bytes", "acct_infer_decode", "acct_infer_decode_static", "acct_device_status",
     "acct_last_error", "acct_abi_version",
+    "acct_ms_set_fa_attrs", "acct_ms_fa_fwd", "acct_ms_fa_grad", "acct_ms_infer_fa",
 ]
 
 

@@ -1,0 +1,192 @@
+// Entry points with the signature MindSpore gives a custom operator of func_type "aot":
+//   int f(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream, void* extra)
+// (params: the inputs followed by the outputs, all device pointers).  They unpack that call into the argument
+// structs of the library's own entry points, so that the reference's two primitives
+//   train/acctransformer/flash_attention/ops/flash_attention/flash_attention_impl.py:96-126  (grad)
+//   train/acctransformer/flash_attention/ops/flash_attention/flash_attention_impl.py:129-154 (forward)
+// and its inference op (infer/flash_attention/tik/op_proto/flash_attention_tik.h:22-27) can be registered as
+// ops.Custom("libacct_b200.so:acct_ms_fa_fwd", ..., func_type="aot").  Host code only.
+//
+// The optional inputs carry no names in this calling convention; they are told apart by rank and shape, in the
+// reference's order attn_mask, dropout_mask, alibi_mask:
+//   rank 3 (or rank 2 128x128)            attn_mask  [1 or B, S_q, S_k] / [1,128,128]
+//   rank 4 with shape [B,N,1,S_k]         alibi_mask (when S_q != 1)
+//   rank 4 with shape [B,N,S_q,S_k]       dropout_mask
+// Operator attributes (band limits, keep probability for uint8 masks, the scale) are not part of the call either:
+// acct_ms_set_fa_attrs() sets them for the process, as the reference bakes them into each primitive when it is built
+// (flash_attention_impl.py:146-152).
+#include <atomic>
+#include <cstring>
+
+#include "../../include/acct_b200.h"
+
+namespace {
+
+struct FaAttrs {
+  int prev_block_num = ACCT_BAND_UNBOUNDED;
+  int next_block_num = ACCT_BAND_UNBOUNDED;
+  float keep_prob = 1.0f;
+  float scale = 1.0f;   // the raw primitive does not scale (the cell pre-multiplies q and k)
+  int causal = 0;
+};
+FaAttrs g_attrs;
+std::atomic<int> g_attrs_guard{0};   // bumped around updates; readers copy the struct (set-up time only)
+
+int dtype_code(const char* s) {
+  if (s == nullptr) return -1;
+  if (std::strcmp(s, "float16") == 0) return ACCT_F16;
+  if (std::strcmp(s, "bfloat16") == 0) return ACCT_BF16;
+  if (std::strcmp(s, "uint8") == 0 || std::strcmp(s, "bool") == 0) return ACCT_U8;
+  if (std::strcmp(s, "float32") == 0) return ACCT_F32;
+  return -1;
+}
+
+// Fills the tensor part of `a` from q, k, v at params[0..2]; false if they are not rank-4 [B,N,S,D].
+bool fill_qkv(acct_fa_args& a, void** params, const int* ndims, int64_t** shapes, const char** dtypes) {
+  if (ndims[0] != 4 || ndims[1] != 4 || ndims[2] != 4) return false;
+  const int dt = dtype_code(dtypes[0]);
+  if (dt != ACCT_F16 && dt != ACCT_BF16) return false;
+  a.dtype = dt;
+  a.B = static_cast<int32_t>(shapes[0][0]);
+  a.N = static_cast<int32_t>(shapes[0][1]);
+  a.S_q = static_cast<int32_t>(shapes[0][2]);
+  a.D = static_cast<int32_t>(shapes[0][3]);
+  a.S_k = static_cast<int32_t>(shapes[1][2]);
+  a.q = params[0];
+  a.k = params[1];
+  a.v = params[2];
+  return true;
+}
+
+// Classifies params[first .. last) as attn_mask / dropout_mask / alibi_mask; false on an input it cannot place.
+bool fill_optionals(acct_fa_args& a, int first, int last, void** params, const int* ndims, int64_t** shapes,
+                    const char** dtypes) {
+  for (int i = first; i < last; ++i) {
+    const int r = ndims[i];
+    const int64_t* s = shapes[i];
+    const int dt = dtype_code(dtypes[i]);
+    if (r == 3 || r == 2) {
+      if (a.attn_mask != nullptr || dt < 0 || dt == ACCT_F32) return false;
+      const bool tile = (r == 3 && s[0] == 1 && s[1] == 128 && s[2] == 128 && !(a.S_q == 128 && a.S_k == 128)) ||
+                        (r == 2 && s[0] == 128 && s[1] == 128);
+      a.attn_mask = params[i];
+      a.mask_dtype = dt;
+      a.mask_kind = tile ? ACCT_MASK_TILE128 : ACCT_MASK_FULL;   // attention.py:279-285
+      a.mask_batch = (tile || r == 2) ? 1 : static_cast<int32_t>(s[0]);
+    } else if (r == 4 && s[0] == a.B && s[1] == a.N && s[2] == 1 && s[3] == a.S_k && a.S_q != 1) {
+      if (a.alibi != nullptr || dt != a.dtype) return false;
+      a.alibi = params[i];
+    } else if (r == 4 && s[0] == a.B && s[1] == a.N && s[2] == a.S_q && s[3] == a.S_k) {
+      if (a.dropout_mask != nullptr || dt < 0 || dt == ACCT_F32) return false;
+      a.dropout_mask = params[i];
+      a.dropout_dtype = dt;
+    } else {
+      return false;
+    }
+  }
+  return true;
+}
+
+void apply_attrs(acct_fa_args& a) {
+  const FaAttrs at = g_attrs;
+  a.prev_block_num = at.prev_block_num;
+  a.next_block_num = at.next_block_num;
+  a.keep_prob = at.keep_prob;
+  a.scale = at.scale;
+  a.causal = at.causal;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Process-wide operator attributes for the two training entry points below (set while the graph is built).
+ACCT_API void acct_ms_set_fa_attrs(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal) {
+  g_attrs_guard.fetch_add(1);
+  g_attrs.prev_block_num = prev_block_num;
+  g_attrs.next_block_num = next_block_num;
+  g_attrs.keep_prob = keep_prob;
+  g_attrs.scale = scale;
+  g_attrs.causal = causal;
+  g_attrs_guard.fetch_add(1);
+}
+
+// inputs query, key, value, [attn_mask], [dropout_mask], [alibi_mask]; outputs output, rowsum
+ACCT_API int acct_ms_fa_fwd(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
+                            void* /*extra*/) {
+  if (nparam < 5 || nparam > 8 || params == nullptr || ndims == nullptr || shapes == nullptr || dtypes == nullptr)
+    return ACCT_ERR_SHAPE;
+  acct_fa_args a;
+  std::memset(&a, 0, sizeof a);
+  if (!fill_qkv(a, params, ndims, shapes, dtypes)) return ACCT_ERR_SHAPE;
+  if (!fill_optionals(a, 3, nparam - 2, params, ndims, shapes, dtypes)) return ACCT_ERR_SHAPE;
+  if (dtype_code(dtypes[nparam - 1]) != ACCT_F32) return ACCT_ERR_DTYPE;   // rowsum is fp32 (impl.py:134-136)
+  a.o = params[nparam - 2];
+  a.lse = static_cast<float*>(params[nparam - 1]);
+  apply_attrs(a);
+  return acct_fa_fwd(&a, stream);
+}
+
+// inputs query, key, value, output, do, rowsum, [attn_mask], [dropout_mask], [alibi_mask];
+// outputs dq, dk, dv (fp32, as the reference's grad primitive returns them) and a uint8 workspace tensor of
+// acct_fa_bwd_workspace_bytes() bytes, declared as a fourth output so that the framework allocates it.
+ACCT_API int acct_ms_fa_grad(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
+                             void* /*extra*/) {
+  if (nparam < 10 || nparam > 13 || params == nullptr || ndims == nullptr || shapes == nullptr || dtypes == nullptr)
+    return ACCT_ERR_SHAPE;
+  acct_fa_args a;
+  std::memset(&a, 0, sizeof a);
+  if (!fill_qkv(a, params, ndims, shapes, dtypes)) return ACCT_ERR_SHAPE;
+  const int first_out = nparam - 4;
+  if (!fill_optionals(a, 6, first_out, params, ndims, shapes, dtypes)) return ACCT_ERR_SHAPE;
+  for (int i = first_out; i < first_out + 3; ++i)
+    if (dtype_code(dtypes[i]) != ACCT_F32) return ACCT_ERR_DTYPE;
+  if (ndims[nparam - 1] != 1) return ACCT_ERR_WORKSPACE;
+  a.o = params[3];
+  a.lse = static_cast<float*>(params[5]);
+  apply_attrs(a);
+  a.flags |= ACCT_FLAG_GRAD_F32;
+  acct_fa_bwd_io g;
+  std::memset(&g, 0, sizeof g);
+  g.d_o = params[4];
+  g.dq = params[first_out];
+  g.dk = params[first_out + 1];
+  g.dv = params[first_out + 2];
+  g.workspace = params[nparam - 1];
+  g.workspace_bytes = static_cast<size_t>(shapes[nparam - 1][0]);
+  return acct_fa_bwd(&a, &g, stream);
+}
+
+// inputs q, k, v (rank 3 [B*N,S,D] or rank 4 [B,N,S,D]); output y shaped like q
+// (infer/flash_attention/tik/op_proto/flash_attention_tik.cpp:163-191)
+ACCT_API int acct_ms_infer_fa(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
+                              void* /*extra*/) {
+  if (nparam != 4 || params == nullptr || ndims == nullptr || shapes == nullptr || dtypes == nullptr)
+    return ACCT_ERR_SHAPE;
+  const int r = ndims[0];
+  if ((r != 3 && r != 4) || ndims[1] != r || ndims[2] != r) return ACCT_ERR_SHAPE;
+  acct_infer_args a;
+  std::memset(&a, 0, sizeof a);
+  const int dt = dtype_code(dtypes[0]);
+  if (dt != ACCT_F16 && dt != ACCT_BF16) return ACCT_ERR_DTYPE;
+  a.dtype = dt;
+  a.rank = r;
+  const int o = r - 3;   // index of the heads (rank 3: batch*heads) dimension
+  a.B = r == 4 ? static_cast<int32_t>(shapes[0][0]) : 1;
+  a.N = static_cast<int32_t>(shapes[0][o]);
+  a.S_q = static_cast<int32_t>(shapes[0][o + 1]);
+  a.D = static_cast<int32_t>(shapes[0][o + 2]);
+  a.S_k = static_cast<int32_t>(shapes[1][o + 1]);
+  if (shapes[1][o] != shapes[0][o] || shapes[2][o] != shapes[0][o] || shapes[1][o + 2] != a.D ||
+      shapes[2][o + 2] != a.D || shapes[2][o + 1] != a.S_k)
+    return ACCT_ERR_SHAPE;
+  a.q = params[0];
+  a.k = params[1];
+  a.v = params[2];
+  a.y = params[3];
+  a.causal = 0;
+  a.scale = 1.0f;   // the reference op applies no scale
+  return acct_infer_prefill(&a, stream);
+}
+
+}  // extern "C"

@@ -211,6 +211,29 @@ ACCT_API int acct_infer_decode(const acct_decode_args* a, void* stream);
 #define ACCT_DECODE_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
 ACCT_API int acct_infer_decode_static(const acct_decode_args* a, void* stream);
 
+/* The same operators behind the calling convention MindSpore uses for ops.Custom(func_type="aot"):
+ *   int f(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream, void* extra)
+ * with params = the inputs followed by the outputs (device pointers), dtypes as MindSpore names them ("float16",
+ * "bfloat16", "float32", "uint8", "bool").  They stand where the reference registers its TBE kernels:
+ *   acct_ms_fa_fwd   ops.Custom(..., func_type="tbe") forward, flash_attention_impl.py:129-154
+ *                    inputs query, key, value, [attn_mask], [dropout_mask], [alibi_mask]; outputs output, rowsum
+ *   acct_ms_fa_grad  the grad primitive, flash_attention_impl.py:96-126
+ *                    inputs query, key, value, output, do, rowsum, [attn_mask], [dropout_mask], [alibi_mask];
+ *                    outputs dq, dk, dv (fp32) and a 1-D uint8 workspace of acct_fa_bwd_workspace_bytes() bytes,
+ *                    declared as a fourth output so that the framework allocates it
+ *   acct_ms_infer_fa FlashAttentionTik(q, k, v) -> y, flash_attention_tik.h:22-27 (rank 3 or 4)
+ * Optional inputs are recognised by rank and shape (rank 3 / 128x128: attn_mask; [B,N,1,S_k]: alibi_mask;
+ * [B,N,S_q,S_k]: dropout_mask).  The attributes the reference bakes into each primitive (band limits; plus the keep
+ * probability for uint8 dropout masks, a scale and an implicit causal mask, which are this library's additions)
+ * are process-wide and set with acct_ms_set_fa_attrs; the defaults are "no band, keep_prob 1, scale 1, not causal". */
+ACCT_API void acct_ms_set_fa_attrs(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal);
+ACCT_API int acct_ms_fa_fwd(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
+                            void* extra);
+ACCT_API int acct_ms_fa_grad(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
+                             void* extra);
+ACCT_API int acct_ms_infer_fa(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
+                              void* extra);
+
 /* Reads and clears the device-side status word of the current device (synchronises `stream`).
  * Returns ACCT_OK, or ACCT_ERR_DEVICE_TIMEOUT if some kernel gave up on a bounded wait since the last call. */
 ACCT_API int acct_device_status(void* stream);
