@@ -14,7 +14,8 @@ LIB_PATH = os.path.join(HERE, "libacct_b200.so")
 ACCT_F16, ACCT_BF16, ACCT_U8, ACCT_F32 = 0, 1, 2, 3
 MASK_NONE, MASK_FULL, MASK_TILE128 = 0, 1, 2
 BAND_UNBOUNDED = 65536
-FLAG_GRAD_F32, FLAG_DETERMINISTIC = 1, 2
+ABI_VERSION = 2       # ACCT_ABI_VERSION of include/acct_b200.h these mirrors were written for
+FLAG_GRAD_F32, FLAG_DETERMINISTIC, FLAG_DROPOUT_PHILOX = 1, 2, 4
 DECODE_STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
 
 ERR_NAMES = {
@@ -27,7 +28,7 @@ EXPORTS = [
     "acct_fa_fwd", "acct_fa_bwd_workspace_bytes", "acct_fa_bwd", "acct_infer_prefill",
     "acct_infer_decode_workspace_bytes", "acct_infer_decode", "acct_infer_decode_static", "acct_device_status",
     "acct_last_error", "acct_abi_version",
-    "acct_ms_set_fa_attrs", "acct_ms_fa_fwd", "acct_ms_fa_grad", "acct_ms_infer_fa",
+    "acct_ms_set_fa_attrs", "acct_ms_fa_fwd", "acct_ms_fa_grad", "acct_ms_infer_fa", "acct_dropout_mask",
 ]
 
 
@@ -54,6 +55,7 @@ class FaArgs(C.Structure):
         ("scale", C.c_float),
         ("seq_lens", C.c_void_p),
         ("flags", C.c_uint32), ("tri_block", C.c_int32),
+        ("dropout_seed", C.c_uint64), ("dropout_offset", C.c_uint64),
     ]
 
 
@@ -115,9 +117,11 @@ def load():
     lib.acct_device_status.restype = C.c_int
     lib.acct_last_error.argtypes = []
     lib.acct_last_error.restype = C.c_char_p
+    lib.acct_dropout_mask.argtypes = [C.POINTER(FaArgs), C.c_void_p, C.c_void_p]
+    lib.acct_dropout_mask.restype = C.c_int
     lib.acct_abi_version.argtypes = []
     lib.acct_abi_version.restype = C.c_int
-    if lib.acct_abi_version() != 1:
+    if lib.acct_abi_version() != ABI_VERSION:
         raise ImportError("libacct_b200.so was built from a different header version")
     _lib = lib
     return lib

@@ -187,9 +187,20 @@ int validate_fa(const acct_fa_args* a, Strides* st, bool backward = false) {
     if (a->dropout_dtype == ACCT_U8 && !(a->keep_prob > 0.f && a->keep_prob <= 1.f))
       return fail(ACCT_ERR_SHAPE, "keep_prob must be in (0, 1]");
   }
+  if (a->flags & ACCT_FLAG_DROPOUT_PHILOX) {
+    if (a->dropout_mask) return fail(ACCT_ERR_SHAPE, "ACCT_FLAG_DROPOUT_PHILOX excludes a dropout_mask tensor");
+    if (!(a->keep_prob > 0.f && a->keep_prob <= 1.f)) return fail(ACCT_ERR_SHAPE, "keep_prob must be in (0, 1]");
+    if (a->dropout_offset >> 32) return fail(ACCT_ERR_SHAPE, "dropout_offset must be below 2^32");
+  }
   if (a->tri_block < 0) return fail(ACCT_ERR_SHAPE, "tri_block must be >= 0");
   if (a->alibi && a->alibi_slopes) return fail(ACCT_ERR_SHAPE, "give either alibi or alibi_slopes, not both");
   return 0;
+}
+
+// round(keep_prob * 256) clamped to [1, 256]: positions whose random byte is below it are kept
+unsigned int dropout_threshold(float keep_prob) {
+  const long t = lroundf(keep_prob * 256.0f);
+  return static_cast<unsigned int>(t < 1 ? 1 : (t > 256 ? 256 : t));
 }
 
 ScoreMods make_mods(const acct_fa_args* a) {
@@ -208,6 +219,17 @@ ScoreMods make_mods(const acct_fa_args* a) {
   m.alibi_slopes = a->alibi_slopes;
   m.seq_lens = a->seq_lens;
   m.tri_block = a->tri_block;
+  m.drop_philox = 0;
+  m.drop_seed_lo = m.drop_seed_hi = m.drop_offset = 0;
+  m.drop_threshold = 256;
+  if ((a->flags & ACCT_FLAG_DROPOUT_PHILOX) && dropout_threshold(a->keep_prob) < 256u) {
+    m.drop_philox = 1;
+    m.drop_seed_lo = static_cast<unsigned int>(a->dropout_seed & 0xffffffffull);
+    m.drop_seed_hi = static_cast<unsigned int>(a->dropout_seed >> 32);
+    m.drop_offset = static_cast<unsigned int>(a->dropout_offset);
+    m.drop_threshold = dropout_threshold(a->keep_prob);
+    m.drop_scale = 256.0f / static_cast<float>(m.drop_threshold);
+  }
   return m;
 }
 
@@ -250,6 +272,20 @@ int acct_device_status(void* stream) {
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     return fail(ACCT_ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded wait (code %u: 1=TMA load, 2=MMA completion, 3=hand-off, 4=shared-memory base misaligned)", host);
   }
+  return ACCT_OK;
+}
+
+int acct_dropout_mask(const acct_fa_args* a, uint8_t* mask, void* stream) {
+  if (a == nullptr || mask == nullptr) return fail(ACCT_ERR_NULL, "acct_dropout_mask: NULL argument");
+  if (a->B <= 0 || a->N <= 0 || a->S_q <= 0 || a->S_k <= 0) return fail(ACCT_ERR_SHAPE, "B, N, S_q, S_k must be positive");
+  if (!(a->keep_prob > 0.f && a->keep_prob <= 1.f)) return fail(ACCT_ERR_SHAPE, "keep_prob must be in (0, 1]");
+  if (a->dropout_offset >> 32) return fail(ACCT_ERR_SHAPE, "dropout_offset must be below 2^32");
+  if (device_status_ptr() == nullptr) return ACCT_ERR_NO_DEVICE;
+  cudaError_t e = launch_dropout_mask(mask, a->B * a->N, a->S_q, a->S_k, static_cast<unsigned int>(a->dropout_seed & 0xffffffffull),
+                                      static_cast<unsigned int>(a->dropout_seed >> 32),
+                                      static_cast<unsigned int>(a->dropout_offset), dropout_threshold(a->keep_prob),
+                                      static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda(e, "launching the dropout mask kernel");
   return ACCT_OK;
 }
 

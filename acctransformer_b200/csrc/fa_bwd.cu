@@ -82,6 +82,30 @@ __device__ __forceinline__ void p_fast(const uint32_t (&s)[32], const float* lse
   }
 }
 
+// Keep bits of in-kernel dropout for one key row and 32 consecutive queries q0 .. q0+31 (bit e = query q0 + e).
+// The generator works on (query, 16 consecutive keys); the 32 lanes of a warp hold 32 consecutive key rows, i.e.
+// two such groups of 16.  Every lane makes the calls of two of the 32 queries for its half-warp's key group and
+// the 16-bit results are handed round by shuffles, so a warp makes 64 calls for its 32 x 32 decisions.
+// All 32 lanes must call this together.
+__device__ __forceinline__ uint32_t philox_keep_column(const ScoreMods& mods, int bh, int q0, int q_max, int kv_idx,
+                                                       int lane) {
+  const DropoutRng rng = {mods.drop_seed_lo, mods.drop_seed_hi, mods.drop_offset, mods.drop_threshold};
+  const uint32_t key16 = static_cast<uint32_t>(kv_idx) >> 4;
+  uint32_t mine[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int q = min(q0 + 2 * (lane & 15) + u, q_max);
+    mine[u] = dropout_keep16(rng, static_cast<uint32_t>(bh), static_cast<uint32_t>(q), key16);
+  }
+  uint32_t bits = 0;
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    const uint32_t m16 = __shfl_sync(0xffffffffu, mine[e & 1], (lane & 16) | (e >> 1));
+    bits |= ((m16 >> (kv_idx & 15)) & 1u) << e;
+  }
+  return bits;
+}
+
 }  // namespace
 
 // GENERIC = mask tensor, dropout mask or triangle row groups may be present; the plain instantiation carries
@@ -371,11 +395,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       const float* dlt = sh.delta[n & 1];
       const bool use_mask = (mods.mask_kind == 1) || (mods.mask_kind == 2 && i == j);
       const bool diag = mods.causal && (q_base < j * kTile + kTile - 1);
-      const bool generic = GENERIC && (use_mask || mods.drop != nullptr || mods.tri_block > 0);
+      const bool dropping = mods.drop != nullptr || mods.drop_philox != 0;
+      const bool generic = GENERIC && (use_mask || dropping || mods.tri_block > 0);
 
       // P^T (dropped) goes over the first 32 of this half's own 64 S^T columns, which the half has
       // finished reading by then.
       float pr[2][32];
+      uint32_t keep_bits[2] = {0xffffffffu, 0xffffffffu};   // in-kernel dropout: bit e = query q0 + e keeps this key
       {
         uint32_t s[2][32];
         tmem_ld32(t_st + (hf * 2) * 32, s[0]);
@@ -438,10 +464,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
               }
             }
             uint32_t pk[16];
-            if (mods.drop != nullptr) {
+            if (dropping) {
               float fac[32];
-              load_col32(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q0, p.S_q - 1, p.S_k, kv_c,
-                         mods.drop_scale, fac);
+              if (mods.drop_philox) {
+                keep_bits[cc] = philox_keep_column(mods, bh, q0, p.S_q - 1, kv_idx, lane);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) fac[e] = ((keep_bits[cc] >> e) & 1u) ? mods.drop_scale : 0.f;
+              } else {
+                load_col32(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q0, p.S_q - 1, p.S_k, kv_c,
+                           mods.drop_scale, fac);
+              }
 #pragma unroll
               for (int e = 0; e < 16; ++e)
                 pk[e] = pack2<BF16>(pr[cc][2 * e] * fac[2 * e], pr[cc][2 * e + 1] * fac[2 * e + 1]);
@@ -469,7 +501,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         for (int cc = 0; cc < 2; ++cc) {
           const int c = hf * 2 + cc;
           uint32_t dk_[16];
-          if (!GENERIC || mods.drop == nullptr) {
+          if (!GENERIC || (mods.drop == nullptr && !mods.drop_philox)) {
 #pragma unroll
             for (int e4 = 0; e4 < 8; ++e4) {
               const float4 Dl = *reinterpret_cast<const float4*>(dlt + c * 32 + 4 * e4);
@@ -482,8 +514,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
             }
           } else if constexpr (GENERIC) {
             float fac[32];
-            load_col32(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q_base + c * 32, p.S_q - 1, p.S_k,
-                       min(kv_idx, p.S_k - 1), mods.drop_scale, fac);
+            if (mods.drop_philox) {   // the keep bits of this chunk were formed in the P part
+#pragma unroll
+              for (int e = 0; e < 32; ++e) fac[e] = ((keep_bits[cc] >> e) & 1u) ? mods.drop_scale : 0.f;
+            } else {
+              load_col32(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q_base + c * 32, p.S_q - 1, p.S_k,
+                         min(kv_idx, p.S_k - 1), mods.drop_scale, fac);
+            }
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
               const float d0 = pr[cc][2 * e] * (__uint_as_float(dp[cc][2 * e]) * fac[2 * e] - dlt[c * 32 + 2 * e]);
@@ -618,7 +655,7 @@ cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : 128;
   const size_t smem = static_cast<size_t>(3 + kStages) * (dpad / 64) * 16384 + 2 * 32768 + sizeof(BwdShared);
   dim3 grid((p.S_k + kTile - 1) / kTile, p.B * p.N);
-  const bool generic = p.mods.mask_kind != 0 || p.mods.drop != nullptr || p.mods.tri_block > 0;
+  const bool generic = p.mods.mask_kind != 0 || p.mods.drop != nullptr || p.mods.drop_philox != 0 || p.mods.tri_block > 0;
   void (*kern)(const BwdParams) = nullptr;
   if (dpad == 64) {
     if (generic) kern = bf16 ? fa_bwd_kernel<64, true, true> : fa_bwd_kernel<64, false, true>;

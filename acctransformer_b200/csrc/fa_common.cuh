@@ -159,4 +159,38 @@ __device__ __forceinline__ void load_col32(const void* base, int dtype, int64_t 
   }
 }
 
+// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11): a counter-based generator,
+// so every (batch*head, query, key) position gets its random byte from its coordinates alone and the forward and
+// the backward reproduce the same dropout mask without storing it.
+__device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    c0 = hi1 ^ c1 ^ k0;
+    c1 = lo1;
+    c2 = hi0 ^ c3 ^ k1;
+    c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return make_uint4(c0, c1, c2, c3);
+}
+
+// In-kernel dropout.  One Philox call, counter (query, key >> 4, batch*heads + head, offset) and key
+// (seed low, seed high), yields 16 bytes; the byte of key position k is byte (k & 15) of the result, taken
+// little-endian from the four words; the position is KEPT iff that byte < threshold, threshold =
+// round(keep_prob * 256).  Bit i of the returned word: position (key16 * 16 + i) is kept.
+struct DropoutRng {
+  uint32_t seed_lo, seed_hi, offset, threshold;
+};
+__device__ __forceinline__ uint32_t dropout_keep16(const DropoutRng& g, uint32_t bh, uint32_t q, uint32_t key16) {
+  const uint4 r = philox4x32_10(q, key16, bh, g.offset, g.seed_lo, g.seed_hi);
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+  uint32_t bits = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) bits |= (((w[i >> 2] >> (8 * (i & 3))) & 0xffu) < g.threshold ? 1u : 0u) << i;
+  return bits;
+}
+
 }  // namespace acct

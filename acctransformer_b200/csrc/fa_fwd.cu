@@ -363,13 +363,23 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       const uint64_t mult2 = f2_pack(mult, mult);
       auto exp_chunk = [&](int c, uint64_t negm2, uint64_t (&l4)[4], uint32_t (&pk)[16]) {
         bool dropped = false;
-        if constexpr (GENERIC) if (mods.drop != nullptr) {
+        if constexpr (GENERIC) if (mods.drop != nullptr || mods.drop_philox) {
           dropped = true;
           const int col0 = col_base + c * 32;
-          const bool drop_vec = col_base + kTile <= p.S_k && (p.S_k & 15) == 0 &&
-                                (reinterpret_cast<uintptr_t>(mods.drop) & 15u) == 0;
           float f[32];
-          load_row32(mods.drop, mods.drop_dtype, drop_row + col0, p.S_k - col0, drop_vec, mods.drop_scale, f);
+          if (mods.drop_philox) {
+            // the mask is computed, not loaded: two generator calls give this row's 32 keep bits of the chunk
+            const DropoutRng rng = {mods.drop_seed_lo, mods.drop_seed_hi, mods.drop_offset, mods.drop_threshold};
+            const uint32_t q_u = static_cast<uint32_t>(min(q_row, p.S_q - 1)), k16 = static_cast<uint32_t>(col0) >> 4;
+            const uint32_t bits = dropout_keep16(rng, static_cast<uint32_t>(bh), q_u, k16) |
+                                  (dropout_keep16(rng, static_cast<uint32_t>(bh), q_u, k16 + 1) << 16);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = ((bits >> i) & 1u) ? mods.drop_scale : 0.f;
+          } else {
+            const bool drop_vec = col_base + kTile <= p.S_k && (p.S_k & 15) == 0 &&
+                                  (reinterpret_cast<uintptr_t>(mods.drop) & 15u) == 0;
+            load_row32(mods.drop, mods.drop_dtype, drop_row + col0, p.S_k - col0, drop_vec, mods.drop_scale, f);
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             float x0, x1;
@@ -515,6 +525,33 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
   }
 }
 
+// One thread per (unit, query, 16 keys): one generator call, 16 mask bytes.
+__global__ void dropout_mask_kernel(unsigned char* mask, int units, int S_q, int S_k, DropoutRng rng) {
+  const int groups = (S_k + 15) / 16;
+  const int64_t total = static_cast<int64_t>(units) * S_q * groups;
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(t % groups);
+    const int64_t row = t / groups;               // unit * S_q + q
+    const int q = static_cast<int>(row % S_q);
+    const int unit = static_cast<int>(row / S_q);
+    const uint32_t bits = dropout_keep16(rng, static_cast<uint32_t>(unit), static_cast<uint32_t>(q), static_cast<uint32_t>(g));
+    unsigned char* dst = mask + row * S_k + g * 16;
+    const int n = min(16, S_k - g * 16);
+    for (int i = 0; i < n; ++i) dst[i] = (bits >> i) & 1u;
+  }
+}
+
+cudaError_t launch_dropout_mask(unsigned char* mask, int units, int S_q, int S_k, unsigned int seed_lo, unsigned int seed_hi,
+                                unsigned int offset, unsigned int threshold, cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(units) * S_q * ((S_k + 15) / 16);
+  const int64_t blocks = (total + 255) / 256;
+  const DropoutRng rng = {seed_lo, seed_hi, offset, threshold};
+  dropout_mask_kernel<<<static_cast<unsigned>(blocks < 148 * 32 ? (blocks < 1 ? 1 : blocks) : 148 * 32), 256, 0, stream>>>(
+      mask, units, S_q, S_k, rng);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : (p.D <= 128 ? 128 : 256);
   const int nq = dpad > 128 ? 1 : 2, stages = dpad > 128 ? 1 : kStages;
@@ -522,7 +559,7 @@ cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
   const int n_pairs = (p.S_q + nq * kTile - 1) / (nq * kTile);
   dim3 grid(static_cast<unsigned>(n_pairs) * static_cast<unsigned>(p.B * p.N));
   const bool generic = p.mods.mask_kind != 0 || p.mods.alibi != nullptr || p.mods.alibi_slopes != nullptr ||
-                       p.mods.drop != nullptr;
+                       p.mods.drop != nullptr || p.mods.drop_philox != 0;
   void (*kern)(const FwdParams) = nullptr;
   if (dpad == 64) {
     if (generic) kern = bf16 ? fa_fwd_kernel<64, true, true> : fa_fwd_kernel<64, false, true>;

@@ -23,6 +23,8 @@ struct ScoreMods {
   const float* alibi_slopes;        // [N]
   const int* seq_lens;              // [B]
   int tri_block;                    // > 0: query row r sees keys < (r / tri_block + 1) * tri_block only
+  int drop_philox;                  // 1: dropout decided in the kernel (DropoutRng), `drop` is null, drop_scale = 256/threshold
+  unsigned int drop_seed_lo, drop_seed_hi, drop_offset, drop_threshold;
 };
 
 struct alignas(64) FwdParams {
@@ -70,6 +72,9 @@ struct DecodeParams {
 // Launchers: return cudaGetLastError() of the launch.
 cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream);
 cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream);
+// writes the {0,1} mask the kernels' in-kernel dropout uses, [units, S_q, S_k] uint8 (units = B*N)
+cudaError_t launch_dropout_mask(unsigned char* mask, int units, int S_q, int S_k, unsigned int seed_lo, unsigned int seed_hi,
+                                unsigned int offset, unsigned int threshold, cudaStream_t stream);
 cudaError_t launch_bwd_delta(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t o_stride_b,
                              int64_t o_stride_h, int64_t o_stride_s, int N, int S_q, bool bf16,
                              cudaStream_t stream);

@@ -59,7 +59,13 @@ class FlashAttention(torch.nn.Module):
         self.alibi = alibi
         self.dp, self.mp = dp, mp
         self.in_strategy = None
-        self.generator = None      # optional torch.Generator (CUDA) for reproducible dropout
+        self.generator = None      # optional torch.Generator for reproducible dropout
+        # The reference draws a [B,N,S,S] mask tensor per step (DropoutGenMask, reference :124-130,198-203) and keeps
+        # it for the backward.  Here the kernels decide dropout from (seed, offset) on the fly; set
+        # dropout_in_kernel = False to get the mask as a tensor instead (same statistics, 1 byte per score).
+        self.dropout_in_kernel = True
+        self._dropout_seed = None
+        self._dropout_step = 0
 
     def shard(self, in_strategy=None, out_strategy=None):
         """Records the split strategy (reference :132-177).  Nothing else to do: the op needs no
@@ -88,11 +94,20 @@ class FlashAttention(torch.nn.Module):
                 "If different head_num are used, users need to change themselves to be same by tile.")
         if alibi_mask is not None and not self.alibi:
             raise ValueError("alibi_mask given but the layer was built with alibi=False")
-        drop_mask = None
+        drop_mask, seed, offset = None, None, 0
         if self.enable_dropout and self.training:
-            drop_mask = (torch.rand((bsz, head_num, seq_len, k.shape[2]), device=q.device,
-                                    generator=self.generator) < self.keep_prob).to(torch.uint8)
-        o, _ = self.flash_attention(q, k, v, attn_mask, drop_mask, alibi_mask, keep_prob=self.keep_prob)
+            if self.dropout_in_kernel:
+                if self._dropout_seed is None:      # one 64-bit seed per layer, drawn from the generator once
+                    gen = self.generator
+                    dev = gen.device if gen is not None else "cpu"
+                    self._dropout_seed = int(torch.randint(0, 2 ** 62, (1,), generator=gen, device=dev).item())
+                seed, offset = self._dropout_seed, self._dropout_step
+                self._dropout_step = (self._dropout_step + 1) % (2 ** 32)
+            else:
+                drop_mask = (torch.rand((bsz, head_num, seq_len, k.shape[2]), device=q.device,
+                                        generator=self.generator) < self.keep_prob).to(torch.uint8)
+        o, _ = self.flash_attention(q, k, v, attn_mask, drop_mask, alibi_mask, keep_prob=self.keep_prob,
+                                    dropout_seed=seed, dropout_offset=offset)
         return o
 
     forward = construct

@@ -43,12 +43,13 @@ def get_flash_attention_grad(prev_block_num=65536, next_block_num=65536, tiling_
     at some cost in speed; dk and dv always are."""
 
     def fa_grad(query, key, value, output, do, rowsum, attn_mask=None, dropout_mask=None, alibi_mask=None,
-                keep_prob=1.0, grads_fp32=True):
+                keep_prob=1.0, grads_fp32=True, dropout_seed=None, dropout_offset=0):
         return _ops.fa_backward(query, key, value, output, rowsum, do, attn_mask,
                                 mask_tile128=_is_tile_mask(attn_mask), causal=causal,
                                 dropout_mask=dropout_mask, keep_prob=keep_prob, alibi=alibi_mask,
                                 prev_block_num=prev_block_num, next_block_num=next_block_num, scale=scale,
-                                grads_fp32=grads_fp32, deterministic=deterministic)
+                                grads_fp32=grads_fp32, deterministic=deterministic,
+                                dropout_seed=dropout_seed, dropout_offset=dropout_offset)
 
     fa_grad.prev_block_num = prev_block_num
     fa_grad.next_block_num = next_block_num
@@ -63,7 +64,8 @@ class _FlashAttentionFunction(torch.autograd.Function):
             query, key, value, attn_mask, mask_tile128=_is_tile_mask(attn_mask), causal=cfg["causal"],
             dropout_mask=dropout_mask, keep_prob=cfg["keep_prob"], alibi=alibi_mask,
             prev_block_num=cfg["prev_block_num"], next_block_num=cfg["next_block_num"], scale=cfg["scale"],
-            tri_block=cfg.get("tri_block", 0))
+            tri_block=cfg.get("tri_block", 0), dropout_seed=cfg.get("dropout_seed"),
+            dropout_offset=cfg.get("dropout_offset", 0))
         ctx.save_for_backward(query, key, value, output, rowsum,
                               *(t for t in (attn_mask, dropout_mask, alibi_mask) if t is not None))
         ctx.present = (attn_mask is not None, dropout_mask is not None, alibi_mask is not None)
@@ -86,7 +88,8 @@ class _FlashAttentionFunction(torch.autograd.Function):
             mask_tile128=_is_tile_mask(attn_mask), causal=cfg["causal"], dropout_mask=dropout_mask,
             keep_prob=cfg["keep_prob"], alibi=alibi_mask, prev_block_num=cfg["prev_block_num"],
             next_block_num=cfg["next_block_num"], scale=cfg["scale"], grads_fp32=False,
-            tri_block=cfg.get("tri_block", 0), deterministic=cfg.get("deterministic", False))
+            tri_block=cfg.get("tri_block", 0), deterministic=cfg.get("deterministic", False),
+            dropout_seed=cfg.get("dropout_seed"), dropout_offset=cfg.get("dropout_offset", 0))
         return dq, dk, dv, None, None, None, None
 
 
@@ -95,9 +98,13 @@ def get_flash_attention(prev_block_num=65536, next_block_num=65536, tiling_stgy_
     """Returns the forward primitive.  ``scale`` (default 1: the raw primitive) and ``causal``
     (an in-kernel triangle that needs no mask tensor) are this library's additions."""
 
-    def fa_forward(query, key, value, attn_mask=None, dropout_mask=None, alibi_mask=None, keep_prob=1.0):
+    def fa_forward(query, key, value, attn_mask=None, dropout_mask=None, alibi_mask=None, keep_prob=1.0,
+                   dropout_seed=None, dropout_offset=0):
+        # dropout_seed / dropout_offset: dropout decided inside the kernels (no mask tensor); the backward that
+        # autograd runs later reuses the same two values
         cfg = dict(prev_block_num=prev_block_num, next_block_num=next_block_num, scale=scale, causal=causal,
-                   keep_prob=keep_prob, deterministic=deterministic)
+                   keep_prob=keep_prob, deterministic=deterministic, dropout_seed=dropout_seed,
+                   dropout_offset=dropout_offset)
         return _FlashAttentionFunction.apply(query, key, value, attn_mask, dropout_mask, alibi_mask, cfg)
 
     fa_forward.prev_block_num = prev_block_num

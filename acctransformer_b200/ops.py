@@ -9,7 +9,7 @@ import math
 import torch
 
 from . import _lib
-from ._lib import (ACCT_BF16, ACCT_F16, ACCT_U8, BAND_UNBOUNDED, FLAG_DETERMINISTIC, FLAG_GRAD_F32, MASK_FULL, MASK_NONE,
+from ._lib import (ACCT_BF16, ACCT_F16, ACCT_U8, BAND_UNBOUNDED, FLAG_DETERMINISTIC, FLAG_DROPOUT_PHILOX, FLAG_GRAD_F32, MASK_FULL, MASK_NONE,
                    MASK_TILE128, DecodeArgs, FaArgs, FaBwdIO, InferArgs, check, load)
 
 _DTYPES = {torch.float16: ACCT_F16, torch.bfloat16: ACCT_BF16, torch.uint8: ACCT_U8, torch.bool: ACCT_U8}
@@ -37,7 +37,8 @@ def _strides3(t):
 
 
 def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
-                  alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, flags=0, tri_block=0):
+                  alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, flags=0, tri_block=0,
+                  dropout_seed=None, dropout_offset=0):
     for name, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda(name, t)
         if t.dim() != 4:
@@ -104,6 +105,12 @@ def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask
         sl = seq_lens.to(torch.int32).contiguous()
         keep.append(sl)
         a.seq_lens = sl.data_ptr()
+    if dropout_seed is not None:
+        if dropout_mask is not None:
+            raise ValueError("give either dropout_mask (tensor form) or dropout_seed (in-kernel form), not both")
+        flags |= FLAG_DROPOUT_PHILOX
+        a.dropout_seed = int(dropout_seed) & 0xFFFFFFFFFFFFFFFF
+        a.dropout_offset = int(dropout_offset)
     a.flags = flags
     a.tri_block = int(tri_block)
     return a, keep
@@ -111,13 +118,19 @@ def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask
 
 def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dropout_mask=None,
                keep_prob=1.0, alibi=None, alibi_slopes=None, prev_block_num=BAND_UNBOUNDED,
-               next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None, need_lse=True, tri_block=0):
-    """Forward primitive: returns (output [B,N,S_q,D] in q's dtype, lse [B,N,S_q] fp32 or None)."""
+               next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None, need_lse=True, tri_block=0,
+               dropout_seed=None, dropout_offset=0):
+    """Forward primitive: returns (output [B,N,S_q,D] in q's dtype, lse [B,N,S_q] fp32 or None).
+
+    Dropout comes either as a tensor (``dropout_mask`` + ``keep_prob``) or is decided inside the kernel from
+    ``dropout_seed`` / ``dropout_offset`` + ``keep_prob`` (no [B,N,S_q,S_k] tensor exists then; the backward must
+    be given the same three values)."""
     lib = load()
     o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if need_lse else None
     a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
-                            alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, tri_block=tri_block)
+                            alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, tri_block=tri_block,
+                            dropout_seed=dropout_seed, dropout_offset=dropout_offset)
     with torch.cuda.device(q.device):
         check(lib.acct_fa_fwd(C.byref(a), _stream()))
     del keep
@@ -127,7 +140,7 @@ def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dro
 def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, causal=False,
                 dropout_mask=None, keep_prob=1.0, alibi=None, alibi_slopes=None,
                 prev_block_num=BAND_UNBOUNDED, next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None,
-                grads_fp32=False, tri_block=0, deterministic=False):
+                grads_fp32=False, tri_block=0, deterministic=False, dropout_seed=None, dropout_offset=0):
     """Grad primitive: returns (dq, dk, dv), fp32 when ``grads_fp32`` (what the reference primitive
     returns) else in q's dtype (what its bprop hands back after the cast)."""
     lib = load()
@@ -145,7 +158,7 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
     a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
                             alibi_slopes, prev_block_num, next_block_num, scale, seq_lens,
                             flags=(FLAG_GRAD_F32 if grads_fp32 else 0) | (FLAG_DETERMINISTIC if deterministic else 0),
-                            tri_block=tri_block)
+                            tri_block=tri_block, dropout_seed=dropout_seed, dropout_offset=dropout_offset)
     nbytes = lib.acct_fa_bwd_workspace_bytes(C.byref(a))
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     g = FaBwdIO()
@@ -155,6 +168,22 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
         check(lib.acct_fa_bwd(C.byref(a), C.byref(g), _stream()))
     del keep
     return dq, dk, dv
+
+
+def dropout_mask(B, N, S_q, S_k, keep_prob, dropout_seed, dropout_offset=0, device="cuda"):
+    """The uint8 {0,1} mask [B,N,S_q,S_k] that in-kernel dropout with these values uses (for checks, or for a caller
+    that wants the tensor form)."""
+    lib = load()
+    dev = torch.device(device)
+    mask = torch.empty((B, N, S_q, S_k), dtype=torch.uint8, device=dev)
+    a = FaArgs()
+    a.B, a.N, a.S_q, a.S_k = B, N, S_q, S_k
+    a.keep_prob = float(keep_prob)
+    a.dropout_seed = int(dropout_seed) & 0xFFFFFFFFFFFFFFFF
+    a.dropout_offset = int(dropout_offset)
+    with torch.cuda.device(dev):
+        check(lib.acct_dropout_mask(C.byref(a), mask.data_ptr(), _stream()))
+    return mask
 
 
 def infer_prefill(q, k, v, *, causal=False, scale=1.0, seq_lens=None):

@@ -40,6 +40,9 @@ class TriangleAttention(torch.nn.Module):
         self.dp, self.mp = dp, mp
         self.assume_causal = assume_causal
         self.generator = None
+        self.dropout_in_kernel = True   # dropout decided inside the kernels from (seed, step); False: a mask tensor
+        self._dropout_seed = None
+        self._dropout_step = 0
 
     def tiles_skipped_fraction(self, seq_length):
         """Fraction of the 128x128 score tiles the kernel never touches for this sequence length."""
@@ -55,15 +58,24 @@ class TriangleAttention(torch.nn.Module):
 
     def construct(self, query, key, value, attention_mask):
         bsz, head_num, seq_length, _ = query.shape
-        drop_mask = None
+        drop_mask, seed, offset = None, None, 0
         if self.enable_dropout and self.training:
-            drop_mask = (torch.rand((bsz, head_num, seq_length, key.shape[2]), device=query.device,
-                                    generator=self.generator) < self.keep_prob).to(torch.uint8)
+            if self.dropout_in_kernel:
+                if self._dropout_seed is None:
+                    gen = self.generator
+                    dev = gen.device if gen is not None else "cpu"
+                    self._dropout_seed = int(torch.randint(0, 2 ** 62, (1,), generator=gen, device=dev).item())
+                seed, offset = self._dropout_seed, self._dropout_step
+                self._dropout_step = (self._dropout_step + 1) % (2 ** 32)
+            else:
+                drop_mask = (torch.rand((bsz, head_num, seq_length, key.shape[2]), device=query.device,
+                                        generator=self.generator) < self.keep_prob).to(torch.uint8)
         # tri_block: a query row in group g sees keys [0, (g+1)*block_size) only, as in the reference's slices;
         # inside that range the mask tensor decides (or the in-kernel triangle when assume_causal).
         # (under the in-kernel triangle the group bound excludes nothing more, so it is not passed)
         cfg = dict(prev_block_num=65536, next_block_num=65536, scale=1.0, causal=self.assume_causal,
-                   keep_prob=self.keep_prob, tri_block=0 if self.assume_causal else self.block_size)
+                   keep_prob=self.keep_prob, tri_block=0 if self.assume_causal else self.block_size,
+                   dropout_seed=seed, dropout_offset=offset)
         mask = None if self.assume_causal else attention_mask
         out, _ = _FlashAttentionFunction.apply(query, key, value, mask, drop_mask, None, cfg)
         return out

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define ACCT_ABI_VERSION 1
+#define ACCT_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define ACCT_API __attribute__((visibility("default")))
@@ -69,6 +69,9 @@ extern "C" {
 #define ACCT_FLAG_GRAD_F32 1u      /* acct_fa_bwd writes dq/dk/dv as fp32 (what the reference primitive returns) */
 #define ACCT_FLAG_DETERMINISTIC 2u /* acct_fa_bwd adds the dq contributions of the K/V tiles in a fixed order, so that
                                       dq is bit-identical from run to run (dk, dv and the forward always are) */
+
+#define ACCT_FLAG_DROPOUT_PHILOX 4u /* dropout decided inside the kernels from (dropout_seed, dropout_offset): no
+                                      [B,N,S_q,S_k] mask tensor exists; dropout_mask must be NULL.  See acct_dropout_mask */
 
 /* Arguments shared by the training forward and backward.
  *
@@ -118,6 +121,8 @@ typedef struct acct_fa_args {
   int32_t tri_block;        /* 0 = off.  > 0: TriangleAttention row groups of this many query rows; a query row in
                                group g sees keys [0, min(S_k, (g+1)*tri_block)) only -- the keys the reference slices in
                                for that group (train/acctransformer/triangle_attention/triangle_attention.py:137-163) */
+  uint64_t dropout_seed;    /* ACCT_FLAG_DROPOUT_PHILOX: key of the generator */
+  uint64_t dropout_offset;  /* ACCT_FLAG_DROPOUT_PHILOX: below 2^32; a caller advances it from step to step */
 } acct_fa_args;
 
 /* Extra I/O of the backward.
@@ -138,6 +143,17 @@ typedef struct acct_fa_bwd_io {
   void* workspace;          /* device, >= acct_fa_bwd_workspace_bytes(); contents undefined on entry */
   size_t workspace_bytes;
 } acct_fa_bwd_io;
+
+/* In-kernel dropout (ACCT_FLAG_DROPOUT_PHILOX) replaces the mask tensor the reference cell generates and keeps in
+ * memory for the backward (DropoutGenMask / DropoutDoMask, nn/layer/flash_attention.py:124-130,198-203; 4.3 GB at
+ * B=2 N=32 S=8192).  The mask is a pure function of the position:
+ *   r = Philox4x32-10(counter = (query, key >> 4, b*N + n, dropout_offset), key = (seed & 0xffffffff, seed >> 32))
+ *   byte = byte (key & 15) of the 16 bytes r[0..3], little-endian;   kept  iff  byte < T,  T = round(keep_prob*256)
+ * and kept probabilities are multiplied by 256/T, so the effective keep probability is T/256 (keep_prob is
+ * quantised to 1/256; T is clamped to [1, 256]).  acct_dropout_mask writes exactly that mask as a packed uint8
+ * {0,1} tensor [B,N,S_q,S_k] (reads B, N, S_q, S_k, keep_prob, dropout_seed, dropout_offset of `a` only): with it,
+ * the tensor form (dropout_mask = that tensor, dropout_dtype = ACCT_U8, keep_prob = T/256) gives the same results. */
+ACCT_API int acct_dropout_mask(const acct_fa_args* a, uint8_t* mask, void* stream);
 
 /* Forward: writes o and (if non-NULL) lse. */
 ACCT_API int acct_fa_fwd(const acct_fa_args* a, void* stream);

@@ -265,3 +265,51 @@ def data_compare(ground_truth, predict, rtol=0.001, rtol_pct_thd=0.001, atol=0.0
     p2 = np.sum(diff > max_rtol * np.abs(gt) + atol) / total
     ok = not (p1 > rtol_pct_thd or p2 > 0)
     return ("Pass" if ok else "Failed"), float(p1), float(p2)
+
+
+# ----------------------------------------------------------------------------------------------
+# In-kernel dropout: the mask as a function of the position
+# ----------------------------------------------------------------------------------------------
+# No counterpart in the reference, whose cell draws the mask with MindSpore's DropoutGenMask
+# (nn/layer/flash_attention.py:124-130,198-203) and keeps the tensor for the backward.  The
+# generator is Philox4x32-10 (Salmon, Moraes, Dror, Shaw, "Parallel random numbers: as easy as
+# 1, 2, 3", SC'11), restated here from the paper; it is pinned by the known-answer vectors the
+# authors publish with their Random123 library (tests/test_dropout_philox.py).
+_PHILOX_M0, _PHILOX_M1 = 0xD2511F53, 0xCD9E8D57
+_PHILOX_W0, _PHILOX_W1 = 0x9E3779B9, 0xBB67AE85
+
+
+def philox4x32_10(ctr, key):
+    """ctr: four uint32 arrays (broadcastable), key: two uint32 scalars.  Returns four uint32 arrays."""
+    c = [np.asarray(x, dtype=np.uint64) for x in ctr]
+    k0, k1 = np.uint64(key[0]), np.uint64(key[1])
+    lo32 = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0 = np.uint64(_PHILOX_M0) * c[0]
+        p1 = np.uint64(_PHILOX_M1) * c[2]
+        c = [(p1 >> np.uint64(32)) ^ c[1] ^ k0, p1 & lo32, (p0 >> np.uint64(32)) ^ c[3] ^ k1, p0 & lo32]
+        k0 = (k0 + np.uint64(_PHILOX_W0)) & lo32
+        k1 = (k1 + np.uint64(_PHILOX_W1)) & lo32
+    return [x.astype(np.uint32) for x in c]
+
+
+def dropout_threshold(keep_prob):
+    """round(keep_prob * 256) clamped to [1, 256] (float32 arithmetic, ties away from zero like lroundf)."""
+    t = int(np.floor(np.float32(keep_prob) * np.float32(256.0) + np.float32(0.5)))
+    return min(256, max(1, t))
+
+
+def dropout_mask_philox(B, N, S_q, S_k, keep_prob, seed, offset=0):
+    """uint8 {0,1} mask [B,N,S_q,S_k]: position (b,n,q,k) is kept iff byte (k & 15) of
+    Philox(counter = (q, k >> 4, b*N + n, offset), key = (seed low, seed high)) is below the threshold."""
+    groups = (S_k + 15) // 16
+    q = np.arange(S_q, dtype=np.uint32).reshape(1, S_q, 1)
+    g = np.arange(groups, dtype=np.uint32).reshape(1, 1, groups)
+    u = np.arange(B * N, dtype=np.uint32).reshape(B * N, 1, 1)
+    shape = (B * N, S_q, groups)
+    words = philox4x32_10([np.broadcast_to(q, shape), np.broadcast_to(g, shape), np.broadcast_to(u, shape),
+                           np.full(shape, offset & 0xFFFFFFFF, dtype=np.uint32)],
+                          (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))
+    by = np.stack([(w >> np.uint32(8 * i)) & np.uint32(0xFF) for w in words for i in range(4)], axis=-1)  # [..., 16]
+    keep = (by < dropout_threshold(keep_prob)).astype(np.uint8).reshape(B * N, S_q, groups * 16)[:, :, :S_k]
+    return np.ascontiguousarray(keep.reshape(B, N, S_q, S_k))

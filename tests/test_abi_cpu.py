@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol(lib):
         assert hasattr(lib, name), name
     assert sorted(set(declared)) == sorted(set(_lib.EXPORTS) | (set(declared) - set(_lib.EXPORTS)))
     assert set(_lib.EXPORTS) <= set(declared)
-    assert lib.acct_abi_version() == 1
+    assert lib.acct_abi_version() == 2
 
 
 def test_ctypes_mirrors_match_c_layout(tmp_path):
@@ -38,7 +38,7 @@ def test_ctypes_mirrors_match_c_layout(tmp_path):
     fields = {
         "acct_fa_args": ["dtype", "q", "lse", "q_stride", "o_stride", "mask_kind", "attn_mask", "dropout_mask",
                          "dropout_dtype", "keep_prob", "alibi", "alibi_slopes", "prev_block_num", "scale",
-                         "seq_lens", "flags", "tri_block"],
+                         "seq_lens", "flags", "tri_block", "dropout_seed", "dropout_offset"],
         "acct_fa_bwd_io": ["d_o", "dq", "workspace", "workspace_bytes"],
         "acct_infer_args": ["dtype", "rank", "D", "q", "y", "causal", "scale", "seq_lens"],
         "acct_decode_args": ["dtype", "D", "q", "kv_stride", "seq_lens", "y", "scale", "num_splits", "workspace",
