@@ -55,7 +55,7 @@ class FaArgs(C.Structure):
         ("scale", C.c_float),
         ("seq_lens", C.c_void_p),
         ("flags", C.c_uint32), ("tri_block", C.c_int32),
-        ("dropout_seed", C.c_uint64), ("dropout_offset", C.c_uint64),
+        ("dropout_seed", C.c_uint64), ("dropout_offset", C.c_uint64), ("N_kv", C.c_int32),
     ]
 
 
@@ -71,7 +71,7 @@ class InferArgs(C.Structure):
         ("dtype", C.c_int32), ("rank", C.c_int32), ("B", C.c_int32), ("N", C.c_int32), ("S_q", C.c_int32),
         ("S_k", C.c_int32), ("D", C.c_int32),
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("y", C.c_void_p),
-        ("causal", C.c_int32), ("scale", C.c_float), ("seq_lens", C.c_void_p),
+        ("causal", C.c_int32), ("scale", C.c_float), ("seq_lens", C.c_void_p), ("N_kv", C.c_int32),
     ]
 
 
@@ -82,7 +82,7 @@ class DecodeArgs(C.Structure):
         ("kv_stride", C.c_int64 * 3),
         ("seq_lens", C.c_void_p), ("y", C.c_void_p),
         ("scale", C.c_float), ("num_splits", C.c_int32),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("N_kv", C.c_int32),
     ]
 
 

@@ -152,6 +152,9 @@ struct Strides {
   int64_t q[3], k[3], v[3], o[3];
 };
 
+// heads of k / v: one per query head unless the caller groups them
+int kv_heads(const acct_fa_args* a) { return a->N_kv > 0 ? a->N_kv : a->N; }
+
 int validate_fa(const acct_fa_args* a, Strides* st, bool backward = false) {
   if (a == nullptr) return fail(ACCT_ERR_NULL, "args is NULL");
   if (a->dtype != ACCT_F16 && a->dtype != ACCT_BF16) return fail(ACCT_ERR_DTYPE, "dtype must be ACCT_F16 or ACCT_BF16");
@@ -163,8 +166,11 @@ int validate_fa(const acct_fa_args* a, Strides* st, bool backward = false) {
   if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o))
     return fail(ACCT_ERR_ALIGN, "q, k, v, o must be 16-byte aligned");
   if ((rc = check_strides("q", a->q_stride, a->S_q, a->N, a->D, st->q))) return rc;
-  if ((rc = check_strides("k", a->k_stride, a->S_k, a->N, a->D, st->k))) return rc;
-  if ((rc = check_strides("v", a->v_stride, a->S_k, a->N, a->D, st->v))) return rc;
+  if (a->N_kv < 0 || (a->N_kv > 0 && a->N % a->N_kv != 0))
+    return fail(ACCT_ERR_SHAPE, "N_kv = %d must be 0 or a divisor of N = %d", a->N_kv, a->N);
+  const int n_kv = kv_heads(a);
+  if ((rc = check_strides("k", a->k_stride, a->S_k, n_kv, a->D, st->k))) return rc;
+  if ((rc = check_strides("v", a->v_stride, a->S_k, n_kv, a->D, st->v))) return rc;
   if ((rc = check_strides("o", a->o_stride, a->S_q, a->N, a->D, st->o))) return rc;
   if (!(a->scale > 0.f) || !(a->scale < 1e30f)) return fail(ACCT_ERR_SHAPE, "scale must be a positive finite number");
   if (a->prev_block_num < 0 || a->next_block_num < 0) return fail(ACCT_ERR_SHAPE, "prev/next_block_num must be >= 0");
@@ -240,7 +246,7 @@ int make_qkv_maps(const acct_fa_args* a, const Strides& st, CUtensorMap* mq, CUt
   t.ptr = a->q; t.dims[0] = a->D; t.dims[1] = a->S_q; t.dims[2] = a->N; t.dims[3] = a->B;
   t.strides[0] = st.q[2]; t.strides[1] = st.q[1]; t.strides[2] = st.q[0];
   if ((rc = make_tmap_4d(mq, t, kTile))) return rc;
-  t.ptr = a->k; t.dims[1] = a->S_k;
+  t.ptr = a->k; t.dims[1] = a->S_k; t.dims[2] = kv_heads(a);
   t.strides[0] = st.k[2]; t.strides[1] = st.k[1]; t.strides[2] = st.k[0];
   if ((rc = make_tmap_4d(mk, t, kTile))) return rc;
   t.ptr = a->v;
@@ -309,6 +315,7 @@ int acct_fa_fwd(const acct_fa_args* a, void* stream) {
   p.lse = a->lse;
   p.o_stride_b = st.o[0]; p.o_stride_h = st.o[1]; p.o_stride_s = st.o[2];
   p.B = a->B; p.N = a->N; p.S_q = a->S_q; p.S_k = a->S_k; p.D = a->D;
+  p.kv_group = a->N / kv_heads(a);
   p.scale_log2 = a->scale * kLog2e;
   p.mods = make_mods(a);
   p.status = status;
@@ -373,6 +380,7 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   p.dk = g->dk; p.dv = g->dv;
   p.grads_f32 = (a->flags & ACCT_FLAG_GRAD_F32) ? 1 : 0;
   p.B = a->B; p.N = a->N; p.S_q = a->S_q; p.S_k = a->S_k; p.D = a->D;
+  p.kv_group = a->N / kv_heads(a);
   p.scale = a->scale; p.scale_log2 = a->scale * kLog2e;
   p.mods = make_mods(a);
   p.status = status;
@@ -403,6 +411,7 @@ int acct_infer_prefill(const acct_infer_args* a, void* stream) {
   f.scale = a->scale;
   f.seq_lens = a->seq_lens;
   f.keep_prob = 1.0f;
+  f.N_kv = a->N_kv;
   return acct_fa_fwd(&f, stream);
 }
 
@@ -422,8 +431,14 @@ int acct_infer_decode(const acct_decode_args* a, void* stream) {
   if (!aligned16(a->q) || !aligned16(a->k_cache) || !aligned16(a->v_cache) || !aligned16(a->y))
     return fail(ACCT_ERR_ALIGN, "q, k_cache, v_cache, y must be 16-byte aligned");
   if (!(a->scale > 0.f)) return fail(ACCT_ERR_SHAPE, "scale must be positive");
+  if (a->N_kv < 0 || (a->N_kv > 0 && a->N % a->N_kv != 0))
+    return fail(ACCT_ERR_SHAPE, "N_kv = %d must be 0 or a divisor of N = %d", a->N_kv, a->N);
+  const int n_kv = a->N_kv > 0 ? a->N_kv : a->N;
+  const int group = a->N / n_kv;
+  if (group != 1 && group != 2 && group != 4 && group != 8)
+    return fail(ACCT_ERR_SHAPE, "decode takes N / N_kv in {1, 2, 4, 8}, got %d", group);
   int64_t kvs[3];
-  int rc = check_strides("kv", a->kv_stride, a->S_max, a->N, a->D, kvs);
+  int rc = check_strides("kv", a->kv_stride, a->S_max, n_kv, a->D, kvs);
   if (rc) return rc;
   int splits = a->num_splits;
   if (splits < 0 || splits > 64) return fail(ACCT_ERR_SHAPE, "num_splits must be in [0, 64]");
@@ -432,7 +447,7 @@ int acct_infer_decode(const acct_decode_args* a, void* stream) {
   if ((rc = device_info(&info))) return rc;
   if (splits == 0) {
     // enough CTAs for ~4 waves of 2 resident CTAs per SM, but never splits shorter than 256 keys
-    const int64_t units = static_cast<int64_t>(a->B) * a->N;
+    const int64_t units = static_cast<int64_t>(a->B) * n_kv;
     int64_t want = (static_cast<int64_t>(info.sm_count) * 8 + units - 1) / units;
     int64_t cap = (a->S_max + 255) / 256;
     splits = static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
@@ -449,6 +464,7 @@ int acct_infer_decode(const acct_decode_args* a, void* stream) {
   p.part_ml = p.part_acc + static_cast<size_t>(a->B) * a->N * splits * a->D;
   p.kv_stride_b = kvs[0]; p.kv_stride_h = kvs[1]; p.kv_stride_s = kvs[2];
   p.B = a->B; p.N = a->N; p.S_max = a->S_max; p.D = a->D;
+  p.kv_group = group;
   p.splits = splits;
   p.scale_log2 = a->scale * kLog2e;
   cudaError_t e = launch_decode(p, a->dtype == ACCT_BF16, static_cast<cudaStream_t>(stream));

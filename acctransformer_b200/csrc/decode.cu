@@ -52,19 +52,23 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   }
 }
 
-template <int LPR, bool BF16>
+// G = query heads per key/value head (grouped-query attention): the G heads of a group share one pass over their
+// cache rows, so the cache is read once per group instead of once per query head.
+template <int LPR, bool BF16, int G>
 __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const DecodeParams p) {
   constexpr int RPW = 32 / LPR;                 // cache rows per warp per load instruction
   constexpr int kWarps = kDecodeThreads / 32;
-  constexpr int kGroups = kWarps * RPW;         // independent softmax states per CTA
+  constexpr int kGroups = kWarps * RPW;         // independent softmax states per CTA and query head
   constexpr int DMAX = LPR * 8;
+  constexpr int kCh = G >= 4 ? kChunk / 2 : kChunk;   // fewer loads in flight when G heads of state are held
 
-  __shared__ float s_m[kGroups], s_l[kGroups];
-  __shared__ float s_acc[kGroups][DMAX];
+  __shared__ float s_m[G][kGroups], s_l[G][kGroups];
+  __shared__ float s_acc[G][kGroups][DMAX];
 
   const int split = blockIdx.x;
-  const int unit = blockIdx.y;
-  const int b = unit / p.N, h = unit % p.N;
+  const int n_kv = p.N / G;
+  const int unit_kv = blockIdx.y;               // (batch, key/value head)
+  const int b = unit_kv / n_kv, h_kv = unit_kv % n_kv;
   int len = p.S_max;
   if (p.seq_lens != nullptr) len = min(p.S_max, max(0, p.seq_lens[b]));
   const int per = (((len + p.splits - 1) / p.splits) + 63) & ~63;
@@ -76,93 +80,116 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
   const int dcol = sub * 8;
   const bool active = dcol < p.D;
 
-  float qf[8];
-  {
+  float qf[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const int64_t unit = static_cast<int64_t>(b) * p.N + h_kv * G + g;
     uint4 qu = make_uint4(0, 0, 0, 0);
-    if (active) qu = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + static_cast<int64_t>(unit) * p.D + dcol);
-    unpack8<BF16>(qu, qf);
+    if (active) qu = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + unit * p.D + dcol);
+    unpack8<BF16>(qu, qf[g]);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) qf[e] *= p.scale_log2;
+    for (int e = 0; e < 8; ++e) qf[g][e] *= p.scale_log2;
   }
-  const uint16_t* kbase = reinterpret_cast<const uint16_t*>(p.k) + b * p.kv_stride_b + h * p.kv_stride_h + dcol;
-  const uint16_t* vbase = reinterpret_cast<const uint16_t*>(p.v) + b * p.kv_stride_b + h * p.kv_stride_h + dcol;
+  const uint16_t* kbase = reinterpret_cast<const uint16_t*>(p.k) + b * p.kv_stride_b + h_kv * p.kv_stride_h + dcol;
+  const uint16_t* vbase = reinterpret_cast<const uint16_t*>(p.v) + b * p.kv_stride_b + h_kv * p.kv_stride_h + dcol;
 
-  float m = -INFINITY, l = 0.f;
-  float acc[8];
+  float m[G], l[G];
+  float acc[G][8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+  }
 
-  for (int row0 = k0 + warp * (RPW * kChunk); row0 < k1; row0 += kWarps * RPW * kChunk) {
-    uint4 ku[kChunk], vu[kChunk];
+  for (int row0 = k0 + warp * (RPW * kCh); row0 < k1; row0 += kWarps * RPW * kCh) {
+    uint4 ku[kCh], vu[kCh];
 #pragma unroll
-    for (int i = 0; i < kChunk; ++i) {
+    for (int i = 0; i < kCh; ++i) {
       const int row = row0 + i * RPW + rsub;
       ku[i] = (active && row < k1) ? ld_stream(kbase + static_cast<int64_t>(row) * p.kv_stride_s) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int i = 0; i < kChunk; ++i) {
+    for (int i = 0; i < kCh; ++i) {
       const int row = row0 + i * RPW + rsub;
       vu[i] = (active && row < k1) ? ld_stream(vbase + static_cast<int64_t>(row) * p.kv_stride_s) : make_uint4(0, 0, 0, 0);
     }
-    float s[kChunk];
-    float cmax = -INFINITY;
+    float s[G][kCh];
+    float cmax[G];
 #pragma unroll
-    for (int i = 0; i < kChunk; ++i) {
+    for (int g = 0; g < G; ++g) cmax[g] = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kCh; ++i) {
       float kf[8];
       unpack8<BF16>(ku[i], kf);
-      float d = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) d = fmaf(kf[e], qf[e], d);
-#pragma unroll
-      for (int off = 1; off < LPR; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
       const int row = row0 + i * RPW + rsub;
-      s[i] = row < k1 ? d : -INFINITY;
-      cmax = fmaxf(cmax, s[i]);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d = fmaf(kf[e], qf[g][e], d);
+#pragma unroll
+        for (int off = 1; off < LPR; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        s[g][i] = row < k1 ? d : -INFINITY;
+        cmax[g] = fmaxf(cmax[g], s[g][i]);
+      }
     }
-    const float m_new = fmaxf(m, cmax);
-    if (m_new != -INFINITY) {
-      const float alpha = ex2(m - m_new);   // m = -inf gives 0
-      l *= alpha;
+    float vf[kCh][8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] *= alpha;
-      m = m_new;
+    for (int i = 0; i < kCh; ++i) unpack8<BF16>(vu[i], vf[i]);
 #pragma unroll
-      for (int i = 0; i < kChunk; ++i) {
-        const float pr = ex2(s[i] - m);
-        l += pr;
-        float vf[8];
-        unpack8<BF16>(vu[i], vf);
+    for (int g = 0; g < G; ++g) {
+      const float m_new = fmaxf(m[g], cmax[g]);
+      if (m_new != -INFINITY) {
+        const float alpha = ex2(m[g] - m_new);   // m = -inf gives 0
+        l[g] *= alpha;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = fmaf(pr, vf[e], acc[e]);
+        for (int e = 0; e < 8; ++e) acc[g][e] *= alpha;
+        m[g] = m_new;
+#pragma unroll
+        for (int i = 0; i < kCh; ++i) {
+          const float pr = ex2(s[g][i] - m_new);
+          l[g] += pr;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pr, vf[i][e], acc[g][e]);
+        }
       }
     }
   }
 
-  // merge the CTA's groups
-  const int g = warp * RPW + rsub;
-  if (sub == 0) { s_m[g] = m; s_l[g] = l; }
+  // merge the CTA's groups, per query head
+  const int grp = warp * RPW + rsub;
 #pragma unroll
-  for (int e = 0; e < 8; ++e) s_acc[g][dcol + e] = acc[e];
-  __syncthreads();
-  const int64_t slot = static_cast<int64_t>(unit) * p.splits + split;
-  float big = -INFINITY;
+  for (int g = 0; g < G; ++g) {
+    if (sub == 0) { s_m[g][grp] = m[g]; s_l[g][grp] = l[g]; }
 #pragma unroll
-  for (int i = 0; i < kGroups; ++i) big = fmaxf(big, s_m[i]);
-  for (int t = threadIdx.x; t < p.D; t += kDecodeThreads) {
-    float a = 0.f;
-#pragma unroll
-    for (int i = 0; i < kGroups; ++i) {
-      const float w = (s_m[i] == -INFINITY) ? 0.f : ex2(s_m[i] - big);
-      a = fmaf(s_acc[i][t], w, a);
-    }
-    p.part_acc[slot * p.D + t] = a;
+    for (int e = 0; e < 8; ++e) s_acc[g][grp][dcol + e] = acc[g][e];
   }
-  if (threadIdx.x == 0) {
-    float lsum = 0.f;
+  __syncthreads();
+#pragma unroll 1
+  for (int g = 0; g < G; ++g) {
+    const int64_t unit = static_cast<int64_t>(b) * p.N + h_kv * G + g;
+    const int64_t slot = unit * p.splits + split;
+    float big = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < kGroups; ++i) lsum += (s_m[i] == -INFINITY) ? 0.f : s_l[i] * ex2(s_m[i] - big);
-    p.part_ml[slot * 2] = big;
-    p.part_ml[slot * 2 + 1] = lsum;
+    for (int i = 0; i < kGroups; ++i) big = fmaxf(big, s_m[g][i]);
+    for (int t = threadIdx.x; t < p.D; t += kDecodeThreads) {
+      float a = 0.f;
+#pragma unroll
+      for (int i = 0; i < kGroups; ++i) {
+        const float w = (s_m[g][i] == -INFINITY) ? 0.f : ex2(s_m[g][i] - big);
+        a = fmaf(s_acc[g][i][t], w, a);
+      }
+      p.part_acc[slot * p.D + t] = a;
+    }
+    if (threadIdx.x == 0) {
+      float lsum = 0.f;
+#pragma unroll
+      for (int i = 0; i < kGroups; ++i) lsum += (s_m[g][i] == -INFINITY) ? 0.f : s_l[g][i] * ex2(s_m[g][i] - big);
+      p.part_ml[slot * 2] = big;
+      p.part_ml[slot * 2 + 1] = lsum;
+    }
   }
 }
 
@@ -187,17 +214,28 @@ __global__ void decode_merge_kernel(const DecodeParams p) {
   }
 }
 
-template <int LPR>
-cudaError_t launch_decode_lpr(const DecodeParams& p, bool bf16, cudaStream_t stream) {
-  dim3 grid(p.splits, p.B * p.N);
-  if (bf16) decode_split_kernel<LPR, true><<<grid, kDecodeThreads, 0, stream>>>(p);
-  else decode_split_kernel<LPR, false><<<grid, kDecodeThreads, 0, stream>>>(p);
+template <int LPR, int G>
+cudaError_t launch_decode_g(const DecodeParams& p, bool bf16, cudaStream_t stream) {
+  dim3 grid(p.splits, p.B * (p.N / G));
+  if (bf16) decode_split_kernel<LPR, true, G><<<grid, kDecodeThreads, 0, stream>>>(p);
+  else decode_split_kernel<LPR, false, G><<<grid, kDecodeThreads, 0, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int threads = p.D <= 64 ? 64 : (p.D <= 128 ? 128 : 256);
   if (bf16) decode_merge_kernel<true><<<p.B * p.N, threads, 0, stream>>>(p);
   else decode_merge_kernel<false><<<p.B * p.N, threads, 0, stream>>>(p);
   return cudaGetLastError();
+}
+
+template <int LPR>
+cudaError_t launch_decode_lpr(const DecodeParams& p, bool bf16, cudaStream_t stream) {
+  switch (p.kv_group) {
+    case 1: return launch_decode_g<LPR, 1>(p, bf16, stream);
+    case 2: return launch_decode_g<LPR, 2>(p, bf16, stream);
+    case 4: return launch_decode_g<LPR, 4>(p, bf16, stream);
+    case 8: return launch_decode_g<LPR, 8>(p, bf16, stream);
+    default: return cudaErrorInvalidValue;   // the entry point admits 1, 2, 4, 8 only
+  }
 }
 
 }  // namespace

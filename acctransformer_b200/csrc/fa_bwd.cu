@@ -130,8 +130,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int bh = blockIdx.y;
-  const int b = bh / p.N, h = bh % p.N;
+  // blockIdx.y = (batch, key/value head).  With grouped-query attention the CTA walks the Q tiles of every query
+  // head of its group in turn (dK and dV sum over them); head_of(n) / tile_of(n) name the n-th step.
+  const int n_kv = p.N / p.kv_group;
+  const int bh_kv = blockIdx.y;
+  const int b = bh_kv / n_kv, h_kv = bh_kv % n_kv;
   const int j = blockIdx.x;                      // K/V tile
   const ScoreMods& mods = p.mods;
 
@@ -150,7 +153,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   if (mods.causal) i_lo = max(i_lo, j);
   if (mods.tri_block > 0) i_lo = max(i_lo, (((j * kTile) / mods.tri_block) * mods.tri_block) / kTile);
   if (j * kTile >= kv_len) i_hi = i_lo - 1;
-  const int n_iter = max(0, i_hi - i_lo + 1);
+  const int n_per = max(0, i_hi - i_lo + 1);       // Q tiles per query head
+  const int n_iter = n_per * p.kv_group;
+  auto head_of = [&](int n) { return h_kv * p.kv_group + n / max(n_per, 1); };
+  auto tile_of = [&](int n) { return i_lo + n % max(n_per, 1); };
 
   if (tid == 0) {
     mbar_init(&sh.kv_full, 1);
@@ -183,10 +189,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_do);
         prefetch_tmap(&p.map_dq);
         mbar_expect_tx(&sh.kv_full, 2 * kTileBytes);
-        for (int nb = 0; nb < NB; ++nb) tma_load_4d(sK + nb * 16384, &p.map_k, &sh.kv_full, nb * 64, j * kTile, h, b);
-        for (int nb = 0; nb < NB; ++nb) tma_load_4d(sV + nb * 16384, &p.map_v, &sh.kv_full, nb * 64, j * kTile, h, b);
+        for (int nb = 0; nb < NB; ++nb) tma_load_4d(sK + nb * 16384, &p.map_k, &sh.kv_full, nb * 64, j * kTile, h_kv, b);
+        for (int nb = 0; nb < NB; ++nb) tma_load_4d(sV + nb * 16384, &p.map_v, &sh.kv_full, nb * 64, j * kTile, h_kv, b);
         for (int n = 0; n < n_iter; ++n) {
-          const int i = i_lo + n;
+          const int i = tile_of(n), h = head_of(n);
           const int st = n % kStages;
           // the Q stage is free once the dK product of two tiles ago has finished
           if (n >= kStages) mbar_wait(&sh.q_empty[st], ((n / kStages) - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
@@ -279,7 +285,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     const uint32_t t_dq = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kColDP;
     const bool elected = (r == 0);
     for (int n = 0; n < n_iter; ++n) {
-      const int q_base = (i_lo + n) * kTile;
+      const int q_base = tile_of(n) * kTile;
+      const int h = head_of(n);
+      const int bh = b * p.N + h;
       mbar_wait(&sh.dq_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
       uint32_t dq[kChunks][32];
@@ -308,7 +316,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
             // Fixed summation order for dQ (opt-in): the K/V tiles that touch Q tile i add their parts in
             // descending tile order, which is the order in which they naturally reach tile i under a causal
             // mask.  j_top is the last K/V tile that touches tile i: it inverts the Q-tile range above.
-            const int i = i_lo + n;
+            const int i = tile_of(n);
             int j_top = (kv_len + kTile - 1) / kTile - 1;
             if (mods.next_block_num < 65536) j_top = min(j_top, i + mods.next_block_num);
             if (mods.causal) j_top = min(j_top, i);
@@ -332,7 +340,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
           if (p.dq_order != nullptr && rd == kChunks / 2 - 1) {
             // pass the turn on once this tile's additions have been performed
             tma_store_wait_all();
-            unsigned int* slot = p.dq_order + static_cast<int64_t>(bh) * ((p.S_q + kTile - 1) / kTile) + (i_lo + n);
+            unsigned int* slot = p.dq_order + static_cast<int64_t>(bh) * ((p.S_q + kTile - 1) / kTile) + tile_of(n);
             asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(slot) : "memory");
           }
         }
@@ -350,27 +358,34 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     const uint32_t t_dp = tmem + lane_base + kColDP;
     const bool kv_ok = kv_idx < kv_len;
     uint8_t* my_ds = sDS + hf * 16384u;                  // this half's dS^T block
-    float bias = kNegInf;                                // alibi term in log2 units; -inf removes the key row
-    if (kv_ok) {
-      bias = 0.f;
-      if (mods.alibi != nullptr) bias = load16<BF16>(mods.alibi, static_cast<int64_t>(bh) * p.S_k + kv_idx) * kLog2e;
-      else if (mods.alibi_slopes != nullptr) bias = mods.alibi_slopes[h] * static_cast<float>(kv_idx) * kLog2e;
-    }
+    // alibi term of this key row in log2 units for query head h; -inf removes a key row that does not exist
+    auto bias_of = [&](int h) {
+      float v = kNegInf;
+      if (kv_ok) {
+        v = 0.f;
+        if (mods.alibi != nullptr) v = load16<BF16>(mods.alibi, (static_cast<int64_t>(b) * p.N + h) * p.S_k + kv_idx) * kLog2e;
+        else if (mods.alibi_slopes != nullptr) v = mods.alibi_slopes[h] * static_cast<float>(kv_idx) * kLog2e;
+      }
+      return v;
+    };
+    float bias = kNegInf;
 
     // statistics of the first Q tile
     float nxt_lse = 0.f, nxt_dlt = 0.f;
     if (hf == 0 && n_iter > 0) {
       const int q_row = i_lo * kTile + r;
       const bool q_ok = q_row < p.S_q;
-      const int64_t idx = static_cast<int64_t>(bh) * p.S_q + q_row;
+      const int64_t idx = (static_cast<int64_t>(b) * p.N + head_of(0)) * p.S_q + q_row;
       sh.lse2[0][r] = q_ok ? p.lse[idx] * kLog2e : INFINITY;
       sh.delta[0][r] = q_ok ? p.delta[idx] : 0.f;
       mbar_arrive(&sh.stats_ready);
     }
 
     for (int n = 0; n < n_iter; ++n) {
-      const int i = i_lo + n;
+      const int i = tile_of(n);
       const int q_base = i * kTile;
+      const int bh = b * p.N + head_of(n);
+      if (n % max(n_per, 1) == 0) bias = bias_of(head_of(n));   // first tile of a query head
       // ---- P part: needs S^T only
       mbar_wait(&sh.st_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
@@ -384,9 +399,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       }
       // fetch the next tile's statistics now
       if (hf == 0 && n + 1 < n_iter) {
-        const int q_row = q_base + kTile + r;
+        const int q_row = tile_of(n + 1) * kTile + r;
         const bool q_ok = q_row < p.S_q;
-        const int64_t idx = static_cast<int64_t>(bh) * p.S_q + q_row;
+        const int64_t idx = (static_cast<int64_t>(b) * p.N + head_of(n + 1)) * p.S_q + q_row;
         nxt_lse = q_ok ? p.lse[idx] * kLog2e : INFINITY;
         nxt_dlt = q_ok ? p.delta[idx] : 0.f;
       }
@@ -551,7 +566,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     if (n_iter > 0) mbar_wait(&sh.dq_full, (n_iter - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
     tc_fence_after_sync();
     const bool row_ok = kv_idx < p.S_k;
-    const int64_t row_off = (static_cast<int64_t>(bh) * p.S_k + kv_idx) * p.D;
+    const int64_t row_off = (static_cast<int64_t>(bh_kv) * p.S_k + kv_idx) * p.D;
 #pragma unroll 1
     for (int which = 0; which < 2; ++which) {
       const uint32_t t_src = tmem + lane_base + (which == 0 ? kColDK : kColDV);
@@ -654,7 +669,7 @@ __global__ void bwd_convert_kernel(const float* __restrict__ src, void* __restri
 cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : 128;
   const size_t smem = static_cast<size_t>(3 + kStages) * (dpad / 64) * 16384 + 2 * 32768 + sizeof(BwdShared);
-  dim3 grid((p.S_k + kTile - 1) / kTile, p.B * p.N);
+  dim3 grid((p.S_k + kTile - 1) / kTile, p.B * (p.N / p.kv_group));
   const bool generic = p.mods.mask_kind != 0 || p.mods.drop != nullptr || p.mods.drop_philox != 0 || p.mods.tri_block > 0;
   void (*kern)(const BwdParams) = nullptr;
   if (dpad == 64) {

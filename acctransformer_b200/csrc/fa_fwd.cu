@@ -112,6 +112,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
     bh = g * kUnitGroup + within % g_units;
   }
   const int b = bh / p.N, h = bh % p.N;
+  const int h_kv = h / p.kv_group;   // grouped-query attention: several query heads read one key/value head
 
   int kv_len = p.S_k;
   if (mods.seq_lens != nullptr) kv_len = min(p.S_k, max(0, mods.seq_lens[b]));
@@ -162,11 +163,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         if (it >= kSt) mbar_wait(&sh.k_empty[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         mbar_expect_tx(&sh.k_full[st], kTileBytes);
         for (int nb = 0; nb < NB; ++nb)
-          tma_load_4d(sK + st * kTileBytes + nb * 16384, &p.map_k, &sh.k_full[st], nb * 64, j * kTile, h, b);
+          tma_load_4d(sK + st * kTileBytes + nb * 16384, &p.map_k, &sh.k_full[st], nb * 64, j * kTile, h_kv, b);
         if (it >= kSt) mbar_wait(&sh.v_empty[st], reuse_parity, abort_flag, p.status, DEV_TIMEOUT_SYNC);
         mbar_expect_tx(&sh.v_full[st], kTileBytes);
         for (int nb = 0; nb < NB; ++nb)
-          tma_load_4d(sV + st * kTileBytes + nb * 16384, &p.map_v, &sh.v_full[st], nb * 64, j * kTile, h, b);
+          tma_load_4d(sV + st * kTileBytes + nb * 16384, &p.map_v, &sh.v_full[st], nb * 64, j * kTile, h_kv, b);
       }
     }
   } else if (warp == 9) {

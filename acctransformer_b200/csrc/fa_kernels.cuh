@@ -33,6 +33,7 @@ struct alignas(64) FwdParams {
   float* lse;
   int64_t o_stride_b, o_stride_h, o_stride_s;
   int B, N, S_q, S_k, D;
+  int kv_group;                     // query heads per key/value head (1 unless grouped-query attention)
   float scale_log2;                 // scale * log2(e)
   ScoreMods mods;
   unsigned int* status;
@@ -49,6 +50,7 @@ struct alignas(64) BwdParams {
   void* dv;
   int grads_f32;
   int B, N, S_q, S_k, D;
+  int kv_group;                     // query heads per key/value head; dk, dv are [B, N / kv_group, S_k, D]
   float scale;                      // multiplies dS for dQ and dK
   float scale_log2;
   ScoreMods mods;
@@ -65,6 +67,7 @@ struct DecodeParams {
   float* part_ml;                   // [B*N, splits, 2]
   int64_t kv_stride_b, kv_stride_h, kv_stride_s;
   int B, N, S_max, D;
+  int kv_group;                     // query heads per key/value head: 1, 2, 4 or 8
   int splits;
   float scale_log2;
 };

@@ -64,6 +64,10 @@ class FlashAttention(torch.nn.Module):
         # it for the backward.  Here the kernels decide dropout from (seed, offset) on the fly; set
         # dropout_in_kernel = False to get the mask as a tensor instead (same statistics, 1 byte per score).
         self.dropout_in_kernel = True
+        # The reference refuses key / value tensors with fewer heads than the query ("change themselves to be same by
+        # tile", reference :193-196).  Set allow_grouped_kv = True to pass such tensors as they are (grouped-query /
+        # multi-query attention: query head n reads key/value head n // (N // N_kv); no tiled copy is made).
+        self.allow_grouped_kv = False
         self._dropout_seed = None
         self._dropout_step = 0
 
@@ -88,7 +92,9 @@ class FlashAttention(torch.nn.Module):
         """
         bsz, head_num, seq_len, _ = q.shape
         k_head_num, v_head_num = k.shape[1], v.shape[1]
-        if head_num != k_head_num or head_num != v_head_num:
+        grouped = (self.allow_grouped_kv and k_head_num == v_head_num and k_head_num > 0
+                   and head_num % k_head_num == 0)
+        if (head_num != k_head_num or head_num != v_head_num) and not grouped:
             raise ValueError(
                 "the head_num of query, key and value must be the same, "
                 "If different head_num are used, users need to change themselves to be same by tile.")

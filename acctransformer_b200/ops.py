@@ -46,10 +46,12 @@ def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask
     if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
         raise ValueError("q, k, v must share dtype float16 or bfloat16")
     B, N, S_q, D = q.shape
-    S_k = k.shape[2]
-    if k.shape != (B, N, S_k, D) or v.shape != (B, N, S_k, D):
-        raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
+    S_k, N_kv = k.shape[2], k.shape[1]
+    if k.shape != (B, N_kv, S_k, D) or v.shape != (B, N_kv, S_k, D) or N_kv < 1 or N % N_kv != 0:
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)} "
+                         "(k and v may have fewer heads than q if their head count divides q's)")
     a = FaArgs()
+    a.N_kv = N_kv
     a.dtype = _DTYPES[q.dtype]
     a.B, a.N, a.S_q, a.S_k, a.D = B, N, S_q, S_k, D
     a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
@@ -197,14 +199,15 @@ def infer_prefill(q, k, v, *, causal=False, scale=1.0, seq_lens=None):
     if k.dim() != rank or v.dim() != rank or k.shape != v.shape:
         raise ValueError("k and v must have q's rank and one shape")
     q4, k4, v4 = (t.contiguous() if rank == 4 else t.contiguous().unsqueeze(0) for t in (q, k, v))
-    if q4.shape[:2] != k4.shape[:2] or q4.shape[3] != k4.shape[3]:
-        raise ValueError("q and k must agree on batch, heads and head_dim")
+    if q4.shape[0] != k4.shape[0] or q4.shape[3] != k4.shape[3] or q4.shape[1] % k4.shape[1] != 0:
+        raise ValueError("q and k must agree on batch and head_dim, and k's head count must divide q's")
     y = torch.empty_like(q4)
     a = InferArgs()
     a.dtype = _DTYPES[q.dtype] if q.dtype in (torch.float16, torch.bfloat16) else -1
     a.rank = rank
     a.B, a.N, a.S_q, a.D = q4.shape[0], q4.shape[1], q4.shape[2], q4.shape[3]
     a.S_k = k4.shape[2]
+    a.N_kv = k4.shape[1]
     a.q, a.k, a.v, a.y = q4.data_ptr(), k4.data_ptr(), v4.data_ptr(), y.data_ptr()
     a.causal = 1 if causal else 0
     a.scale = float(scale)
@@ -228,15 +231,18 @@ class DecodeWorkspace:
 
 
 def infer_decode(q, k_cache, v_cache, seq_lens=None, *, scale=None, num_splits=0, workspace=None, out=None):
-    """y[b,n,0,:] = softmax(scale * q K[:len_b]^T) V[:len_b] for q [B,N,1,D], caches [B,N,S_max,D]."""
+    """y[b,n,0,:] = softmax(scale * q K[:len_b]^T) V[:len_b] for q [B,N,1,D], caches [B,N_kv,S_max,D]
+    (N_kv = N, or N / N_kv in {2, 4, 8}: grouped-query attention, the heads of a group share one pass over the cache)."""
     lib = load()
     for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache)):
         _require_cuda(name, t)
     B, N, one, D = q.shape
     if one != 1:
         raise ValueError("decode takes one query token: q must be [B, N, 1, D]")
-    if k_cache.shape != v_cache.shape or k_cache.shape[0] != B or k_cache.shape[1] != N or k_cache.shape[3] != D:
-        raise ValueError("k_cache and v_cache must be [B, N, S_max, D]")
+    N_kv = k_cache.shape[1]
+    if (k_cache.shape != v_cache.shape or k_cache.shape[0] != B or k_cache.shape[3] != D or N_kv < 1
+            or N % N_kv != 0):
+        raise ValueError("k_cache and v_cache must be [B, N_kv, S_max, D] with N_kv dividing q's head count")
     if k_cache.stride() != v_cache.stride():
         raise ValueError("k_cache and v_cache must share strides")
     q = q.contiguous()
@@ -246,6 +252,7 @@ def infer_decode(q, k_cache, v_cache, seq_lens=None, *, scale=None, num_splits=0
     a = DecodeArgs()
     a.dtype = _DTYPES.get(q.dtype, -1)
     a.B, a.N, a.S_max, a.D = B, N, k_cache.shape[2], D
+    a.N_kv = N_kv
     a.q, a.k_cache, a.v_cache, a.y = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), y.data_ptr()
     a.kv_stride = _strides3(k_cache)
     sl = None

@@ -92,8 +92,8 @@ typedef struct acct_fa_args {
   int32_t dtype;            /* ACCT_F16 or ACCT_BF16: type of q, k, v, o, do, alibi */
   int32_t B, N, S_q, S_k, D;
   const void* q;            /* device [B,N,S_q,D] */
-  const void* k;            /* device [B,N,S_k,D] */
-  const void* v;            /* device [B,N,S_k,D] */
+  const void* k;            /* device [B,N_kv,S_k,D] */
+  const void* v;            /* device [B,N_kv,S_k,D] */
   void* o;                  /* device [B,N,S_q,D]; written by fwd, read by bwd */
   float* lse;               /* device [B,N,S_q] fp32, packed; written by fwd (may be NULL), read by bwd */
   int64_t q_stride[3];      /* element strides of B, N, S; 0 = packed */
@@ -123,6 +123,9 @@ typedef struct acct_fa_args {
                                for that group (train/acctransformer/triangle_attention/triangle_attention.py:137-163) */
   uint64_t dropout_seed;    /* ACCT_FLAG_DROPOUT_PHILOX: key of the generator */
   uint64_t dropout_offset;  /* ACCT_FLAG_DROPOUT_PHILOX: below 2^32; a caller advances it from step to step */
+  int32_t N_kv;             /* heads of k, v (and dk, dv): 0 or N = one per query head, as the reference requires
+                               (nn/layer/flash_attention.py:193-196); a divisor of N = grouped-query attention, query
+                               head n reads key/value head n / (N / N_kv); 1 = multi-query */
 } acct_fa_args;
 
 /* Extra I/O of the backward.
@@ -138,8 +141,8 @@ typedef struct acct_fa_args {
 typedef struct acct_fa_bwd_io {
   const void* d_o;          /* device [B,N,S_q,D], strides = o_stride */
   void* dq;                 /* device [B,N,S_q,D] packed */
-  void* dk;                 /* device [B,N,S_k,D] packed */
-  void* dv;                 /* device [B,N,S_k,D] packed */
+  void* dk;                 /* device [B,N_kv,S_k,D] packed */
+  void* dv;                 /* device [B,N_kv,S_k,D] packed */
   void* workspace;          /* device, >= acct_fa_bwd_workspace_bytes(); contents undefined on entry */
   size_t workspace_bytes;
 } acct_fa_bwd_io;
@@ -187,6 +190,7 @@ typedef struct acct_infer_args {
   int32_t causal;
   float scale;
   const int32_t* seq_lens;  /* device [B] or NULL */
+  int32_t N_kv;             /* heads of k and v: 0 or N, or a divisor of N (grouped-query attention) */
 } acct_infer_args;
 
 ACCT_API int acct_infer_prefill(const acct_infer_args* a, void* stream);
@@ -209,6 +213,8 @@ typedef struct acct_decode_args {
   int32_t num_splits;       /* 0 = choose from the device's SM count */
   void* workspace;          /* device, >= acct_infer_decode_workspace_bytes() */
   size_t workspace_bytes;
+  int32_t N_kv;             /* heads of the caches: 0 or N, or a divisor of N with N / N_kv <= 8 (grouped-query
+                               attention: the query heads of a group share one pass over their key/value head) */
 } acct_decode_args;
 
 ACCT_API size_t acct_infer_decode_workspace_bytes(const acct_decode_args* a);

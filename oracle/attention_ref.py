@@ -313,3 +313,30 @@ def dropout_mask_philox(B, N, S_q, S_k, keep_prob, seed, offset=0):
     by = np.stack([(w >> np.uint32(8 * i)) & np.uint32(0xFF) for w in words for i in range(4)], axis=-1)  # [..., 16]
     keep = (by < dropout_threshold(keep_prob)).astype(np.uint8).reshape(B * N, S_q, groups * 16)[:, :, :S_k]
     return np.ascontiguousarray(keep.reshape(B, N, S_q, S_k))
+
+
+# ----------------------------------------------------------------------------------------------
+# Grouped-query attention (fewer key/value heads than query heads)
+# ----------------------------------------------------------------------------------------------
+# The reference has no such path: its cell asks the user to tile K and V up to the query's head
+# count (nn/layer/flash_attention.py:193-196).  These helpers ARE that tiling, around the
+# functions above, so the grouped path is checked against the reference's own prescription.
+def expand_kv_heads(x, n_q_heads):
+    """[B,N_kv,S,D] -> [B,N,S,D]: query head n uses key/value head n // (N // N_kv)."""
+    group = n_q_heads // x.shape[1]
+    return np.repeat(x, group, axis=1)
+
+
+def reduce_kv_heads(g, n_kv_heads):
+    """Gradient of expand_kv_heads: sums the heads of each group.  [B,N,S,D] -> [B,N_kv,S,D]."""
+    B, N, S, D = g.shape
+    return g.reshape(B, n_kv_heads, N // n_kv_heads, S, D).sum(axis=2)
+
+
+def gqa_fwd(q, k, v, **kw):
+    return sa_fwd(q, expand_kv_heads(k, q.shape[1]), expand_kv_heads(v, q.shape[1]), **kw)
+
+
+def gqa_grad(q, k, v, do, **kw):
+    dq, dk, dv = sa_grad(q, expand_kv_heads(k, q.shape[1]), expand_kv_heads(v, q.shape[1]), do, **kw)
+    return dq, reduce_kv_heads(dk, k.shape[1]), reduce_kv_heads(dv, v.shape[1])

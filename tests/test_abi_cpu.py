@@ -38,11 +38,11 @@ def test_ctypes_mirrors_match_c_layout(tmp_path):
     fields = {
         "acct_fa_args": ["dtype", "q", "lse", "q_stride", "o_stride", "mask_kind", "attn_mask", "dropout_mask",
                          "dropout_dtype", "keep_prob", "alibi", "alibi_slopes", "prev_block_num", "scale",
-                         "seq_lens", "flags", "tri_block", "dropout_seed", "dropout_offset"],
+                         "seq_lens", "flags", "tri_block", "dropout_seed", "dropout_offset", "N_kv"],
         "acct_fa_bwd_io": ["d_o", "dq", "workspace", "workspace_bytes"],
-        "acct_infer_args": ["dtype", "rank", "D", "q", "y", "causal", "scale", "seq_lens"],
+        "acct_infer_args": ["dtype", "rank", "D", "q", "y", "causal", "scale", "seq_lens", "N_kv"],
         "acct_decode_args": ["dtype", "D", "q", "kv_stride", "seq_lens", "y", "scale", "num_splits", "workspace",
-                             "workspace_bytes"],
+                             "workspace_bytes", "N_kv"],
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', 'int main(void){']
     for st, fs in fields.items():
