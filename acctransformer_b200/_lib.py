@@ -83,6 +83,7 @@ class DecodeArgs(C.Structure):
         ("seq_lens", C.c_void_p), ("y", C.c_void_p),
         ("scale", C.c_float), ("num_splits", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("N_kv", C.c_int32),
+        ("block_table", C.c_void_p), ("page_size", C.c_int32), ("max_pages", C.c_int32),
     ]
 
 

@@ -437,8 +437,17 @@ int acct_infer_decode(const acct_decode_args* a, void* stream) {
   const int group = a->N / n_kv;
   if (group != 1 && group != 2 && group != 4 && group != 8)
     return fail(ACCT_ERR_SHAPE, "decode takes N / N_kv in {1, 2, 4, 8}, got %d", group);
+  int page_shift = 0;
+  if (a->block_table != nullptr) {
+    if (a->page_size < 16 || (a->page_size & (a->page_size - 1)) != 0)
+      return fail(ACCT_ERR_SHAPE, "page_size = %d must be a power of two >= 16", a->page_size);
+    if (a->max_pages <= 0 || static_cast<int64_t>(a->max_pages) * a->page_size < a->S_max)
+      return fail(ACCT_ERR_SHAPE, "block_table with %d pages of %d rows cannot hold S_max = %d", a->max_pages, a->page_size, a->S_max);
+    while ((1 << page_shift) < a->page_size) ++page_shift;
+  }
   int64_t kvs[3];
-  int rc = check_strides("kv", a->kv_stride, a->S_max, n_kv, a->D, kvs);
+  // paged: the strides are those of a [num_pages, N_kv, page_size, D] pool
+  int rc = check_strides("kv", a->kv_stride, a->block_table ? a->page_size : a->S_max, n_kv, a->D, kvs);
   if (rc) return rc;
   int splits = a->num_splits;
   if (splits < 0 || splits > 64) return fail(ACCT_ERR_SHAPE, "num_splits must be in [0, 64]");
@@ -465,6 +474,7 @@ int acct_infer_decode(const acct_decode_args* a, void* stream) {
   p.kv_stride_b = kvs[0]; p.kv_stride_h = kvs[1]; p.kv_stride_s = kvs[2];
   p.B = a->B; p.N = a->N; p.S_max = a->S_max; p.D = a->D;
   p.kv_group = group;
+  p.block_table = a->block_table; p.page_shift = page_shift; p.max_pages = a->max_pages;
   p.splits = splits;
   p.scale_log2 = a->scale * kLog2e;
   cudaError_t e = launch_decode(p, a->dtype == ACCT_BF16, static_cast<cudaStream_t>(stream));

@@ -90,8 +90,18 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
 #pragma unroll
     for (int e = 0; e < 8; ++e) qf[g][e] *= p.scale_log2;
   }
-  const uint16_t* kbase = reinterpret_cast<const uint16_t*>(p.k) + b * p.kv_stride_b + h_kv * p.kv_stride_h + dcol;
-  const uint16_t* vbase = reinterpret_cast<const uint16_t*>(p.v) + b * p.kv_stride_b + h_kv * p.kv_stride_h + dcol;
+  // Contiguous caches: row r of this (batch, head) sits at base + r * row stride.  Paged caches: the page number
+  // comes from the block table (rows past the sequence are never dereferenced: the loads below are guarded).
+  const bool paged = p.block_table != nullptr;
+  const int* table = paged ? p.block_table + static_cast<int64_t>(b) * p.max_pages : nullptr;
+  const int64_t head_off = h_kv * p.kv_stride_h + dcol;
+  const uint16_t* kbase = reinterpret_cast<const uint16_t*>(p.k) + (paged ? 0 : b * p.kv_stride_b) + head_off;
+  const uint16_t* vbase = reinterpret_cast<const uint16_t*>(p.v) + (paged ? 0 : b * p.kv_stride_b) + head_off;
+  auto row_offset = [&](int row) -> int64_t {
+    if (!paged) return static_cast<int64_t>(row) * p.kv_stride_s;
+    const int page = table[row >> p.page_shift];
+    return static_cast<int64_t>(page) * p.kv_stride_b + static_cast<int64_t>(row & ((1 << p.page_shift) - 1)) * p.kv_stride_s;
+  };
 
   float m[G], l[G];
   float acc[G][8];
@@ -105,15 +115,21 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
 
   for (int row0 = k0 + warp * (RPW * kCh); row0 < k1; row0 += kWarps * RPW * kCh) {
     uint4 ku[kCh], vu[kCh];
+    int64_t off[kCh];
 #pragma unroll
     for (int i = 0; i < kCh; ++i) {
       const int row = row0 + i * RPW + rsub;
-      ku[i] = (active && row < k1) ? ld_stream(kbase + static_cast<int64_t>(row) * p.kv_stride_s) : make_uint4(0, 0, 0, 0);
+      off[i] = row < k1 ? row_offset(row) : 0;
     }
 #pragma unroll
     for (int i = 0; i < kCh; ++i) {
       const int row = row0 + i * RPW + rsub;
-      vu[i] = (active && row < k1) ? ld_stream(vbase + static_cast<int64_t>(row) * p.kv_stride_s) : make_uint4(0, 0, 0, 0);
+      ku[i] = (active && row < k1) ? ld_stream(kbase + off[i]) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < kCh; ++i) {
+      const int row = row0 + i * RPW + rsub;
+      vu[i] = (active && row < k1) ? ld_stream(vbase + off[i]) : make_uint4(0, 0, 0, 0);
     }
     float s[G][kCh];
     float cmax[G];

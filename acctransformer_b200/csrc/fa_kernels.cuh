@@ -68,6 +68,8 @@ struct DecodeParams {
   int64_t kv_stride_b, kv_stride_h, kv_stride_s;
   int B, N, S_max, D;
   int kv_group;                     // query heads per key/value head: 1, 2, 4 or 8
+  const int* block_table;           // [B, max_pages] page numbers, or nullptr: contiguous caches
+  int page_shift, max_pages;        // rows per page = 1 << page_shift; kv_stride_b is then the page stride
   int splits;
   float scale_log2;
 };

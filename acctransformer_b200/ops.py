@@ -230,9 +230,13 @@ class DecodeWorkspace:
         self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
 
 
-def infer_decode(q, k_cache, v_cache, seq_lens=None, *, scale=None, num_splits=0, workspace=None, out=None):
+def infer_decode(q, k_cache, v_cache, seq_lens=None, *, scale=None, num_splits=0, workspace=None, out=None,
+                 block_table=None):
     """y[b,n,0,:] = softmax(scale * q K[:len_b]^T) V[:len_b] for q [B,N,1,D], caches [B,N_kv,S_max,D]
-    (N_kv = N, or N / N_kv in {2, 4, 8}: grouped-query attention, the heads of a group share one pass over the cache)."""
+    (N_kv = N, or N / N_kv in {2, 4, 8}: grouped-query attention, the heads of a group share one pass over the cache).
+
+    With ``block_table`` ([B, max_pages] int32) the caches are page pools [num_pages, N_kv, page_size, D] and key
+    position s of sequence b is row s % page_size of page block_table[b, s // page_size]."""
     lib = load()
     for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache)):
         _require_cuda(name, t)
@@ -240,9 +244,11 @@ def infer_decode(q, k_cache, v_cache, seq_lens=None, *, scale=None, num_splits=0
     if one != 1:
         raise ValueError("decode takes one query token: q must be [B, N, 1, D]")
     N_kv = k_cache.shape[1]
-    if (k_cache.shape != v_cache.shape or k_cache.shape[0] != B or k_cache.shape[3] != D or N_kv < 1
+    paged = block_table is not None
+    if (k_cache.shape != v_cache.shape or (not paged and k_cache.shape[0] != B) or k_cache.shape[3] != D or N_kv < 1
             or N % N_kv != 0):
-        raise ValueError("k_cache and v_cache must be [B, N_kv, S_max, D] with N_kv dividing q's head count")
+        raise ValueError("k_cache and v_cache must be [B, N_kv, S_max, D] (or page pools [pages, N_kv, page_size, D]) "
+                         "with N_kv dividing q's head count")
     if k_cache.stride() != v_cache.stride():
         raise ValueError("k_cache and v_cache must share strides")
     q = q.contiguous()
@@ -251,8 +257,19 @@ def infer_decode(q, k_cache, v_cache, seq_lens=None, *, scale=None, num_splits=0
         workspace = DecodeWorkspace(B, N, D, q.device, num_splits)
     a = DecodeArgs()
     a.dtype = _DTYPES.get(q.dtype, -1)
-    a.B, a.N, a.S_max, a.D = B, N, k_cache.shape[2], D
+    a.B, a.N, a.D = B, N, D
     a.N_kv = N_kv
+    bt = None
+    if paged:
+        _require_cuda("block_table", block_table)
+        bt = block_table.to(torch.int32).contiguous()
+        if bt.dim() != 2 or bt.shape[0] != B:
+            raise ValueError("block_table must be [B, max_pages]")
+        a.block_table = bt.data_ptr()
+        a.page_size, a.max_pages = k_cache.shape[2], bt.shape[1]
+        a.S_max = a.page_size * a.max_pages
+    else:
+        a.S_max = k_cache.shape[2]
     a.q, a.k_cache, a.v_cache, a.y = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), y.data_ptr()
     a.kv_stride = _strides3(k_cache)
     sl = None
@@ -264,4 +281,5 @@ def infer_decode(q, k_cache, v_cache, seq_lens=None, *, scale=None, num_splits=0
     a.workspace, a.workspace_bytes = workspace.buf.data_ptr(), workspace.nbytes
     with torch.cuda.device(q.device):
         check(lib.acct_infer_decode(C.byref(a), _stream()))
+    del bt, sl
     return y

@@ -215,6 +215,13 @@ typedef struct acct_decode_args {
   size_t workspace_bytes;
   int32_t N_kv;             /* heads of the caches: 0 or N, or a divisor of N with N / N_kv <= 8 (grouped-query
                                attention: the query heads of a group share one pass over their key/value head) */
+  /* Paged caches (block_table != NULL): k_cache / v_cache are page pools [num_pages, N_kv, page_size, D] (kv_stride =
+   * element strides of page, head, row; 0 = packed), and key position s of sequence b lives in row s % page_size of
+   * page block_table[b * max_pages + s / page_size].  S_max is then max_pages * page_size.  No counterpart in the
+   * reference (it has no decode path); this is the cache layout serving stacks use. */
+  const int32_t* block_table; /* device [B, max_pages] int32 page numbers, or NULL = contiguous caches */
+  int32_t page_size;          /* rows per page: a power of two >= 16 */
+  int32_t max_pages;          /* columns of block_table */
 } acct_decode_args;
 
 ACCT_API size_t acct_infer_decode_workspace_bytes(const acct_decode_args* a);

@@ -42,7 +42,7 @@ def test_ctypes_mirrors_match_c_layout(tmp_path):
         "acct_fa_bwd_io": ["d_o", "dq", "workspace", "workspace_bytes"],
         "acct_infer_args": ["dtype", "rank", "D", "q", "y", "causal", "scale", "seq_lens", "N_kv"],
         "acct_decode_args": ["dtype", "D", "q", "kv_stride", "seq_lens", "y", "scale", "num_splits", "workspace",
-                             "workspace_bytes", "N_kv"],
+                             "workspace_bytes", "N_kv", "block_table", "page_size", "max_pages"],
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', 'int main(void){']
     for st, fs in fields.items():

@@ -114,3 +114,35 @@ def test_prefill_and_decode_with_fewer_kv_heads(dev):
         ops.infer_decode(torch.zeros(1, 6, 1, 64, dtype=torch.float16, device=dev),
                          torch.zeros(1, 2, 64, 64, dtype=torch.float16, device=dev),
                          torch.zeros(1, 2, 64, 64, dtype=torch.float16, device=dev))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N_kv, page", [(8, 16), (2, 64), (1, 256)])
+def test_decode_over_a_paged_cache(dev, N_kv, page):
+    """Paged caches give the same bits as the contiguous cache they were cut from."""
+    from acctransformer_b200 import ops
+    rs = np.random.RandomState(6)
+    B, N, D = 4, 8, 128
+    lens_list = [1000, 17, 512, 1]
+    max_pages = (max(lens_list) + page - 1) // page
+    S = max_pages * page
+    q = torch.tensor(rs.randn(B, N, 1, D).astype(np.float32)).half().to(dev)
+    kc = torch.tensor(rs.randn(B, N_kv, S, D).astype(np.float32)).half().to(dev)
+    vc = torch.tensor(rs.randn(B, N_kv, S, D).astype(np.float32)).half().to(dev)
+    lens = torch.tensor(lens_list, dtype=torch.int32, device=dev)
+    y_flat = ops.infer_decode(q, kc, vc, lens, num_splits=4)
+    # scatter the pages of every sequence over a shuffled pool (with some unused pages in between)
+    n_pool = B * max_pages + 5
+    perm = rs.permutation(n_pool)[:B * max_pages].reshape(B, max_pages)
+    kp = torch.zeros(n_pool, N_kv, page, D, dtype=torch.float16, device=dev)
+    vp = torch.full((n_pool, N_kv, page, D), float("nan"), dtype=torch.float16, device=dev)
+    for b in range(B):
+        for pg in range(max_pages):
+            kp[perm[b, pg]] = kc[b, :, pg * page:(pg + 1) * page]
+            vp[perm[b, pg]] = vc[b, :, pg * page:(pg + 1) * page]
+    table = torch.tensor(perm.astype(np.int32), device=dev)
+    y_paged = ops.infer_decode(q, kp, vp, lens, num_splits=4, block_table=table)
+    assert torch.equal(y_paged, y_flat)
+    scale = 1.0 / math.sqrt(D)
+    y_ref = ref.decode_ref(_np(q), ref.expand_kv_heads(_np(kc), N), ref.expand_kv_heads(_np(vc), N), np.array(lens_list), scale)
+    assert np.max(np.abs(_np(y_paged) - y_ref)) <= 2e-3
