@@ -216,14 +216,21 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         const uint32_t idesc_dq = make_idesc(BF16, 128, DPAD, true, true);     // dQ
         const uint64_t kmajor = make_sdesc_base(16, 1024);
         const uint64_t mnmajor = make_sdesc_base(16384, 1024);
-        const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS), aDO = smem_u32(sDO);
+        // Descriptors as (low word, high word): the low word holds the start address in 16-byte units, so stepping
+        // along a tile is one 32-bit add and the issuing thread spends next to nothing between two MMAs.
+        const uint32_t k_hi = static_cast<uint32_t>(kmajor >> 32), k_lo = static_cast<uint32_t>(kmajor);
+        const uint32_t mn_hi = static_cast<uint32_t>(mnmajor >> 32), mn_lo = static_cast<uint32_t>(mnmajor);
+        auto lo_of = [](uint32_t base_lo, const uint8_t* ptr) { return base_lo | ((smem_u32(ptr) >> 4) & 0x3fffu); };
+        const uint32_t kK = lo_of(k_lo, sK), kV = lo_of(k_lo, sV), kDO = lo_of(k_lo, sDO), kQ0 = lo_of(k_lo, sQ);
+        const uint32_t mK = lo_of(mn_lo, sK), mDS = lo_of(mn_lo, sDS), mDO = lo_of(mn_lo, sDO), mQ0 = lo_of(mn_lo, sQ);
+        constexpr uint32_t kTileUnits = kTileBytes >> 4;
 
         auto issue_st = [&](int st) {   // S^T = K Q^T
-          const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
+          const uint32_t kQ = kQ0 + st * kTileUnits;
 #pragma unroll
           for (int kk = 0; kk < DPAD / 16; ++kk) {
-            const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
-            umma_ss(tmem + kColST, sdesc_at(kmajor, aK + off), sdesc_at(kmajor, aQ + off), idesc_s, kk > 0);
+            const uint32_t off = (kk >> 2) * 1024u + (kk & 3) * 2u;   // 16-byte units
+            umma_ss_lohi(tmem + kColST, kK + off, k_hi, kQ + off, k_hi, idesc_s, kk > 0);
           }
           umma_commit(&sh.st_full);
         };
@@ -235,15 +242,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         for (int n = 0; n < n_iter; ++n) {
           const int st = n % kStages;
           const int stn = (n + 1) % kStages;
-          const uint32_t aQ = smem_u32(sQ + st * kTileBytes);
+          const uint32_t mQ = mQ0 + st * kTileUnits;
           // dP^T = V dO^T as early as possible: it only needs dO and the previous dQ out of its columns
           mbar_wait(&sh.do_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
           if (n > 0) mbar_wait(&sh.dq_read, (n - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
           tc_fence_after_sync();
 #pragma unroll
           for (int kk = 0; kk < DPAD / 16; ++kk) {
-            const uint32_t off = (kk >> 2) * 16384u + (kk & 3) * 32u;
-            umma_ss(tmem + kColDP, sdesc_at(kmajor, aV + off), sdesc_at(kmajor, aDO + off), idesc_s, kk > 0);
+            const uint32_t off = (kk >> 2) * 1024u + (kk & 3) * 2u;
+            umma_ss_lohi(tmem + kColDP, kV + off, k_hi, kDO + off, k_hi, idesc_s, kk > 0);
           }
           umma_commit(&sh.dp_full);
           // dV += P^T dO as soon as P^T is in tensor memory (the compute warps go on to dS meanwhile);
@@ -252,8 +259,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
           tc_fence_after_sync();
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ts(tmem + kColDV, tmem + kColST + (kk >> 2) * 64 + (kk & 3) * 8, sdesc_at(mnmajor, aDO + kk * 2048u),
-                    idesc_kv, n > 0 || kk > 0);
+            umma_ts_lohi(tmem + kColDV, tmem + kColST + (kk >> 2) * 64 + (kk & 3) * 8, mDO + kk * 128u, mn_hi,
+                         idesc_kv, n > 0 || kk > 0);
           umma_commit(&sh.do_empty);
           // S^T of the next Q tile right behind it (the tensor pipe runs in order, so P^T has been consumed)
           if (n + 1 < n_iter) {
@@ -266,11 +273,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
           tc_fence_after_sync();
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk)   // dK: A = dS^T packed over the dP^T columns, like P^T over S^T
-            umma_ts(tmem + kColDK, tmem + kColDP + (kk >> 2) * 64 + (kk & 3) * 8, sdesc_at(mnmajor, aQ + kk * 2048u),
-                    idesc_kv, n > 0 || kk > 0);
+            umma_ts_lohi(tmem + kColDK, tmem + kColDP + (kk >> 2) * 64 + (kk & 3) * 8, mQ + kk * 128u, mn_hi,
+                         idesc_kv, n > 0 || kk > 0);
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ss(tmem + kColDP, sdesc_at(mnmajor, aDS + kk * 2048u), sdesc_at(mnmajor, aK + kk * 2048u), idesc_dq, kk > 0);
+            umma_ss_lohi(tmem + kColDP, mDS + kk * 128u, mn_hi, mK + kk * 128u, mn_hi, idesc_dq, kk > 0);
           umma_commit(&sh.dq_full);
           umma_commit(&sh.q_empty[st]);
         }
