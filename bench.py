@@ -315,9 +315,9 @@ def run_ours(args):
     roofline = {"kernel": "fa_bwd_kernel (timed as the whole acct_fa_bwd call: + row-sum, zero-fill, dQ convert)",
                 "bound": "tensor", "achieved": bwd_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
                 "frac": bwd_tflops / peaks["tflops"], "peak_source": f"{peaks['which']} bf16_tflops_sustained",
-                # DRAM read + write bytes of one backward-kernel launch: ncu capture on workload P (203.5 + 90.0 MB,
+                # DRAM read + write bytes of one backward-kernel launch: ncu capture on workload P (203.8 + 89.3 MB,
                 # profiles/fa_bwd_kernel_P_ncu_full.md) scaled by the units x sequence ratio of the workload
-                "traffic": 293.5e6 * (cfg["B"] * cfg["N"] * cfg["S"]) / (2 * 16 * 4096), "ms": ms_bwd,
+                "traffic": 293.1e6 * (cfg["B"] * cfg["N"] * cfg["S"]) / (2 * 16 * 4096), "ms": ms_bwd,
                 "fwd": {"kernel": "fa_fwd_kernel", "achieved": fwd_tflops, "frac": fwd_tflops / peaks["tflops"], "ms": ms_fwd},
                 "step_frac_of_sustained": (flops_step / (ms_step * 1e-3) / 1e12) / peaks["tflops"],
                 "step_frac_of_burst": (flops_step / (ms_step * 1e-3) / 1e12) / peaks["tflops_burst"],
