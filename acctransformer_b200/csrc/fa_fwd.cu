@@ -453,16 +453,22 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       }
       tmem_st16(t_s, pk0);
       // 16-bit P goes back over the S buffer; the first half is handed to the MMA warp as soon as it is stored
-#pragma unroll
-      for (int c = 1; c < 4; ++c) {
+      {
         uint32_t pk[16];
-        exp_chunk(c, negm2, l_part, pk);
-        tmem_st16(t_s + c * 16, pk);
-        if (c == 1) {
-          tmem_wait_st();
-          tc_fence_before_sync();
-          mbar_arrive(&sh.p_half[qt]);
-        }
+        exp_chunk(1, negm2, l_part, pk);
+        tmem_st16(t_s + 16, pk);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&sh.p_half[qt]);
+      }
+      {
+        // the second half as one store: the exponentials of chunk 3 overlap the tail of chunk 2
+        uint32_t pk2[16], pk3[16], pk[32];
+        exp_chunk(2, negm2, l_part, pk2);
+        exp_chunk(3, negm2, l_part, pk3);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { pk[i] = pk2[i]; pk[16 + i] = pk3[i]; }
+        tmem_st32(t_s + 32, pk);
       }
       {
         float a0, a1;
