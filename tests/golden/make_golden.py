@@ -1,8 +1,7 @@
 """Regenerates the golden fixtures in this folder from the reference checkout.
 
-Run once, in a container that has the reference project at ``--ref`` (default
-``/root/reference``); the ``.npz`` files it writes are committed, so nothing at test
-time needs the reference.
+Run once, on a machine that has a checkout of the reference project, with ``--ref`` pointing at
+it; the ``.npz`` files it writes are committed, so nothing at test time needs the reference.
 
 What it runs, unmodified:
 
@@ -78,12 +77,12 @@ def infer_case(ref_root, args5):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of the reference project's checkout")
     a = ap.parse_args()
     ns = load_reference_functions(a.ref)
 
     cases = {
-        # BASELINE config 1 shape, gradient-test distribution, full triu mask
+        # benchmark configuration 1's shape, gradient-test distribution, full triu mask
         "fa_cfg1_randn_triu": (11, (1, 2, 256, 64), "triu", "randn"),
         # reference ST shape (1,1,128,80) with both distributions
         "fa_st_128x80_uniform_triu": (12, (1, 1, 128, 80), "triu", "uniform"),
