@@ -29,6 +29,7 @@ EXPORTS = [
     "acct_infer_decode_workspace_bytes", "acct_infer_decode", "acct_infer_decode_static", "acct_device_status",
     "acct_last_error", "acct_abi_version",
     "acct_ms_set_fa_attrs", "acct_ms_fa_fwd", "acct_ms_fa_grad", "acct_ms_infer_fa", "acct_dropout_mask",
+    "acct_mask_is_causal",
 ]
 
 
@@ -120,6 +121,9 @@ def load():
     lib.acct_last_error.restype = C.c_char_p
     lib.acct_dropout_mask.argtypes = [C.POINTER(FaArgs), C.c_void_p, C.c_void_p]
     lib.acct_dropout_mask.restype = C.c_int
+    lib.acct_mask_is_causal.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32),
+                                        C.c_void_p]
+    lib.acct_mask_is_causal.restype = C.c_int
     lib.acct_abi_version.argtypes = []
     lib.acct_abi_version.restype = C.c_int
     if lib.acct_abi_version() != ABI_VERSION:

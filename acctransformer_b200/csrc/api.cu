@@ -32,6 +32,7 @@ int fail_cuda(cudaError_t e, const char* what) {
 // per-device state
 // ---------------------------------------------------------------------------------------------
 __device__ unsigned int g_status_word = 0;
+__device__ unsigned int g_mask_mismatch;   // scratch of acct_mask_is_causal (one call at a time per device)
 
 namespace {
 constexpr int kMaxDevices = 64;
@@ -292,6 +293,26 @@ int acct_dropout_mask(const acct_fa_args* a, uint8_t* mask, void* stream) {
                                       static_cast<unsigned int>(a->dropout_offset), dropout_threshold(a->keep_prob),
                                       static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail_cuda(e, "launching the dropout mask kernel");
+  return ACCT_OK;
+}
+
+int acct_mask_is_causal(const void* mask, int32_t mask_dtype, int32_t mask_batch, int32_t S_q, int32_t S_k,
+                        int32_t* is_causal, void* stream) {
+  if (mask == nullptr || is_causal == nullptr) return fail(ACCT_ERR_NULL, "acct_mask_is_causal: NULL argument");
+  if (mask_dtype != ACCT_F16 && mask_dtype != ACCT_BF16 && mask_dtype != ACCT_U8)
+    return fail(ACCT_ERR_DTYPE, "attn_mask dtype must be F16, BF16 or U8");
+  if (mask_batch <= 0 || S_q <= 0 || S_k <= 0) return fail(ACCT_ERR_SHAPE, "mask_batch, S_q, S_k must be positive");
+  if (device_status_ptr() == nullptr) return ACCT_ERR_NO_DEVICE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned int* flag = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_mask_mismatch);
+  if (e == cudaSuccess) e = cudaMemsetAsync(flag, 0, sizeof(unsigned int), s);
+  if (e == cudaSuccess) e = launch_mask_check(mask, mask_dtype, mask_batch, S_q, S_k, flag, s);
+  unsigned int host = 1;
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&host, flag, sizeof(host), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail_cuda(e, "checking the mask");
+  *is_causal = host == 0 ? 1 : 0;
   return ACCT_OK;
 }
 

@@ -559,6 +559,29 @@ cudaError_t launch_dropout_mask(unsigned char* mask, int units, int S_q, int S_k
   return cudaGetLastError();
 }
 
+// One thread per element pair of rows would be wasteful; a thread walks elements with a grid stride and flags the
+// first difference from the causal mask (1 above the diagonal, 0 on and below it).
+__global__ void mask_check_kernel(const void* mask, int dtype, int64_t total, int S_q, int S_k, unsigned int* mismatch) {
+  unsigned int bad = 0;
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int k = static_cast<int>(t % S_k);
+    const int q = static_cast<int>((t / S_k) % S_q);
+    const float want = k > q ? 1.0f : 0.0f;
+    bad |= (load_mask_value(mask, dtype, t) != want) ? 1u : 0u;
+  }
+  if (__any_sync(0xffffffffu, bad != 0u) && (threadIdx.x & 31) == 0) atomicOr(mismatch, 1u);
+}
+
+cudaError_t launch_mask_check(const void* mask, int dtype, int batch, int S_q, int S_k, unsigned int* mismatch,
+                              cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(batch) * S_q * S_k;
+  const int64_t blocks = (total + 255) / 256;
+  mask_check_kernel<<<static_cast<unsigned>(blocks < 148 * 16 ? (blocks < 1 ? 1 : blocks) : 148 * 16), 256, 0, stream>>>(
+      mask, dtype, total, S_q, S_k, mismatch);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : (p.D <= 128 ? 128 : 256);
   const int nq = dpad > 128 ? 1 : 2, stages = dpad > 128 ? 1 : kStages;

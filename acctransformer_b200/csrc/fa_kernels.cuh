@@ -74,6 +74,10 @@ struct DecodeParams {
   float scale_log2;
 };
 
+// counts into *mismatch the elements of a [batch, S_q, S_k] mask that differ from the causal mask (key > query)
+cudaError_t launch_mask_check(const void* mask, int dtype, int batch, int S_q, int S_k, unsigned int* mismatch,
+                              cudaStream_t stream);
+
 // Launchers: return cudaGetLastError() of the launch.
 cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream);
 cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream);

@@ -23,6 +23,7 @@ import math
 
 import torch
 
+from .... import ops as _ops
 from ...ops.flash_attention.flash_attention_impl import get_flash_attention
 
 __all__ = ['FlashAttention']
@@ -68,6 +69,9 @@ class FlashAttention(torch.nn.Module):
         # tile", reference :193-196).  Set allow_grouped_kv = True to pass such tensors as they are (grouped-query /
         # multi-query attention: query head n reads key/value head n // (N // N_kv); no tiled copy is made).
         self.allow_grouped_kv = False
+        # A full attn_mask is inspected once per tensor (not per step): if it is exactly the causal mask, the kernels
+        # generate the triangle themselves, read no mask and skip the tiles above the diagonal.
+        self.detect_causal_mask = True
         self._dropout_seed = None
         self._dropout_step = 0
 
@@ -112,8 +116,10 @@ class FlashAttention(torch.nn.Module):
             else:
                 drop_mask = (torch.rand((bsz, head_num, seq_len, k.shape[2]), device=q.device,
                                         generator=self.generator) < self.keep_prob).to(torch.uint8)
+        implicit = (self.detect_causal_mask and attn_mask is not None and attn_mask.is_cuda
+                    and attn_mask.numel() != 128 * 128 and _ops.mask_is_causal(attn_mask))
         o, _ = self.flash_attention(q, k, v, attn_mask, drop_mask, alibi_mask, keep_prob=self.keep_prob,
-                                    dropout_seed=seed, dropout_offset=offset)
+                                    dropout_seed=seed, dropout_offset=offset, implicit_causal=implicit)
         return o
 
     forward = construct

@@ -99,12 +99,16 @@ def get_flash_attention(prev_block_num=65536, next_block_num=65536, tiling_stgy_
     (an in-kernel triangle that needs no mask tensor) are this library's additions."""
 
     def fa_forward(query, key, value, attn_mask=None, dropout_mask=None, alibi_mask=None, keep_prob=1.0,
-                   dropout_seed=None, dropout_offset=0):
+                   dropout_seed=None, dropout_offset=0, implicit_causal=False):
         # dropout_seed / dropout_offset: dropout decided inside the kernels (no mask tensor); the backward that
         # autograd runs later reuses the same two values
-        cfg = dict(prev_block_num=prev_block_num, next_block_num=next_block_num, scale=scale, causal=causal,
-                   keep_prob=keep_prob, deterministic=deterministic, dropout_seed=dropout_seed,
-                   dropout_offset=dropout_offset)
+        # implicit_causal: the caller has established that attn_mask is exactly the causal mask; the kernels then
+        # generate the triangle and the tensor is not read
+        if implicit_causal:
+            attn_mask = None
+        cfg = dict(prev_block_num=prev_block_num, next_block_num=next_block_num, scale=scale,
+                   causal=causal or implicit_causal, keep_prob=keep_prob, deterministic=deterministic,
+                   dropout_seed=dropout_seed, dropout_offset=dropout_offset)
         return _FlashAttentionFunction.apply(query, key, value, attn_mask, dropout_mask, alibi_mask, cfg)
 
     fa_forward.prev_block_num = prev_block_num

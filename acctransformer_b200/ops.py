@@ -172,6 +172,34 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
     return dq, dk, dv
 
 
+_causal_cache = {}
+
+
+def mask_is_causal(attn_mask):
+    """True iff ``attn_mask`` ([S_q,S_k] or [Bm,S_q,S_k]) is exactly the causal mask (1 where key > query, else 0).
+    Reads the tensor once on the GPU and synchronises; the answer is remembered per (storage, shape, dtype,
+    version counter), so a mask that is built once and reused is inspected once."""
+    if attn_mask is None or attn_mask.dim() not in (2, 3) or attn_mask.dtype not in _DTYPES:
+        return False
+    _require_cuda("attn_mask", attn_mask)
+    key = (attn_mask.data_ptr(), tuple(attn_mask.shape), attn_mask.stride(), attn_mask.dtype, attn_mask._version,
+           attn_mask.device.index)
+    hit = _causal_cache.get(key)
+    if hit is not None:
+        return hit
+    m = attn_mask.contiguous()
+    if m.dim() == 2:
+        m = m.unsqueeze(0)
+    out = C.c_int32(0)
+    with torch.cuda.device(m.device):
+        check(load().acct_mask_is_causal(m.data_ptr(), _dtype_code(m, "attn_mask"), m.shape[0], m.shape[1], m.shape[2],
+                                         C.byref(out), _stream()))
+    if len(_causal_cache) > 64:
+        _causal_cache.clear()
+    _causal_cache[key] = bool(out.value)
+    return bool(out.value)
+
+
 def dropout_mask(B, N, S_q, S_k, keep_prob, dropout_seed, dropout_offset=0, device="cuda"):
     """The uint8 {0,1} mask [B,N,S_q,S_k] that in-kernel dropout with these values uses (for checks, or for a caller
     that wants the tensor form)."""

@@ -10,13 +10,15 @@ The reference slices q/k/v/mask per row group and runs BatchMatMul / Softmax / C
 lower-left trapezoid.  Here one kernel launch covers the whole sequence: the kernel is told the row
 group size (``tri_block``), skips every 128x128 tile that lies wholly past a row group's ``q_end``,
 excludes single keys past ``q_end`` inside straddling tiles, and still reads and applies the mask
-tensor inside the tiles it computes, so arbitrary masks keep the reference's meaning.  ``assume_causal=True`` (an addition) declares that ``attention_mask`` is the
-strict upper triangle, in which case it is not read at all and the triangle is generated in-kernel.
+tensor inside the tiles it computes, so arbitrary masks keep the reference's meaning.  If ``attention_mask`` is
+exactly the strict upper triangle (checked once per tensor on the GPU, ``detect_causal_mask``; or declared with
+``assume_causal=True``) it is not read at all and the triangle is generated in-kernel.
 """
 from __future__ import annotations
 
 import torch
 
+from .. import ops as _ops
 from ..flash_attention.ops.flash_attention.flash_attention_impl import _FlashAttentionFunction
 
 __all__ = ["TriangleAttention"]
@@ -39,6 +41,9 @@ class TriangleAttention(torch.nn.Module):
         self.keep_prob = 1.0 - dropout_rate
         self.dp, self.mp = dp, mp
         self.assume_causal = assume_causal
+        # attention_mask is inspected once per tensor (not per step): if it is exactly the causal mask the kernels
+        # generate the triangle themselves, read no mask and skip the tiles above the diagonal
+        self.detect_causal_mask = True
         self.generator = None
         self.dropout_in_kernel = True   # dropout decided inside the kernels from (seed, step); False: a mask tensor
         self._dropout_seed = None
@@ -73,10 +78,12 @@ class TriangleAttention(torch.nn.Module):
         # tri_block: a query row in group g sees keys [0, (g+1)*block_size) only, as in the reference's slices;
         # inside that range the mask tensor decides (or the in-kernel triangle when assume_causal).
         # (under the in-kernel triangle the group bound excludes nothing more, so it is not passed)
-        cfg = dict(prev_block_num=65536, next_block_num=65536, scale=1.0, causal=self.assume_causal,
-                   keep_prob=self.keep_prob, tri_block=0 if self.assume_causal else self.block_size,
+        causal = self.assume_causal or (self.detect_causal_mask and attention_mask is not None
+                                        and attention_mask.is_cuda and _ops.mask_is_causal(attention_mask))
+        cfg = dict(prev_block_num=65536, next_block_num=65536, scale=1.0, causal=causal,
+                   keep_prob=self.keep_prob, tri_block=0 if causal else self.block_size,
                    dropout_seed=seed, dropout_offset=offset)
-        mask = None if self.assume_causal else attention_mask
+        mask = None if causal else attention_mask
         out, _ = _FlashAttentionFunction.apply(query, key, value, mask, drop_mask, None, cfg)
         return out
 

@@ -158,6 +158,15 @@ typedef struct acct_fa_bwd_io {
  * the tensor form (dropout_mask = that tensor, dropout_dtype = ACCT_U8, keep_prob = T/256) gives the same results. */
 ACCT_API int acct_dropout_mask(const acct_fa_args* a, uint8_t* mask, void* stream);
 
+/* Tells whether an attn_mask tensor [mask_batch, S_q, S_k] (ACCT_F16 / ACCT_BF16 / ACCT_U8, packed) is exactly the
+ * causal mask: 1 where key > query, 0 elsewhere.  A caller that gets 1 can drop the tensor and set `causal` instead:
+ * the kernels then read no mask at all (268 MB per step at B=8, S=4096) and skip the tiles above the diagonal, which
+ * the reference cannot do because its mask is data (flash_attention_fwd.py:352-361 adds it tile by tile;
+ * triangle_attention.py:126-135 slices it per row group).  Synchronises `stream`; meant to be called once per mask
+ * tensor, not per step.  *is_causal receives 1 or 0. */
+ACCT_API int acct_mask_is_causal(const void* mask, int32_t mask_dtype, int32_t mask_batch, int32_t S_q, int32_t S_k,
+                                 int32_t* is_causal, void* stream);
+
 /* Forward: writes o and (if non-NULL) lse. */
 ACCT_API int acct_fa_fwd(const acct_fa_args* a, void* stream);
 

@@ -391,3 +391,42 @@ def test_headline_size_shard_equivalence_determinism_and_linearity(dev):
     gq, gk, gv = ref.sa_grad(qn, kn, vn, don, causal=True, scale=scale)
     for a, r, n in ((dq, gq, "dq"), (dk, gk, "dk"), (dv, gv, "dv")):
         _check_g(a[sl], r, n)
+
+
+def test_causal_mask_tensor_is_detected_and_not_read(dev):
+    """A mask tensor that is exactly the causal mask is recognised once and replaced by the in-kernel triangle;
+    any other mask keeps going through the tensor path.  Results agree with the oracle either way."""
+    ops = _ops()
+    from acctransformer_b200.flash_attention.nn.layer.flash_attention import FlashAttention
+    from acctransformer_b200.triangle_attention.triangle_attention import TriangleAttention
+    B, N, S, D = 2, 2, 512, 64
+    q, k, v = (_rand((B, N, S, D), s).to(dev) for s in (21, 22, 23))
+    causal = torch.triu(torch.ones(S, S), 1).half().expand(B, S, S).contiguous().to(dev)
+    other = causal.clone()
+    other[1, 100, 3] = 1.0                      # one extra masked position in batch entry 1
+    assert ops.mask_is_causal(causal) and not ops.mask_is_causal(other)
+    assert ops.mask_is_causal(causal[0]) and ops.mask_is_causal(causal.to(torch.uint8))
+    # the answer follows in-place edits of the same tensor
+    causal[0, 5, 2] = 1.0
+    assert not ops.mask_is_causal(causal)
+    causal[0, 5, 2] = 0.0
+    assert ops.mask_is_causal(causal)
+
+    cell = FlashAttention(head_dim=D)
+    scale = 1.0 / math.sqrt(D)
+    for mask in (causal, other):
+        o = cell(q, k, v, mask)
+        o_ref, _ = ref.sa_fwd(_np(q), _np(k), _np(v), attn_mask=_np(mask), scale=scale)
+        _check_o(o, o_ref)
+    cell.detect_causal_mask = False
+    o_tensor_path = cell(q, k, v, causal)
+    o_ref, _ = ref.sa_fwd(_np(q), _np(k), _np(v), attn_mask=_np(causal), scale=scale)
+    _check_o(o_tensor_path, o_ref)
+
+    ta = TriangleAttention(block_size=128)
+    qs = (q.float() * scale).half()             # the layer applies no scale: its callers pre-scale q
+    for mask in (causal, other):
+        o = ta(qs, k, v, mask)
+        o_ref = ref.triangle_fwd(_np(qs), _np(k), _np(v), _np(mask), 128)
+        _check_o(o, o_ref)
+    _status()
