@@ -378,7 +378,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     float bias = kNegInf;
 
     // statistics of the first Q tile
+    // The next tile's statistics are fetched one tile ahead and kept RAW until they are parked: any arithmetic on a
+    // freshly loaded value would stall the warp (in-order issue) for the whole global-memory latency right there.
     float nxt_lse = 0.f, nxt_dlt = 0.f;
+    bool nxt_ok = false;
     if (hf == 0 && n_iter > 0) {
       const int q_row = i_lo * kTile + r;
       const bool q_ok = q_row < p.S_q;
@@ -400,17 +403,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       // compute threads arrived at p_ready(n-1), i.e. after they passed the previous stats_ready wait and
       // finished the dS part that read the buffer being overwritten.
       if (hf == 0 && n > 0) {
-        sh.lse2[n & 1][r] = nxt_lse;
-        sh.delta[n & 1][r] = nxt_dlt;
+        sh.lse2[n & 1][r] = nxt_ok ? nxt_lse * kLog2e : INFINITY;
+        sh.delta[n & 1][r] = nxt_ok ? nxt_dlt : 0.f;
         mbar_arrive(&sh.stats_ready);
       }
       // fetch the next tile's statistics now
       if (hf == 0 && n + 1 < n_iter) {
         const int q_row = tile_of(n + 1) * kTile + r;
-        const bool q_ok = q_row < p.S_q;
-        const int64_t idx = (static_cast<int64_t>(b) * p.N + head_of(n + 1)) * p.S_q + q_row;
-        nxt_lse = q_ok ? p.lse[idx] * kLog2e : INFINITY;
-        nxt_dlt = q_ok ? p.delta[idx] : 0.f;
+        nxt_ok = q_row < p.S_q;
+        const int64_t idx = (static_cast<int64_t>(b) * p.N + head_of(n + 1)) * p.S_q + min(q_row, p.S_q - 1);
+        nxt_lse = p.lse[idx];      // (clamped, always valid address: no branch around the loads)
+        nxt_dlt = p.delta[idx];
       }
       mbar_wait(&sh.stats_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
       const float* lse2 = sh.lse2[n & 1];
