@@ -628,37 +628,43 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   }
 }
 
-// D[row] = sum_d dO[row,d] * O[row,d]  (fp32), one warp per row.
-template <bool BF16>
+// D[row] = sum_d dO[row,d] * O[row,d]  (fp32).  LPR lanes x 16 bytes cover one row, so a warp takes 32 / LPR rows per
+// step and every lane loads; a thread block walks rows with a grid stride.
+template <bool BF16, int LPR>
 __global__ void bwd_delta_kernel(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t sb,
                                  int64_t sh_, int64_t ss, int N, int S_q) {
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + (threadIdx.x >> 5);
-  if (row >= rows) return;
+  constexpr int RPW = 32 / LPR;
   const int lane = threadIdx.x & 31;
-  const int64_t bh = row / S_q;
-  const int64_t off = (bh / N) * sb + (bh % N) * sh_ + (row % S_q) * ss;
-  float acc = 0.f;
-  if (lane * 8 < D) {
-    const uint4 a = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(o) + off + lane * 8);
-    const uint4 g = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(d_o) + off + lane * 8);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+  const int sub = lane % LPR, rsub = lane / LPR;
+  const int64_t warp_global = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + (threadIdx.x >> 5);
+  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x / 32);
+  for (int64_t row0 = warp_global * RPW; row0 < rows; row0 += warps_total * RPW) {
+    const int64_t row = row0 + rsub;
+    float acc = 0.f;
+    if (row < rows && sub * 8 < D) {
+      const int64_t bh = row / S_q;
+      const int64_t off = (bh / N) * sb + (bh % N) * sh_ + (row % S_q) * ss;
+      const uint4 a = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(o) + off + sub * 8);
+      const uint4 g = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(d_o) + off + sub * 8);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float2 x, y;
-      if constexpr (BF16) {
-        x = make_float2(__uint_as_float(aw[e] << 16), __uint_as_float(aw[e] & 0xffff0000u));
-        y = make_float2(__uint_as_float(gw[e] << 16), __uint_as_float(gw[e] & 0xffff0000u));
-      } else {
-        x = __half22float2(*reinterpret_cast<const __half2*>(&aw[e]));
-        y = __half22float2(*reinterpret_cast<const __half2*>(&gw[e]));
+      for (int e = 0; e < 4; ++e) {
+        float2 x, y;
+        if constexpr (BF16) {
+          x = make_float2(__uint_as_float(aw[e] << 16), __uint_as_float(aw[e] & 0xffff0000u));
+          y = make_float2(__uint_as_float(gw[e] << 16), __uint_as_float(gw[e] & 0xffff0000u));
+        } else {
+          x = __half22float2(*reinterpret_cast<const __half2*>(&aw[e]));
+          y = __half22float2(*reinterpret_cast<const __half2*>(&gw[e]));
+        }
+        acc = fmaf(x.x, y.x, acc);
+        acc = fmaf(x.y, y.y, acc);
       }
-      acc = fmaf(x.x, y.x, acc);
-      acc = fmaf(x.y, y.y, acc);
     }
-  }
 #pragma unroll
-  for (int off2 = 16; off2 > 0; off2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off2);
-  if (lane == 0) delta[row] = acc;
+    for (int off2 = LPR / 2; off2 > 0; off2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off2);
+    if (sub == 0 && row < rows) delta[row] = acc;
+  }
 }
 
 template <bool BF16>
@@ -695,14 +701,26 @@ cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+template <int LPR>
+static cudaError_t launch_bwd_delta_lpr(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t sb,
+                                        int64_t sh_, int64_t ss, int N, int S_q, bool bf16, cudaStream_t stream) {
+  const int warps = 8;
+  const int64_t rows_per_block = static_cast<int64_t>(warps) * (32 / LPR);
+  int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
+  const int64_t cap = 148 * 32;   // a few waves of blocks; the grid stride covers the rest
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  if (bf16) bwd_delta_kernel<true, LPR><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(o, d_o, delta, rows, D, sb, sh_, ss, N, S_q);
+  else bwd_delta_kernel<false, LPR><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(o, d_o, delta, rows, D, sb, sh_, ss, N, S_q);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_bwd_delta(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t o_stride_b,
                              int64_t o_stride_h, int64_t o_stride_s, int N, int S_q, bool bf16,
                              cudaStream_t stream) {
-  const int warps = 8;
-  const unsigned blocks = static_cast<unsigned>((rows + warps - 1) / warps);
-  if (bf16) bwd_delta_kernel<true><<<blocks, warps * 32, 0, stream>>>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q);
-  else bwd_delta_kernel<false><<<blocks, warps * 32, 0, stream>>>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q);
-  return cudaGetLastError();
+  if (D <= 64) return launch_bwd_delta_lpr<8>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q, bf16, stream);
+  if (D <= 128) return launch_bwd_delta_lpr<16>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q, bf16, stream);
+  return launch_bwd_delta_lpr<32>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q, bf16, stream);
 }
 
 cudaError_t launch_bwd_convert_dq(const float* dq_acc, void* dq, int64_t n_elems, bool bf16, bool f32_out,
