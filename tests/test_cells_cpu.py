@@ -61,3 +61,35 @@ def test_flop_accounting():
     assert abs(fwd_bwd_flops(CONFIGS["cfg2"]) / 1e9 - 240.5) < 0.1
     assert round(band_fraction(8192, 8192, 4, 4) * 4096) == 556
     assert abs(fwd_bwd_flops(CONFIGS["cfg3"]) / 1e9 - 1044.8) < 0.1
+
+
+def test_band_tile_accounting_matches_the_band_predicate():
+    """The tile counts behind the benchmark's flop figures equal a brute-force evaluation of the reference's band
+    predicate  j - next <= i <= j + prev  on 128-tiles (flash_attention_fwd.py:444-445), for ragged sizes too."""
+    import numpy as np
+    from acctransformer_b200.workloads import band_fraction
+    from oracle import attention_ref as ref
+    rs = np.random.RandomState(0)
+    for _ in range(40):
+        s_q, s_k = int(rs.randint(1, 1500)), int(rs.randint(1, 1500))
+        prev, nxt = int(rs.randint(0, 6)), int(rs.randint(0, 6))
+        m = ref.band_mask(s_q, s_k, prev, nxt)
+        tq, tk = (s_q + 127) // 128, (s_k + 127) // 128
+        tiles = sum(bool(m[i * 128, j * 128]) for i in range(tq) for j in range(tk))
+        assert abs(band_fraction(s_q, s_k, prev, nxt) - tiles / float(tq * tk)) < 1e-12
+    assert band_fraction(8192, 8192, 4, 4) == 556 / 4096.0          # configuration 3: 556 of 4096 tiles
+
+
+def test_triangle_skipped_tiles_match_the_row_group_bounds():
+    """tiles_skipped_fraction() counts exactly the tiles that lie wholly past their rows' group end
+    (triangle_attention.py:137-163: row group g sees keys [0, (g+1)*block_size))."""
+    from acctransformer_b200.triangle_attention.triangle_attention import TriangleAttention
+    for S, block in ((4096, 512), (1000, 300), (4608, 1024), (129, 128)):
+        ta = TriangleAttention(block_size=block)
+        nt = (S + 127) // 128
+        computed = 0
+        for i in range(nt):
+            rows = range(i * 128, min(S, i * 128 + 128))
+            q_end = max(min(S, (r // block + 1) * block) for r in rows)
+            computed += sum(1 for j in range(nt) if j * 128 < q_end)
+        assert abs(ta.tiles_skipped_fraction(S) - (1.0 - computed / float(nt * nt))) < 1e-12
