@@ -64,6 +64,7 @@ class FaBwdIO(C.Structure):
     _fields_ = [
         ("d_o", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("ev_kernel_start", C.c_void_p), ("ev_kernel_stop", C.c_void_p),
     ]
 
 

@@ -405,8 +405,16 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   p.scale = a->scale; p.scale_log2 = a->scale * kLog2e;
   p.mods = make_mods(a);
   p.status = status;
+  if (g->ev_kernel_start != nullptr) {
+    e = cudaEventRecord(static_cast<cudaEvent_t>(g->ev_kernel_start), s);
+    if (e != cudaSuccess) return fail_cuda(e, "recording the kernel-start event");
+  }
   e = launch_fa_bwd(p, bf16, s);
   if (e != cudaSuccess) return fail_cuda(e, "launching the backward kernel");
+  if (g->ev_kernel_stop != nullptr) {
+    e = cudaEventRecord(static_cast<cudaEvent_t>(g->ev_kernel_stop), s);
+    if (e != cudaSuccess) return fail_cuda(e, "recording the kernel-stop event");
+  }
   e = launch_bwd_convert_dq(dq_acc, g->dq, static_cast<int64_t>(rows) * a->D, bf16, p.grads_f32 != 0, s);
   if (e != cudaSuccess) return fail_cuda(e, "launching the dQ conversion kernel");
   return ACCT_OK;

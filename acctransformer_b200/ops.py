@@ -142,7 +142,8 @@ def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dro
 def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, causal=False,
                 dropout_mask=None, keep_prob=1.0, alibi=None, alibi_slopes=None,
                 prev_block_num=BAND_UNBOUNDED, next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None,
-                grads_fp32=False, tri_block=0, deterministic=False, dropout_seed=None, dropout_offset=0):
+                grads_fp32=False, tri_block=0, deterministic=False, dropout_seed=None, dropout_offset=0,
+                kernel_events=None):
     """Grad primitive: returns (dq, dk, dv), fp32 when ``grads_fp32`` (what the reference primitive
     returns) else in q's dtype (what its bprop hands back after the cast)."""
     lib = load()
@@ -166,6 +167,11 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
     g = FaBwdIO()
     g.d_o, g.dq, g.dk, g.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     g.workspace, g.workspace_bytes = ws.data_ptr(), nbytes
+    if kernel_events is not None:     # (start, stop) torch.cuda.Event pair recorded around the main kernel only
+        for ev in kernel_events:
+            if not ev.cuda_event:     # torch creates the underlying event lazily: force it
+                ev.record()
+        g.ev_kernel_start, g.ev_kernel_stop = kernel_events[0].cuda_event, kernel_events[1].cuda_event
     with torch.cuda.device(q.device):
         check(lib.acct_fa_bwd(C.byref(a), C.byref(g), _stream()))
     del keep

@@ -145,6 +145,9 @@ typedef struct acct_fa_bwd_io {
   void* dv;                 /* device [B,N_kv,S_k,D] packed */
   void* workspace;          /* device, >= acct_fa_bwd_workspace_bytes(); contents undefined on entry */
   size_t workspace_bytes;
+  void* ev_kernel_start;    /* optional cudaEvent_t pair (or NULL): recorded on `stream` directly before and after the */
+  void* ev_kernel_stop;     /* main backward kernel, so that a caller can time it apart from the row-sum, zero-fill and
+                               dQ-conversion helpers of the same call */
 } acct_fa_bwd_io;
 
 /* In-kernel dropout (ACCT_FLAG_DROPOUT_PHILOX) replaces the mask tensor the reference cell generates and keeps in

@@ -39,7 +39,7 @@ def test_ctypes_mirrors_match_c_layout(tmp_path):
         "acct_fa_args": ["dtype", "q", "lse", "q_stride", "o_stride", "mask_kind", "attn_mask", "dropout_mask",
                          "dropout_dtype", "keep_prob", "alibi", "alibi_slopes", "prev_block_num", "scale",
                          "seq_lens", "flags", "tri_block", "dropout_seed", "dropout_offset", "N_kv"],
-        "acct_fa_bwd_io": ["d_o", "dq", "workspace", "workspace_bytes"],
+        "acct_fa_bwd_io": ["d_o", "dq", "workspace", "workspace_bytes", "ev_kernel_start", "ev_kernel_stop"],
         "acct_infer_args": ["dtype", "rank", "D", "q", "y", "causal", "scale", "seq_lens", "N_kv"],
         "acct_decode_args": ["dtype", "D", "q", "kv_stride", "seq_lens", "y", "scale", "num_splits", "workspace",
                              "workspace_bytes", "N_kv", "block_table", "page_size", "max_pages"],
