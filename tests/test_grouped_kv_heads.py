@@ -146,3 +146,34 @@ def test_decode_over_a_paged_cache(dev, N_kv, page):
     scale = 1.0 / math.sqrt(D)
     y_ref = ref.decode_ref(_np(q), ref.expand_kv_heads(_np(kc), N), ref.expand_kv_heads(_np(vc), N), np.array(lens_list), scale)
     assert np.max(np.abs(_np(y_paged) - y_ref)) <= 2e-3
+
+
+@pytest.mark.gpu
+def test_grouped_heads_with_in_kernel_dropout_and_mask_tensor(dev):
+    """Everything that is indexed per QUERY head (dropout stream, alibi row) or per batch (mask) keeps its meaning when
+    the key/value heads are shared."""
+    from acctransformer_b200 import ops, _lib
+    rs = np.random.RandomState(8)
+    B, N, N_kv, S, D = 2, 4, 2, 320, 64
+    mk = lambda n: torch.tensor(rs.randn(B, n, S, D).astype(np.float32) * 0.8).half().to(dev)
+    q, k, v, do = mk(N), mk(N_kv), mk(N_kv), mk(N)
+    mask_np = (rs.rand(B, S, S) < 0.2).astype(np.float16)
+    mask = torch.tensor(mask_np).to(dev)
+    keep, seed, offset = 0.75, 4242, 11
+    scale = 1.0 / math.sqrt(D)
+    o, lse = ops.fa_forward(q, k, v, mask, scale=scale, keep_prob=keep, dropout_seed=seed, dropout_offset=offset)
+    dq, dk, dv = ops.fa_backward(q, k, v, o, lse, do, mask, scale=scale, keep_prob=keep, dropout_seed=seed,
+                                 dropout_offset=offset)
+    torch.cuda.synchronize()
+    _lib.device_status()
+    m_ref = ref.dropout_mask_philox(B, N, S, S, keep, seed, offset)
+    keep_eff = ref.dropout_threshold(keep) / 256.0
+    o_ref, l_ref = ref.gqa_fwd(_np(q), _np(k), _np(v), attn_mask=mask_np.astype(np.float32), drop_mask=m_ref,
+                               keep_prob=keep_eff, scale=scale)
+    assert np.max(np.abs(_np(o) - o_ref)) <= 2e-3
+    assert np.max(np.abs(_np(lse) - l_ref)) <= 2e-3
+    g_ref = ref.gqa_grad(_np(q), _np(k), _np(v), _np(do), attn_mask=mask_np.astype(np.float32), drop_mask=m_ref,
+                         keep_prob=keep_eff, scale=scale)
+    for got, want, name in zip((dq, dk, dv), g_ref, ("dq", "dk", "dv")):
+        err = np.max(np.abs(_np(got) - want)) / np.max(np.abs(want))
+        assert err <= 1e-2, (name, err)
