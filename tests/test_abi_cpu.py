@@ -161,3 +161,49 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libacct_b200.so")
     with pytest.raises(ImportError):
         _lib.load()
+
+
+def test_a_plain_c_caller_can_bind_the_library(tmp_path, lib):
+    """The boundary is a C ABI: a C99 program that includes the header, loads the library with dlopen and calls it
+    gets the documented status codes (argument checks run before any device work, so no GPU is needed)."""
+    src = tmp_path / "caller.c"
+    src.write_text(r'''
+#include <dlfcn.h>
+#include <stdio.h>
+#include <string.h>
+#include "acct_b200.h"
+typedef int (*fwd_fn)(const acct_fa_args*, void*);
+typedef int (*ver_fn)(void);
+typedef const char* (*err_fn)(void);
+typedef size_t (*ws_fn)(const acct_fa_args*);
+int main(int argc, char** argv) {
+  void* h = dlopen(argv[1], RTLD_NOW);
+  if (!h) { printf("dlopen failed: %s\n", dlerror()); return 1; }
+  ver_fn ver = (ver_fn)dlsym(h, "acct_abi_version");
+  fwd_fn fwd = (fwd_fn)dlsym(h, "acct_fa_fwd");
+  err_fn err = (err_fn)dlsym(h, "acct_last_error");
+  ws_fn ws = (ws_fn)dlsym(h, "acct_fa_bwd_workspace_bytes");
+  if (!ver || !fwd || !err || !ws) { printf("missing symbol\n"); return 2; }
+  printf("version %d (header %d)\n", ver(), ACCT_ABI_VERSION);
+  acct_fa_args a;
+  memset(&a, 0, sizeof a);
+  printf("null args -> %d\n", fwd(NULL, NULL));
+  a.dtype = ACCT_F16; a.B = 1; a.N = 2; a.S_q = 256; a.S_k = 256; a.D = 60;   /* head_dim not a multiple of 8 */
+  a.scale = 1.0f; a.keep_prob = 1.0f;
+  printf("bad head_dim -> %d (%s)\n", fwd(&a, NULL), err());
+  a.D = 64;
+  printf("null tensors -> %d\n", fwd(&a, NULL));
+  printf("workspace bytes %zu\n", ws(&a));
+  return 0;
+}
+''')
+    exe = tmp_path / "caller"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src),
+                    "-ldl"], check=True)
+    out = subprocess.run([str(exe), _lib.LIB_PATH], check=True, capture_output=True, text=True).stdout
+    assert "version 2 (header 2)" in out
+    assert "null args -> 1" in out                      # ACCT_ERR_NULL
+    assert "bad head_dim -> 4" in out                   # ACCT_ERR_UNSUPPORTED_D
+    assert "null tensors -> 1" in out
+    ws_line = [ln for ln in out.splitlines() if ln.startswith("workspace bytes")][0]
+    assert int(ws_line.split()[-1]) >= 1 * 2 * 256 * 64 * 4     # at least the fp32 dQ accumulator
