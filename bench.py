@@ -38,6 +38,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="H")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode HBM measurement")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="run only the decode measurement on a quarter-size cache (B=8; 3 x 1.07 GB), for profiling, "
+                         "and print its JSON object")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-aux", action="store_true", help="skip the other configurations (2, 3, 4, 5a)")
@@ -436,13 +439,13 @@ def bench_other_configs(torch, ops, dev, peaks):
     return out
 
 
-def bench_decode(torch, ops, dev, peaks):
+def bench_decode(torch, ops, dev, peaks, small=False):
     """Decode step of configuration 5b (B=32 N=32 KV<=16384 D=128 fp16, per-sequence lengths): achieved HBM GB/s
     counting only the valid K and V rows.  Three cache sets (25.8 GB) are rotated so that no step finds its
-    cache in L2."""
+    cache in L2.  ``small``: B=8 (3 x 2.1 GB, still far above L2), few iterations, for a profiler capture."""
     from acctransformer_b200.workloads import CONFIGS
     c = CONFIGS["cfg5b"]
-    B, N, S, D = c["B"], c["N"], c["S"], c["D"]
+    B, N, S, D = (8 if small else c["B"]), c["N"], c["S"], c["D"]
     g = torch.Generator(device=dev).manual_seed(6)
     sets = []
     for _ in range(3):
@@ -456,9 +459,9 @@ def bench_decode(torch, ops, dev, peaks):
     lens = torch.randint(c["len_lo"], S + 1, (B,), generator=gl, dtype=torch.int32).to(dev)
     ws = ops.DecodeWorkspace(B, N, D, dev)
     y = torch.empty_like(qd)
-    for i in range(6):
+    for i in range(3 if small else 6):
         ops.infer_decode(qd, sets[i % 3][0], sets[i % 3][1], lens, workspace=ws, out=y)
-    iters = 30
+    iters = 6 if small else 30
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
@@ -469,7 +472,7 @@ def bench_decode(torch, ops, dev, peaks):
     ms = e0.elapsed_time(e1) / iters
     nbytes = float(lens.sum().item()) * N * D * 2 * 2
     gbps = nbytes / (ms * 1e-3) / 1e9
-    return {"workload": "cfg5b decode B=32 N=32 q_len=1 KV<=16384 D=128 fp16", "ms": ms, "bytes": nbytes,
+    return {"workload": f"cfg5b decode B={B} N=32 q_len=1 KV<=16384 D=128 fp16", "ms": ms, "bytes": nbytes,
             "achieved_gbs": gbps, "peak_gbs": peaks["hbm_gbs"], "frac": gbps / peaks["hbm_gbs"],
             "peak_source": f"{peaks['which']} hbm_gbs"}
 
@@ -478,6 +481,13 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.decode_only:
+        import torch
+        from acctransformer_b200 import ops
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+        print(json.dumps({"decode": bench_decode(torch, ops, dev, measured_peaks(), small=True)}), flush=True)
+        return 0
     return run_ours(args)
 
 
