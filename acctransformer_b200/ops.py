@@ -5,6 +5,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import weakref
 
 import torch
 
@@ -178,21 +179,21 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
     return dq, dk, dv
 
 
-_causal_cache = {}
+_causal_cache = {}     # id(tensor) -> (weak reference to that tensor, its version counter, answer)
 
 
 def mask_is_causal(attn_mask):
     """True iff ``attn_mask`` ([S_q,S_k] or [Bm,S_q,S_k]) is exactly the causal mask (1 where key > query, else 0).
-    Reads the tensor once on the GPU and synchronises; the answer is remembered per (storage, shape, dtype,
-    version counter), so a mask that is built once and reused is inspected once."""
+    Reads the tensor once on the GPU and synchronises.  The answer is remembered for the tensor OBJECT (held by weak
+    reference, so a new tensor that happens to reuse the address of a freed one is inspected afresh) and its version
+    counter (so in-place edits are noticed): a mask that is built once and reused is inspected once."""
     if attn_mask is None or attn_mask.dim() not in (2, 3) or attn_mask.dtype not in _DTYPES:
         return False
     _require_cuda("attn_mask", attn_mask)
-    key = (attn_mask.data_ptr(), tuple(attn_mask.shape), attn_mask.stride(), attn_mask.dtype, attn_mask._version,
-           attn_mask.device.index)
+    key = id(attn_mask)
     hit = _causal_cache.get(key)
-    if hit is not None:
-        return hit
+    if hit is not None and hit[0]() is attn_mask and hit[1] == attn_mask._version:
+        return hit[2]
     m = attn_mask.contiguous()
     if m.dim() == 2:
         m = m.unsqueeze(0)
@@ -201,8 +202,11 @@ def mask_is_causal(attn_mask):
         check(load().acct_mask_is_causal(m.data_ptr(), _dtype_code(m, "attn_mask"), m.shape[0], m.shape[1], m.shape[2],
                                          C.byref(out), _stream()))
     if len(_causal_cache) > 64:
-        _causal_cache.clear()
-    _causal_cache[key] = bool(out.value)
+        for k_ in [k_ for k_, v_ in _causal_cache.items() if v_[0]() is None]:
+            del _causal_cache[k_]
+        if len(_causal_cache) > 64:
+            _causal_cache.clear()
+    _causal_cache[key] = (weakref.ref(attn_mask), attn_mask._version, bool(out.value))
     return bool(out.value)
 
 

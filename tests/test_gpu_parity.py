@@ -411,6 +411,14 @@ def test_causal_mask_tensor_is_detected_and_not_read(dev):
     assert not ops.mask_is_causal(causal)
     causal[0, 5, 2] = 0.0
     assert ops.mask_is_causal(causal)
+    # a NEW tensor at the address of a freed one is inspected afresh (the answer belongs to the object, not the address)
+    tmp = torch.triu(torch.ones(S, S), 1).half().to(dev)
+    assert ops.mask_is_causal(tmp)
+    addr = tmp.data_ptr()
+    del tmp
+    tmp2 = torch.zeros(S, S, dtype=torch.float16, device=dev)
+    if tmp2.data_ptr() == addr:                 # the caching allocator normally hands the block straight back
+        assert not ops.mask_is_causal(tmp2)
 
     cell = FlashAttention(head_dim=D)
     scale = 1.0 / math.sqrt(D)
