@@ -383,14 +383,15 @@ def test_headline_size_shard_equivalence_determinism_and_linearity(dev):
     dq2, dk2, dv2 = ops.fa_backward(q, k, v, o * 2, lse, do * 2, causal=True, scale=scale)
     assert float((dv2.float() - 2 * dv.float()).abs().max()) <= 2.0 ** -23
     _status()
-    # the last (batch, head) unit against the oracle at full length
-    sl = (slice(1, 2), slice(31, 32))
-    qn, kn, vn, don = (_np(t[sl]).astype(np.float16) for t in (q, k, v, do))
-    o_ref, l_ref = ref.sa_fwd(qn, kn, vn, causal=True, scale=scale)
-    _check_o(o[sl], o_ref)
-    gq, gk, gv = ref.sa_grad(qn, kn, vn, don, causal=True, scale=scale)
-    for a, r, n in ((dq, gq, "dq"), (dk, gk, "dk"), (dv, gv, "dv")):
-        _check_g(a[sl], r, n)
+    # the first and the last (batch, head) unit against the oracle at full length
+    for sl in ((slice(0, 1), slice(0, 1)), (slice(1, 2), slice(31, 32))):
+        qn, kn, vn, don = (_np(t[sl]).astype(np.float16) for t in (q, k, v, do))
+        o_ref, l_ref = ref.sa_fwd(qn, kn, vn, causal=True, scale=scale)
+        _check_o(o[sl], o_ref)
+        assert float(np.max(np.abs(_np(lse[sl]) - l_ref))) <= O_TOL
+        gq, gk, gv = ref.sa_grad(qn, kn, vn, don, causal=True, scale=scale)
+        for a, r, n in ((dq, gq, "dq"), (dk, gk, "dk"), (dv, gv, "dv")):
+            _check_g(a[sl], r, n)
 
 
 def test_causal_mask_tensor_is_detected_and_not_read(dev):
