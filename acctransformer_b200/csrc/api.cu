@@ -350,8 +350,9 @@ size_t acct_fa_bwd_workspace_bytes(const acct_fa_args* a) {
   const size_t rows = static_cast<size_t>(a->B) * a->N * a->S_q;
   const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile);
   // delta [rows] fp32 | turn counters of the ordered dQ reduction [B*N*ceil(S_q/128)] u32 | dQ accumulator
-  // [rows, D] fp32; the first two padded to 256 bytes
-  return ((rows * 4 + 255) / 256) * 256 + ((q_tiles * 4 + 255) / 256) * 256 + rows * static_cast<size_t>(a->D) * 4;
+  // [rows, D] fp32; the first two padded to 256 bytes.  With fp32 gradients dq itself is the accumulator.
+  const size_t acc = (a->flags & ACCT_FLAG_GRAD_F32) ? 0 : rows * static_cast<size_t>(a->D) * 4;
+  return ((rows * 4 + 255) / 256) * 256 + ((q_tiles * 4 + 255) / 256) * 256 + acc;
 }
 
 int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
@@ -375,7 +376,10 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile);
   const size_t order_bytes = ((q_tiles * 4 + 255) / 256) * 256;
   unsigned int* dq_order = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(g->workspace) + ((rows * 4 + 255) / 256) * 256);
-  float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dq_order) + order_bytes);
+  // fp32 gradients: the kernel's reduce-add lands in the caller's dq directly, no copy afterwards
+  const bool dq_in_place = (a->flags & ACCT_FLAG_GRAD_F32) != 0;
+  float* dq_acc = dq_in_place ? static_cast<float*>(g->dq)
+                              : reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dq_order) + order_bytes);
 
   BwdParams p;
   memset(&p, 0, sizeof(p));
@@ -391,8 +395,10 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   t.strides[2] = static_cast<int64_t>(a->N) * a->S_q * a->D;
   if ((rc = make_tmap_4d(&p.map_dq, t, kTile))) return rc;
 
-  // one zero-fill covers the turn counters and the accumulator behind them
-  cudaError_t e = cudaMemsetAsync(dq_order, 0, order_bytes + rows * static_cast<size_t>(a->D) * 4, s);
+  // one zero-fill covers the turn counters and the accumulator behind them in the workspace
+  const size_t acc_bytes = rows * static_cast<size_t>(a->D) * 4;
+  cudaError_t e = cudaMemsetAsync(dq_order, 0, order_bytes + (dq_in_place ? 0 : acc_bytes), s);
+  if (e == cudaSuccess && dq_in_place) e = cudaMemsetAsync(dq_acc, 0, acc_bytes, s);
   if (e != cudaSuccess) return fail_cuda(e, "zero-filling the dQ accumulator");
   e = launch_bwd_delta(a->o, g->d_o, delta, static_cast<int64_t>(rows), a->D, st.o[0], st.o[1], st.o[2], a->N, a->S_q, bf16, s);
   if (e != cudaSuccess) return fail_cuda(e, "launching the row-sum kernel");
@@ -415,7 +421,8 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
     e = cudaEventRecord(static_cast<cudaEvent_t>(g->ev_kernel_stop), s);
     if (e != cudaSuccess) return fail_cuda(e, "recording the kernel-stop event");
   }
-  e = launch_bwd_convert_dq(dq_acc, g->dq, static_cast<int64_t>(rows) * a->D, bf16, p.grads_f32 != 0, s);
+  if (dq_in_place) return ACCT_OK;
+  e = launch_bwd_convert_dq(dq_acc, g->dq, static_cast<int64_t>(rows) * a->D, bf16, false, s);
   if (e != cudaSuccess) return fail_cuda(e, "launching the dQ conversion kernel");
   return ACCT_OK;
 }

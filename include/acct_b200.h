@@ -140,7 +140,8 @@ typedef struct acct_fa_args {
  */
 typedef struct acct_fa_bwd_io {
   const void* d_o;          /* device [B,N,S_q,D], strides = o_stride */
-  void* dq;                 /* device [B,N,S_q,D] packed */
+  void* dq;                 /* device [B,N,S_q,D] packed; with ACCT_FLAG_GRAD_F32 it is also the accumulator the
+                               kernel adds into (zero-filled by the call), so no conversion pass follows */
   void* dk;                 /* device [B,N_kv,S_k,D] packed */
   void* dv;                 /* device [B,N_kv,S_k,D] packed */
   void* workspace;          /* device, >= acct_fa_bwd_workspace_bytes(); contents undefined on entry */

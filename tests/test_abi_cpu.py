@@ -123,6 +123,9 @@ def test_backward_workspace_size_and_rejection(lib):
     q_tiles = 2 * 3 * 2          # ceil(200 / 128) Q tiles per (batch, head) slice
     need = ((rows * 4 + 255) // 256) * 256 + ((q_tiles * 4 + 255) // 256) * 256 + rows * 128 * 4
     assert lib.acct_fa_bwd_workspace_bytes(C.byref(a)) == need
+    a.flags = _lib.FLAG_GRAD_F32      # fp32 gradients accumulate in dq itself: no accumulator in the workspace
+    assert lib.acct_fa_bwd_workspace_bytes(C.byref(a)) == need - rows * 128 * 4
+    a.flags = 0
     g = _lib.FaBwdIO()
     g.d_o = g.dq = g.dk = g.dv = 0x3000
     g.workspace, g.workspace_bytes = 0x4000, need - 1
