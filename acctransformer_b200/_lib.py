@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(HERE, "libacct_b200.so")
 ACCT_F16, ACCT_BF16, ACCT_U8, ACCT_F32 = 0, 1, 2, 3
 MASK_NONE, MASK_FULL, MASK_TILE128 = 0, 1, 2
 BAND_UNBOUNDED = 65536
-ABI_VERSION = 2       # ACCT_ABI_VERSION of include/acct_b200.h these mirrors were written for
+ABI_VERSION = 3       # ACCT_ABI_VERSION of include/acct_b200.h these mirrors were written for
 FLAG_GRAD_F32, FLAG_DETERMINISTIC, FLAG_DROPOUT_PHILOX = 1, 2, 4
 DECODE_STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
 
@@ -29,7 +29,7 @@ EXPORTS = [
     "acct_infer_decode_workspace_bytes", "acct_infer_decode", "acct_infer_decode_static", "acct_device_status",
     "acct_last_error", "acct_abi_version",
     "acct_ms_set_fa_attrs", "acct_ms_fa_fwd", "acct_ms_fa_grad", "acct_ms_infer_fa", "acct_dropout_mask",
-    "acct_mask_is_causal",
+    "acct_mask_is_causal", "acct_mask_tiles_bytes", "acct_mask_classify_tiles",
 ]
 
 
@@ -57,6 +57,7 @@ class FaArgs(C.Structure):
         ("seq_lens", C.c_void_p),
         ("flags", C.c_uint32), ("tri_block", C.c_int32),
         ("dropout_seed", C.c_uint64), ("dropout_offset", C.c_uint64), ("N_kv", C.c_int32),
+        ("mask_tiles", C.c_void_p),
     ]
 
 
@@ -125,6 +126,10 @@ def load():
     lib.acct_mask_is_causal.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32),
                                         C.c_void_p]
     lib.acct_mask_is_causal.restype = C.c_int
+    lib.acct_mask_tiles_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+    lib.acct_mask_tiles_bytes.restype = C.c_size_t
+    lib.acct_mask_classify_tiles.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+    lib.acct_mask_classify_tiles.restype = C.c_int
     lib.acct_abi_version.argtypes = []
     lib.acct_abi_version.restype = C.c_int
     if lib.acct_abi_version() != ABI_VERSION:

@@ -186,6 +186,8 @@ int validate_fa(const acct_fa_args* a, Strides* st, bool backward = false) {
       break;
     default: return fail(ACCT_ERR_SHAPE, "unknown mask_kind %d", a->mask_kind);
   }
+  if (a->mask_tiles != nullptr && a->mask_kind != ACCT_MASK_FULL)
+    return fail(ACCT_ERR_SHAPE, "mask_tiles describes an ACCT_MASK_FULL attn_mask only");
   if (a->mask_kind != ACCT_MASK_NONE && a->mask_dtype != ACCT_F16 && a->mask_dtype != ACCT_BF16 && a->mask_dtype != ACCT_U8)
     return fail(ACCT_ERR_DTYPE, "attn_mask dtype must be F16, BF16 or U8");
   if (a->dropout_mask) {
@@ -219,6 +221,7 @@ ScoreMods make_mods(const acct_fa_args* a) {
   m.mask_dtype = a->mask_dtype;
   m.mask_batch = a->mask_batch;
   m.mask = a->mask_kind == ACCT_MASK_NONE ? nullptr : a->attn_mask;
+  m.mask_tiles = a->mask_kind == ACCT_MASK_FULL ? a->mask_tiles : nullptr;
   m.drop = a->dropout_mask;
   m.drop_dtype = a->dropout_dtype;
   m.drop_scale = (a->dropout_mask && a->dropout_dtype == ACCT_U8) ? 1.0f / a->keep_prob : 1.0f;
@@ -313,6 +316,25 @@ int acct_mask_is_causal(const void* mask, int32_t mask_dtype, int32_t mask_batch
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) return fail_cuda(e, "checking the mask");
   *is_causal = host == 0 ? 1 : 0;
+  return ACCT_OK;
+}
+
+size_t acct_mask_tiles_bytes(int32_t mask_batch, int32_t S_q, int32_t S_k) {
+  if (mask_batch <= 0 || S_q <= 0 || S_k <= 0) return 0;
+  return static_cast<size_t>(mask_batch) * ((S_q + kTile - 1) / kTile) * ((S_k + kTile - 1) / kTile);
+}
+
+int acct_mask_classify_tiles(const void* mask, int32_t mask_dtype, int32_t mask_batch, int32_t S_q, int32_t S_k,
+                             uint8_t* tiles, void* stream) {
+  if (mask == nullptr || tiles == nullptr) return fail(ACCT_ERR_NULL, "acct_mask_classify_tiles: NULL argument");
+  if (mask_dtype != ACCT_F16 && mask_dtype != ACCT_BF16 && mask_dtype != ACCT_U8)
+    return fail(ACCT_ERR_DTYPE, "attn_mask dtype must be F16, BF16 or U8");
+  if (mask_batch <= 0 || S_q <= 0 || S_k <= 0) return fail(ACCT_ERR_SHAPE, "mask_batch, S_q, S_k must be positive");
+  if (mask_batch > 65535 || (S_q + kTile - 1) / kTile > 65535)
+    return fail(ACCT_ERR_SHAPE, "mask_batch and S_q / 128 must not exceed 65535");
+  if (device_status_ptr() == nullptr) return ACCT_ERR_NO_DEVICE;
+  cudaError_t e = launch_mask_classify(mask, mask_dtype, mask_batch, S_q, S_k, tiles, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda(e, "launching the mask classification kernel");
   return ACCT_OK;
 }
 

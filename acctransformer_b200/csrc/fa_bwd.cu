@@ -108,9 +108,10 @@ __device__ __forceinline__ uint32_t philox_keep_column(const ScoreMods& mods, in
 
 }  // namespace
 
-// GENERIC = mask tensor, dropout mask or triangle row groups may be present; the plain instantiation carries
-// none of that code, so its register allocation is not disturbed by it.
-template <int DPAD, bool BF16, bool GENERIC>
+// MASKED = a mask tensor or TriangleAttention row groups may be present: tiles that need them get a pass over S^T
+// in tensor memory before the common code.  DROP = 0 no dropout, 1 in-kernel generator, 2 dropout mask tensor.  The
+// plain instantiation carries none of that code, so its register allocation is not disturbed by it.
+template <int DPAD, bool BF16, bool MASKED, int DROP>
 __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_constant__ BwdParams p) {
   constexpr int NB = DPAD / 64;
   constexpr uint32_t kTileBytes = NB * 16384u;   // 128 rows x DPAD 16-bit elements
@@ -391,11 +392,21 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       mbar_arrive(&sh.stats_ready);
     }
 
+    // Optional per-tile summary of a full mask tensor: the class of tile (i, j) is fetched one tile ahead.
+    const uint8_t* tile_class = nullptr;
+    const int tiles_k = (p.S_k + kTile - 1) / kTile;
+    if constexpr (MASKED) if (mods.mask_kind == 1 && mods.mask_tiles != nullptr)
+      tile_class = mods.mask_tiles + static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * ((p.S_q + kTile - 1) / kTile) * tiles_k + j;
+    int mask_class = 1, mask_class_next = 1;
+    if (tile_class != nullptr && n_iter > 0) mask_class_next = tile_class[static_cast<int64_t>(tile_of(0)) * tiles_k];
+
     for (int n = 0; n < n_iter; ++n) {
       const int i = tile_of(n);
       const int q_base = i * kTile;
       const int bh = b * p.N + head_of(n);
       if (n % max(n_per, 1) == 0) bias = bias_of(head_of(n));   // first tile of a query head
+      mask_class = mask_class_next;
+      if (tile_class != nullptr && n + 1 < n_iter) mask_class_next = tile_class[static_cast<int64_t>(tile_of(n + 1)) * tiles_k];
       // ---- P part: needs S^T only
       mbar_wait(&sh.st_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
@@ -418,10 +429,67 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       mbar_wait(&sh.stats_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
       const float* lse2 = sh.lse2[n & 1];
       const float* dlt = sh.delta[n & 1];
-      const bool use_mask = (mods.mask_kind == 1) || (mods.mask_kind == 2 && i == j);
+      // A mask tile that is all 0 is not read; one that is all 1 adds one constant to every score of the tile,
+      // which joins the key row's bias; any other tile is read.
+      const bool mask_const = MASKED && mods.mask_kind == 1 && mask_class == 2;
+      const bool use_mask = MASKED && ((mods.mask_kind == 1 && mask_class != 0 && !mask_const) || (mods.mask_kind == 2 && i == j));
+      const float tile_bias = mask_const ? bias - 10000.0f * kLog2e : bias;
       const bool diag = mods.causal && (q_base < j * kTile + kTile - 1);
-      const bool dropping = mods.drop != nullptr || mods.drop_philox != 0;
-      const bool generic = GENERIC && (use_mask || dropping || mods.tri_block > 0);
+      // TriangleAttention row groups: the rows of this Q tile see keys below the end of their group; the smallest
+      // such end is that of the tile's first row, and a K/V tile that lies wholly below it needs no per-element test
+      const bool tri_partial = MASKED && mods.tri_block > 0 &&
+                               (j * kTile + kTile > (q_base / mods.tri_block + 1) * mods.tri_block);
+
+      if constexpr (MASKED) if (use_mask || tri_partial) {
+        // Pass over this half's S^T columns in tensor memory: the mask term is added in score units (the common
+        // code multiplies by the scale afterwards) and (key, query) pairs outside the query's row group become
+        // -inf.  Loads use clamped (always valid) addresses so that they carry no branches: what they fetch for a
+        // key or query that does not exist meets a P that is exactly 0 there (bias = -inf / L = +inf).
+        const int kv_c = min(kv_idx, p.S_k - 1);
+        const float mask_unit = -10000.0f / p.scale;
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = hf * 2 + cc;
+          const int q0 = q_base + c * 32;
+          uint32_t sc[32];
+          tmem_ld32(t_st + c * 32, sc);
+          uint32_t mraw[16];
+          if (use_mask) {
+            if (mods.mask_kind == 1)
+              load_col32_raw(mods.mask, mods.mask_dtype, static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q, q0,
+                             p.S_q - 1, p.S_k, kv_c, mraw);
+            else   // the 128 x 128 tile: element (query in tile, key in tile)
+              load_col32_raw(mods.mask, mods.mask_dtype, 0, c * 32, kTile - 1, kTile, r, mraw);
+          }
+          tmem_wait_ld();
+          if (use_mask) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              sc[e] = __float_as_uint(fmaf(col_value(mraw[e >> 1], mods.mask_dtype, e & 1), mask_unit, __uint_as_float(sc[e])));
+          }
+          if (tri_partial) {
+            // first key that does not exist for query q0 + e: end of its row group
+            const int g0 = q0 / mods.tri_block;
+            const int rem0 = q0 - g0 * mods.tri_block;
+            const int end0 = (g0 + 1) * mods.tri_block;
+            if (mods.tri_block >= 32) {      // at most one group boundary inside the 32 queries
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const int lim = rem0 + e < mods.tri_block ? end0 : end0 + mods.tri_block;
+                sc[e] = kv_idx >= lim ? __float_as_uint(kNegInf) : sc[e];
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const int lim = ((q0 + e) / mods.tri_block + 1) * mods.tri_block;
+                sc[e] = kv_idx >= lim ? __float_as_uint(kNegInf) : sc[e];
+              }
+            }
+          }
+          tmem_st32(t_st + c * 32, sc);
+        }
+        tmem_wait_st();
+      }
 
       // P^T (dropped) goes over the first 32 of this half's own 64 S^T columns, which the half has
       // finished reading by then.
@@ -432,82 +500,32 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         tmem_ld32(t_st + (hf * 2) * 32, s[0]);
         tmem_ld32(t_st + (hf * 2 + 1) * 32, s[1]);
         tmem_wait_ld();
-        if (!generic) {
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
-            const int c = hf * 2 + cc;
-            if (diag) p_fast<true>(s[cc], lse2 + c * 32, p.scale_log2, bias, kv_idx, q_base + c * 32, pr[cc]);
-            else p_fast<false>(s[cc], lse2 + c * 32, p.scale_log2, bias, kv_idx, q_base + c * 32, pr[cc]);
-            uint32_t pk[16];
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = hf * 2 + cc;
+          uint32_t draw[16];       // dropout mask tensor: raw values of this chunk's queries, in flight under the exponentials
+          if constexpr (DROP == 2)
+            load_col32_raw(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q_base + c * 32, p.S_q - 1, p.S_k,
+                           min(kv_idx, p.S_k - 1), draw);
+          if (diag) p_fast<true>(s[cc], lse2 + c * 32, p.scale_log2, tile_bias, kv_idx, q_base + c * 32, pr[cc]);
+          else p_fast<false>(s[cc], lse2 + c * 32, p.scale_log2, tile_bias, kv_idx, q_base + c * 32, pr[cc]);
+          uint32_t pk[16];
+          if constexpr (DROP == 1) {
+            keep_bits[cc] = philox_keep_column(mods, bh, q_base + c * 32, p.S_q - 1, kv_idx, lane);
+#pragma unroll
+            for (int e = 0; e < 16; ++e)   // (explicit roundings: both dropout forms must give the same bits)
+              pk[e] = pack2<BF16>(__fmul_rn(pr[cc][2 * e], ((keep_bits[cc] >> (2 * e)) & 1u) ? mods.drop_scale : 0.f),
+                                  __fmul_rn(pr[cc][2 * e + 1], ((keep_bits[cc] >> (2 * e + 1)) & 1u) ? mods.drop_scale : 0.f));
+          } else if constexpr (DROP == 2) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              pk[e] = pack2<BF16>(__fmul_rn(pr[cc][2 * e], __fmul_rn(col_value(draw[e], mods.drop_dtype, 0), mods.drop_scale)),
+                                  __fmul_rn(pr[cc][2 * e + 1], __fmul_rn(col_value(draw[e], mods.drop_dtype, 1), mods.drop_scale)));
+          } else {
 #pragma unroll
             for (int e = 0; e < 16; ++e) pk[e] = pack2<BF16>(pr[cc][2 * e], pr[cc][2 * e + 1]);
-            tmem_st16(t_st + hf * 64 + cc * 16, pk);
           }
-        } else if constexpr (GENERIC) {
-          // general path: mask tensor, dropout mask, triangle row groups.  Loads use clamped (always valid)
-          // addresses so that they carry no branches: whatever they fetch for a key or query that does not
-          // exist is multiplied by a P that is exactly 0 there (bias = -inf / L = +inf).
-          const int kv_c = min(kv_idx, p.S_k - 1);
-#pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
-            const int c = hf * 2 + cc;
-            const int q0 = q_base + c * 32;
-            float add[32];
-            if (use_mask) {
-              if (mods.mask_kind == 1)
-                load_col32(mods.mask, mods.mask_dtype, static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q, q0,
-                           p.S_q - 1, p.S_k, kv_c, -10000.0f * kLog2e, add);
-              else   // the 128 x 128 tile: element (query in tile, key in tile)
-                load_col32(mods.mask, mods.mask_dtype, 0, c * 32, kTile - 1, kTile, r, -10000.0f * kLog2e, add);
-            } else {
-#pragma unroll
-              for (int e = 0; e < 32; ++e) add[e] = 0.f;
-            }
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              float pv = ex2(fmaf(__uint_as_float(s[cc][e]), p.scale_log2, bias) + add[e] - lse2[c * 32 + e]);
-              if (diag) pv = (kv_idx > q0 + e) ? 0.f : pv;
-              pr[cc][e] = pv;
-            }
-            if (mods.tri_block > 0) {
-              // first key that does not exist for query q0 + e: end of its row group
-              const int g0 = q0 / mods.tri_block;
-              const int rem0 = q0 - g0 * mods.tri_block;
-              const int end0 = (g0 + 1) * mods.tri_block;
-              if (mods.tri_block >= 32) {      // at most one group boundary inside the 32 queries
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                  const int lim = rem0 + e < mods.tri_block ? end0 : end0 + mods.tri_block;
-                  pr[cc][e] = kv_idx >= lim ? 0.f : pr[cc][e];
-                }
-              } else {
-#pragma unroll   // (static indices keep the probabilities in registers)
-                for (int e = 0; e < 32; ++e) {
-                  const int lim = ((q0 + e) / mods.tri_block + 1) * mods.tri_block;
-                  pr[cc][e] = kv_idx >= lim ? 0.f : pr[cc][e];
-                }
-              }
-            }
-            uint32_t pk[16];
-            if (dropping) {
-              float fac[32];
-              if (mods.drop_philox) {
-                keep_bits[cc] = philox_keep_column(mods, bh, q0, p.S_q - 1, kv_idx, lane);
-#pragma unroll
-                for (int e = 0; e < 32; ++e) fac[e] = ((keep_bits[cc] >> e) & 1u) ? mods.drop_scale : 0.f;
-              } else {
-                load_col32(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q0, p.S_q - 1, p.S_k, kv_c,
-                           mods.drop_scale, fac);
-              }
-#pragma unroll
-              for (int e = 0; e < 16; ++e)
-                pk[e] = pack2<BF16>(pr[cc][2 * e] * fac[2 * e], pr[cc][2 * e + 1] * fac[2 * e + 1]);
-            } else {
-#pragma unroll
-              for (int e = 0; e < 16; ++e) pk[e] = pack2<BF16>(pr[cc][2 * e], pr[cc][2 * e + 1]);
-            }
-            tmem_st16(t_st + hf * 64 + cc * 16, pk);
-          }
+          tmem_st16(t_st + hf * 64 + cc * 16, pk);
         }
       }
       tmem_wait_st();
@@ -519,14 +537,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       tc_fence_after_sync();
       {
         uint32_t dp[2][32];
-        tmem_ld32(t_dp + (hf * 2) * 32, dp[0]);
-        tmem_ld32(t_dp + (hf * 2 + 1) * 32, dp[1]);
-        tmem_wait_ld();
+        if constexpr (DROP == 0) {
+          tmem_ld32(t_dp + (hf * 2) * 32, dp[0]);
+          tmem_ld32(t_dp + (hf * 2 + 1) * 32, dp[1]);
+          tmem_wait_ld();
+        }
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           const int c = hf * 2 + cc;
           uint32_t dk_[16];
-          if (!GENERIC || (mods.drop == nullptr && !mods.drop_philox)) {
+          if constexpr (DROP == 0) {
 #pragma unroll
             for (int e4 = 0; e4 < 8; ++e4) {
               const float4 Dl = *reinterpret_cast<const float4*>(dlt + c * 32 + 4 * e4);
@@ -537,20 +557,31 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
               dk_[2 * e4] = pack2<BF16>(d0, d1);
               dk_[2 * e4 + 1] = pack2<BF16>(d2, d3);
             }
-          } else if constexpr (GENERIC) {
-            float fac[32];
-            if (mods.drop_philox) {   // the keep bits of this chunk were formed in the P part
+          } else {
+            // With dropout dP is multiplied by the pair's dropout factor before D is subtracted.  One chunk of
+            // dP^T at a time keeps the registers within the budget (the dS^T written below goes over columns of
+            // chunk 0, which is in registers by then, never over chunk 1).
+            tmem_ld32(t_dp + c * 32, dp[cc]);
+            uint32_t draw[16];
+            if constexpr (DROP == 2)
+              load_col32_raw(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q_base + c * 32, p.S_q - 1,
+                             p.S_k, min(kv_idx, p.S_k - 1), draw);
+            tmem_wait_ld();
 #pragma unroll
-              for (int e = 0; e < 32; ++e) fac[e] = ((keep_bits[cc] >> e) & 1u) ? mods.drop_scale : 0.f;
-            } else {
-              load_col32(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q_base + c * 32, p.S_q - 1, p.S_k,
-                         min(kv_idx, p.S_k - 1), mods.drop_scale, fac);
-            }
+            for (int e4 = 0; e4 < 8; ++e4) {
+              const float4 Dl = *reinterpret_cast<const float4*>(dlt + c * 32 + 4 * e4);
+              const float dl[4] = {Dl.x, Dl.y, Dl.z, Dl.w};
+              float d[4];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const float d0 = pr[cc][2 * e] * (__uint_as_float(dp[cc][2 * e]) * fac[2 * e] - dlt[c * 32 + 2 * e]);
-              const float d1 = pr[cc][2 * e + 1] * (__uint_as_float(dp[cc][2 * e + 1]) * fac[2 * e + 1] - dlt[c * 32 + 2 * e + 1]);
-              dk_[e] = pack2<BF16>(d0, d1);
+              for (int u = 0; u < 4; ++u) {
+                const int e = 4 * e4 + u;
+                float f;
+                if constexpr (DROP == 1) f = ((keep_bits[cc] >> e) & 1u) ? mods.drop_scale : 0.f;
+                else f = __fmul_rn(col_value(draw[e >> 1], mods.drop_dtype, e & 1), mods.drop_scale);
+                d[u] = __fmul_rn(pr[cc][e], __fmaf_rn(__uint_as_float(dp[cc][e]), f, -dl[u]));
+              }
+              dk_[2 * e4] = pack2<BF16>(d[0], d[1]);
+              dk_[2 * e4 + 1] = pack2<BF16>(d[2], d[3]);
             }
           }
           // dS^T goes to two places: over the first 32 of this half's own 64 dP^T columns (both chunks of which
@@ -686,15 +717,17 @@ cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : 128;
   const size_t smem = static_cast<size_t>(3 + kStages) * (dpad / 64) * 16384 + 2 * 32768 + sizeof(BwdShared);
   dim3 grid((p.S_k + kTile - 1) / kTile, p.B * (p.N / p.kv_group));
-  const bool generic = p.mods.mask_kind != 0 || p.mods.drop != nullptr || p.mods.drop_philox != 0 || p.mods.tri_block > 0;
+  const bool masked = p.mods.mask_kind != 0 || p.mods.tri_block > 0;
+  const int drop = p.mods.drop_philox != 0 ? 1 : (p.mods.drop != nullptr ? 2 : 0);
   void (*kern)(const BwdParams) = nullptr;
-  if (dpad == 64) {
-    if (generic) kern = bf16 ? fa_bwd_kernel<64, true, true> : fa_bwd_kernel<64, false, true>;
-    else kern = bf16 ? fa_bwd_kernel<64, true, false> : fa_bwd_kernel<64, false, false>;
-  } else {
-    if (generic) kern = bf16 ? fa_bwd_kernel<128, true, true> : fa_bwd_kernel<128, false, true>;
-    else kern = bf16 ? fa_bwd_kernel<128, true, false> : fa_bwd_kernel<128, false, false>;
-  }
+#define ACCT_BWD_PICK(DP, BF)                                                                          \
+  (masked ? (drop == 0 ? fa_bwd_kernel<DP, BF, true, 0> : drop == 1 ? fa_bwd_kernel<DP, BF, true, 1>   \
+                                                                    : fa_bwd_kernel<DP, BF, true, 2>)  \
+          : (drop == 0 ? fa_bwd_kernel<DP, BF, false, 0> : drop == 1 ? fa_bwd_kernel<DP, BF, false, 1> \
+                                                                     : fa_bwd_kernel<DP, BF, false, 2>))
+  if (dpad == 64) kern = bf16 ? ACCT_BWD_PICK(64, true) : ACCT_BWD_PICK(64, false);
+  else kern = bf16 ? ACCT_BWD_PICK(128, true) : ACCT_BWD_PICK(128, false);
+#undef ACCT_BWD_PICK
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   kern<<<grid, kBwdThreads, smem, stream>>>(p);

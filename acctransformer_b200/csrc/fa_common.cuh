@@ -159,6 +159,37 @@ __device__ __forceinline__ void load_col32(const void* base, int dtype, int64_t 
   }
 }
 
+// The same 32 values as load_col32, left raw and packed two to a register (element e in the low or high half of
+// word e / 2), so that 32 loads can be in flight at a cost of 16 registers; col_value() converts one on use.
+__device__ __forceinline__ void load_col32_raw(const void* base, int dtype, int64_t row_base, int row0, int row_max,
+                                               int64_t row_stride, int col, uint32_t (&raw)[16]) {
+  if (dtype == 2 /*U8*/) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(base) + col;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const uint32_t lo = p[(row_base + min(row0 + 2 * e, row_max)) * row_stride];
+      const uint32_t hi = p[(row_base + min(row0 + 2 * e + 1, row_max)) * row_stride];
+      raw[e] = lo | (hi << 16);
+    }
+  } else {
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + col;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const uint32_t lo = p[(row_base + min(row0 + 2 * e, row_max)) * row_stride];
+      const uint32_t hi = p[(row_base + min(row0 + 2 * e + 1, row_max)) * row_stride];
+      raw[e] = lo | (hi << 16);
+    }
+  }
+}
+
+// element `odd` (0 or 1) of a word written by load_col32_raw, as a float
+__device__ __forceinline__ float col_value(uint32_t word, int dtype, int odd) {
+  const uint32_t h = odd ? (word >> 16) : (word & 0xffffu);
+  if (dtype == 2 /*U8*/) return static_cast<float>(h);
+  if (dtype == 1 /*BF16*/) return __uint_as_float(h << 16);
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
+}
+
 // Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11): a counter-based generator,
 // so every (batch*head, query, key) position gets its random byte from its coordinates alone and the forward and
 // the backward reproduce the same dropout mask without storing it.

@@ -280,13 +280,28 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
     const int bound = min(min(kv_len, tri_end), mods.causal ? q_row + 1 : 0x7fffffff);
     const int bound_tile = min(min(kv_len, tri_end_tile), mods.causal ? q_tile * kTile + 1 : 0x7fffffff);
 
+    // Optional per-tile summary of a full mask tensor: the class of tile (q_tile, j) is fetched one tile ahead,
+    // before the wait for S, so that its latency is not on the path.
+    const uint8_t* tile_class = nullptr;
+    if constexpr (GENERIC) if (mods.mask_kind == 1 && mods.mask_tiles != nullptr)
+      tile_class = mods.mask_tiles + (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * ((p.S_q + kTile - 1) / kTile) +
+                                      min(q_tile, (p.S_q - 1) / kTile)) * ((p.S_k + kTile - 1) / kTile);
+    int mask_class = 1, mask_class_next = 1;
+    if (tile_class != nullptr && rng.lo <= rng.hi) mask_class_next = tile_class[rng.lo];
+
     float m_run = kNegInf, l_run = 0.f;
     int n = 0;
     for (int j = rng.lo; j <= rng.hi; ++j, ++n) {
+      mask_class = mask_class_next;
+      if (tile_class != nullptr && j < rng.hi) mask_class_next = tile_class[j + 1];
       mbar_wait(&sh.s_full[qt], n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
       const int col_base = j * kTile;
-      const bool use_mask = (mods.mask_kind == 1) || (mods.mask_kind == 2 && j == q_tile);
+      // a mask tile that is all 1 adds one constant to every score of the tile: without alibi it is folded into
+      // the exponent's offset below and the tile takes the plain path
+      const bool mask_const = GENERIC && mods.mask_kind == 1 && mask_class == 2 && !has_alibi;
+      const bool use_mask = (mods.mask_kind == 1 && mask_class != 0 && !mask_const) || (mods.mask_kind == 2 && j == q_tile);
+      const float tile_add = mask_const ? -10000.0f * kLog2e : 0.f;
       const bool generic = GENERIC && (use_mask || has_alibi);
       const bool partial = col_base + kTile > bound_tile;   // some (row, key) pairs of this tile do not exist
 
@@ -311,7 +326,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
           tmem_ld32(t_s + c * 32, sc);
           float add[32];
           if (use_mask) {
-            if (mods.mask_kind == 1)
+            if (mods.mask_kind == 1 && mask_class == 2) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) add[i] = -10000.0f * kLog2e;
+            } else if (mods.mask_kind == 1)
               load_row32(mods.mask, mods.mask_dtype, mask_row + col_base + c * 32, p.S_k - (col_base + c * 32), mask_vec,
                          -10000.0f * kLog2e, add);
             else
@@ -411,7 +429,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       uint32_t pk0[16];
       const bool speculate = n > 0;
       if (speculate) {
-        const float m_old = (m_run == kNegInf) ? 0.f : m_run;
+        float m_old = (m_run == kNegInf) ? 0.f : m_run;
+        if constexpr (GENERIC) m_old -= tile_add;
         exp_chunk(0, f2_pack(-m_old, -m_old), l_part, pk0);
       }
       float mx[4];
@@ -421,7 +440,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
 #pragma unroll
         for (int i = 1; i < 31; i += 2) mx[c] = fmax3(mx[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
       }
-      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * mult;   // scale > 0
+      float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * mult;   // scale > 0
+      if constexpr (GENERIC) m_tile += tile_add;
 
       const float m_new = fmaxf(m_run, m_tile);
       const bool grow = (m_new > m_run + kRescaleThreshold) || (m_run == kNegInf && m_new != kNegInf);
@@ -444,7 +464,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
           tmem_st32(t_o + c * 32, r);
         }
       }
-      const float m_use = (m_run == kNegInf) ? 0.f : m_run;
+      float m_use = (m_run == kNegInf) ? 0.f : m_run;
+      if constexpr (GENERIC) m_use -= tile_add;
       const uint64_t negm2 = f2_pack(-m_use, -m_use);
       if (!speculate || any_grow) {
 #pragma unroll
@@ -579,6 +600,36 @@ cudaError_t launch_mask_check(const void* mask, int dtype, int batch, int S_q, i
   const int64_t blocks = (total + 255) / 256;
   mask_check_kernel<<<static_cast<unsigned>(blocks < 148 * 16 ? (blocks < 1 ? 1 : blocks) : 148 * 16), 256, 0, stream>>>(
       mask, dtype, total, S_q, S_k, mismatch);
+  return cudaGetLastError();
+}
+
+// One block per 128x128 tile of a [batch, S_q, S_k] mask: class 0 if every element of the tile is 0, 2 if every
+// element is 1, else 1.  Thread t reads column t % 128 of every second row, so that a warp reads 32 consecutive
+// elements of a row.
+__global__ void mask_classify_kernel(const void* mask, int dtype, int S_q, int S_k, uint8_t* tiles) {
+  const int col = blockIdx.x * kTile + (threadIdx.x & 127);
+  const int64_t base = static_cast<int64_t>(blockIdx.z) * S_q * S_k;
+  int nonzero = 0, notone = 0;
+  if (col < S_k) {
+    for (int r = threadIdx.x >> 7; r < kTile; r += 2) {
+      const int row = blockIdx.y * kTile + r;
+      if (row >= S_q) break;
+      const float v = load_mask_value(mask, dtype, base + static_cast<int64_t>(row) * S_k + col);
+      nonzero |= (v != 0.0f);
+      notone |= (v != 1.0f);
+    }
+  }
+  nonzero = __syncthreads_or(nonzero);
+  notone = __syncthreads_or(notone);
+  if (threadIdx.x == 0)
+    tiles[(static_cast<int64_t>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x] =
+        static_cast<uint8_t>(!nonzero ? 0 : (!notone ? 2 : 1));
+}
+
+cudaError_t launch_mask_classify(const void* mask, int dtype, int batch, int S_q, int S_k, uint8_t* tiles,
+                                 cudaStream_t stream) {
+  dim3 grid((S_k + kTile - 1) / kTile, (S_q + kTile - 1) / kTile, batch);
+  mask_classify_kernel<<<grid, 256, 0, stream>>>(mask, dtype, S_q, S_k, tiles);
   return cudaGetLastError();
 }
 

@@ -16,6 +16,8 @@ struct ScoreMods {
   int prev_block_num, next_block_num;
   int mask_kind, mask_dtype, mask_batch;
   const void* mask;
+  const uint8_t* mask_tiles;        // optional [mask_batch, ceil(S_q/128), ceil(S_k/128)]: 0 = tile all 0 (not read),
+                                    // 2 = tile all 1 (fill value added, not read), 1 = read; null = read every tile
   const void* drop;
   int drop_dtype;
   float drop_scale;                 // 1/keep_prob for uint8 masks, 1 for pre-scaled 16-bit masks
@@ -77,6 +79,11 @@ struct DecodeParams {
 // counts into *mismatch the elements of a [batch, S_q, S_k] mask that differ from the causal mask (key > query)
 cudaError_t launch_mask_check(const void* mask, int dtype, int batch, int S_q, int S_k, unsigned int* mismatch,
                               cudaStream_t stream);
+
+// writes one class byte per 128x128 tile of a [batch, S_q, S_k] mask into tiles[batch, ceil(S_q/128), ceil(S_k/128)]:
+// 0 = all elements 0, 2 = all elements 1, 1 = anything else (ScoreMods::mask_tiles)
+cudaError_t launch_mask_classify(const void* mask, int dtype, int batch, int S_q, int S_k, uint8_t* tiles,
+                                 cudaStream_t stream);
 
 // Launchers: return cudaGetLastError() of the launch.
 cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream);

@@ -29,6 +29,14 @@ from .... import ops as _ops
 __all__ = ["get_flash_attention", "get_flash_attention_grad"]
 
 
+def _mask_tiles(attn_mask, enabled=True):
+    """Per-tile summary of a full attn_mask (made once per mask tensor, see ops.mask_tile_classes), with which the
+    kernels read only the 128x128 tiles of the mask that are neither all 0 nor all 1; None for no mask / the tile form."""
+    if not enabled or attn_mask is None or _is_tile_mask(attn_mask) or not attn_mask.is_cuda:
+        return None
+    return _ops.mask_tile_classes(attn_mask)
+
+
 def _is_tile_mask(attn_mask):
     if attn_mask is None:
         return False
@@ -49,7 +57,8 @@ def get_flash_attention_grad(prev_block_num=65536, next_block_num=65536, tiling_
                                 dropout_mask=dropout_mask, keep_prob=keep_prob, alibi=alibi_mask,
                                 prev_block_num=prev_block_num, next_block_num=next_block_num, scale=scale,
                                 grads_fp32=grads_fp32, deterministic=deterministic,
-                                dropout_seed=dropout_seed, dropout_offset=dropout_offset)
+                                dropout_seed=dropout_seed, dropout_offset=dropout_offset,
+                                mask_tiles=_mask_tiles(attn_mask))
 
     fa_grad.prev_block_num = prev_block_num
     fa_grad.next_block_num = next_block_num
@@ -60,12 +69,13 @@ def get_flash_attention_grad(prev_block_num=65536, next_block_num=65536, tiling_
 class _FlashAttentionFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, query, key, value, attn_mask, dropout_mask, alibi_mask, cfg):
+        ctx.mask_tiles = _mask_tiles(attn_mask, cfg.get("classify_mask_tiles", True))
         output, rowsum = _ops.fa_forward(
             query, key, value, attn_mask, mask_tile128=_is_tile_mask(attn_mask), causal=cfg["causal"],
             dropout_mask=dropout_mask, keep_prob=cfg["keep_prob"], alibi=alibi_mask,
             prev_block_num=cfg["prev_block_num"], next_block_num=cfg["next_block_num"], scale=cfg["scale"],
             tri_block=cfg.get("tri_block", 0), dropout_seed=cfg.get("dropout_seed"),
-            dropout_offset=cfg.get("dropout_offset", 0))
+            dropout_offset=cfg.get("dropout_offset", 0), mask_tiles=ctx.mask_tiles)
         ctx.save_for_backward(query, key, value, output, rowsum,
                               *(t for t in (attn_mask, dropout_mask, alibi_mask) if t is not None))
         ctx.present = (attn_mask is not None, dropout_mask is not None, alibi_mask is not None)
@@ -89,7 +99,8 @@ class _FlashAttentionFunction(torch.autograd.Function):
             keep_prob=cfg["keep_prob"], alibi=alibi_mask, prev_block_num=cfg["prev_block_num"],
             next_block_num=cfg["next_block_num"], scale=cfg["scale"], grads_fp32=False,
             tri_block=cfg.get("tri_block", 0), deterministic=cfg.get("deterministic", False),
-            dropout_seed=cfg.get("dropout_seed"), dropout_offset=cfg.get("dropout_offset", 0))
+            dropout_seed=cfg.get("dropout_seed"), dropout_offset=cfg.get("dropout_offset", 0),
+            mask_tiles=ctx.mask_tiles)
         return dq, dk, dv, None, None, None, None
 
 

@@ -39,7 +39,7 @@ def _strides3(t):
 
 def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
                   alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, flags=0, tri_block=0,
-                  dropout_seed=None, dropout_offset=0):
+                  dropout_seed=None, dropout_offset=0, mask_tiles=None):
     for name, t in (("q", q), ("k", k), ("v", v)):
         _require_cuda(name, t)
         if t.dim() != 4:
@@ -76,6 +76,15 @@ def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask
                 raise ValueError(f"attn_mask must be [1 or B, S_q, S_k], got {tuple(attn_mask.shape)}")
             a.mask_kind, a.mask_batch = MASK_FULL, m.shape[0]
         a.attn_mask = m.data_ptr()
+    if mask_tiles is not None:
+        if a.mask_kind != MASK_FULL:
+            raise ValueError("mask_tiles goes with a full attn_mask tensor")
+        _require_cuda("mask_tiles", mask_tiles)
+        want = (a.mask_batch, -(-S_q // 128), -(-S_k // 128))
+        if mask_tiles.dtype != torch.uint8 or tuple(mask_tiles.shape) != want or not mask_tiles.is_contiguous():
+            raise ValueError(f"mask_tiles must be a contiguous uint8 tensor {want}, as mask_tile_classes() returns it")
+        keep.append(mask_tiles)
+        a.mask_tiles = mask_tiles.data_ptr()
     a.causal = 1 if causal else 0
     a.keep_prob = float(keep_prob)
     if dropout_mask is not None:
@@ -122,8 +131,11 @@ def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask
 def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dropout_mask=None,
                keep_prob=1.0, alibi=None, alibi_slopes=None, prev_block_num=BAND_UNBOUNDED,
                next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None, need_lse=True, tri_block=0,
-               dropout_seed=None, dropout_offset=0):
+               dropout_seed=None, dropout_offset=0, mask_tiles=None):
     """Forward primitive: returns (output [B,N,S_q,D] in q's dtype, lse [B,N,S_q] fp32 or None).
+
+    ``mask_tiles`` (optional, from ``mask_tile_classes(attn_mask)``) lets the kernel skip reading the 128x128 tiles
+    of a full ``attn_mask`` that are all 0 or all 1; results are the same as without it.
 
     Dropout comes either as a tensor (``dropout_mask`` + ``keep_prob``) or is decided inside the kernel from
     ``dropout_seed`` / ``dropout_offset`` + ``keep_prob`` (no [B,N,S_q,S_k] tensor exists then; the backward must
@@ -133,7 +145,7 @@ def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dro
     lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if need_lse else None
     a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
                             alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, tri_block=tri_block,
-                            dropout_seed=dropout_seed, dropout_offset=dropout_offset)
+                            dropout_seed=dropout_seed, dropout_offset=dropout_offset, mask_tiles=mask_tiles)
     with torch.cuda.device(q.device):
         check(lib.acct_fa_fwd(C.byref(a), _stream()))
     del keep
@@ -144,7 +156,7 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
                 dropout_mask=None, keep_prob=1.0, alibi=None, alibi_slopes=None,
                 prev_block_num=BAND_UNBOUNDED, next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None,
                 grads_fp32=False, tri_block=0, deterministic=False, dropout_seed=None, dropout_offset=0,
-                kernel_events=None):
+                kernel_events=None, mask_tiles=None):
     """Grad primitive: returns (dq, dk, dv), fp32 when ``grads_fp32`` (what the reference primitive
     returns) else in q's dtype (what its bprop hands back after the cast)."""
     lib = load()
@@ -162,7 +174,8 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
     a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
                             alibi_slopes, prev_block_num, next_block_num, scale, seq_lens,
                             flags=(FLAG_GRAD_F32 if grads_fp32 else 0) | (FLAG_DETERMINISTIC if deterministic else 0),
-                            tri_block=tri_block, dropout_seed=dropout_seed, dropout_offset=dropout_offset)
+                            tri_block=tri_block, dropout_seed=dropout_seed, dropout_offset=dropout_offset,
+                            mask_tiles=mask_tiles)
     nbytes = lib.acct_fa_bwd_workspace_bytes(C.byref(a))
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     g = FaBwdIO()
@@ -180,6 +193,47 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
 
 
 _causal_cache = {}     # id(tensor) -> (weak reference to that tensor, its version counter, answer)
+_tiles_cache = {}      # the same for mask_tile_classes()
+
+
+def _recall(cache, t):
+    hit = cache.get(id(t))
+    if hit is not None and hit[0]() is t and hit[1] == t._version:
+        return hit
+    return None
+
+
+def _remember(cache, t, answer):
+    if len(cache) > 64:
+        for k_ in [k_ for k_, v_ in cache.items() if v_[0]() is None]:
+            del cache[k_]
+        if len(cache) > 64:
+            cache.clear()
+    cache[id(t)] = (weakref.ref(t), t._version, answer)
+
+
+def mask_tile_classes(attn_mask):
+    """uint8 tensor [Bm, ceil(S_q/128), ceil(S_k/128)] for the ``mask_tiles`` argument of fa_forward / fa_backward:
+    0 where the 128x128 tile of ``attn_mask`` ([S_q,S_k] or [Bm,S_q,S_k]) is all 0, 2 where it is all 1, else 1.
+    One pass over the mask on the GPU, no synchronisation.  Remembered per tensor object and version counter, like
+    mask_is_causal(): a mask that is built once and used by many layers and steps is summarised once."""
+    if attn_mask is None or attn_mask.dim() not in (2, 3) or attn_mask.dtype not in _DTYPES:
+        raise ValueError("attn_mask must be a [S_q,S_k] or [Bm,S_q,S_k] tensor of float16, bfloat16 or uint8")
+    _require_cuda("attn_mask", attn_mask)
+    hit = _recall(_tiles_cache, attn_mask)
+    if hit is not None:
+        return hit[2]
+    m = attn_mask.contiguous()
+    if m.dim() == 2:
+        m = m.unsqueeze(0)
+    lib = load()
+    tiles = torch.empty((m.shape[0], -(-m.shape[1] // 128), -(-m.shape[2] // 128)), dtype=torch.uint8, device=m.device)
+    assert tiles.numel() == lib.acct_mask_tiles_bytes(m.shape[0], m.shape[1], m.shape[2])
+    with torch.cuda.device(m.device):
+        check(lib.acct_mask_classify_tiles(m.data_ptr(), _dtype_code(m, "attn_mask"), m.shape[0], m.shape[1], m.shape[2],
+                                           tiles.data_ptr(), _stream()))
+    _remember(_tiles_cache, attn_mask, tiles)
+    return tiles
 
 
 def mask_is_causal(attn_mask):
@@ -190,9 +244,8 @@ def mask_is_causal(attn_mask):
     if attn_mask is None or attn_mask.dim() not in (2, 3) or attn_mask.dtype not in _DTYPES:
         return False
     _require_cuda("attn_mask", attn_mask)
-    key = id(attn_mask)
-    hit = _causal_cache.get(key)
-    if hit is not None and hit[0]() is attn_mask and hit[1] == attn_mask._version:
+    hit = _recall(_causal_cache, attn_mask)
+    if hit is not None:
         return hit[2]
     m = attn_mask.contiguous()
     if m.dim() == 2:
@@ -201,12 +254,7 @@ def mask_is_causal(attn_mask):
     with torch.cuda.device(m.device):
         check(load().acct_mask_is_causal(m.data_ptr(), _dtype_code(m, "attn_mask"), m.shape[0], m.shape[1], m.shape[2],
                                          C.byref(out), _stream()))
-    if len(_causal_cache) > 64:
-        for k_ in [k_ for k_, v_ in _causal_cache.items() if v_[0]() is None]:
-            del _causal_cache[k_]
-        if len(_causal_cache) > 64:
-            _causal_cache.clear()
-    _causal_cache[key] = (weakref.ref(attn_mask), attn_mask._version, bool(out.value))
+    _remember(_causal_cache, attn_mask, bool(out.value))
     return bool(out.value)
 
 

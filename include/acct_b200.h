@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define ACCT_ABI_VERSION 2
+#define ACCT_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define ACCT_API __attribute__((visibility("default")))
@@ -64,6 +64,11 @@ extern "C" {
 #define ACCT_BAND_BLOCK 128
 /* value added to a score per unit of attn_mask */
 #define ACCT_MASK_FILL_VALUE (-10000.0f)
+
+/* classes of a 128x128 mask tile (acct_fa_args.mask_tiles) */
+#define ACCT_MASK_TILE_ZERO 0
+#define ACCT_MASK_TILE_MIXED 1
+#define ACCT_MASK_TILE_ONE 2
 
 /* flags */
 #define ACCT_FLAG_GRAD_F32 1u      /* acct_fa_bwd writes dq/dk/dv as fp32 (what the reference primitive returns) */
@@ -126,6 +131,12 @@ typedef struct acct_fa_args {
   int32_t N_kv;             /* heads of k, v (and dk, dv): 0 or N = one per query head, as the reference requires
                                (nn/layer/flash_attention.py:193-196); a divisor of N = grouped-query attention, query
                                head n reads key/value head n / (N / N_kv); 1 = multi-query */
+  const uint8_t* mask_tiles;/* device or NULL.  Summary of an ACCT_MASK_FULL attn_mask, one byte per 128x128 tile,
+                               [mask_batch, ceil(S_q/128), ceil(S_k/128)], as acct_mask_classify_tiles writes it:
+                               ACCT_MASK_TILE_ZERO = every element of the tile is 0 (the kernels read nothing for it),
+                               ACCT_MASK_TILE_ONE = every element is 1 (the fill value is added without reading),
+                               ACCT_MASK_TILE_MIXED = the tile is read.  Results are those of reading every tile; the
+                               summary must describe the mask's current contents.  NULL = read every tile */
 } acct_fa_args;
 
 /* Extra I/O of the backward.
@@ -170,6 +181,17 @@ ACCT_API int acct_dropout_mask(const acct_fa_args* a, uint8_t* mask, void* strea
  * tensor, not per step.  *is_causal receives 1 or 0. */
 ACCT_API int acct_mask_is_causal(const void* mask, int32_t mask_dtype, int32_t mask_batch, int32_t S_q, int32_t S_k,
                                  int32_t* is_causal, void* stream);
+
+/* Summarises an attn_mask tensor [mask_batch, S_q, S_k] (ACCT_F16 / ACCT_BF16 / ACCT_U8, packed) per 128x128 tile
+ * into tiles[mask_batch, ceil(S_q/128), ceil(S_k/128)] (device, acct_mask_tiles_bytes() bytes) for
+ * acct_fa_args.mask_tiles.  A mask that is not causal (padding, documents, prefixes) is still mostly made of
+ * tiles that are all 0 or all 1; with the summary the kernels read only the mixed ones, where the reference reads
+ * every tile of every head (flash_attention_fwd.py:352-361, flash_attention_bwd.py:359-372).  One pass over the
+ * mask, enqueued on `stream` (no synchronisation); meant to be made once per mask tensor and reused by every
+ * forward and backward call that takes that mask. */
+ACCT_API size_t acct_mask_tiles_bytes(int32_t mask_batch, int32_t S_q, int32_t S_k);
+ACCT_API int acct_mask_classify_tiles(const void* mask, int32_t mask_dtype, int32_t mask_batch, int32_t S_q, int32_t S_k,
+                                      uint8_t* tiles, void* stream);
 
 /* Forward: writes o and (if non-NULL) lse. */
 ACCT_API int acct_fa_fwd(const acct_fa_args* a, void* stream);

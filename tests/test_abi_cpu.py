@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol(lib):
         assert hasattr(lib, name), name
     assert sorted(set(declared)) == sorted(set(_lib.EXPORTS) | (set(declared) - set(_lib.EXPORTS)))
     assert set(_lib.EXPORTS) <= set(declared)
-    assert lib.acct_abi_version() == 2
+    assert lib.acct_abi_version() == 3
 
 
 def test_ctypes_mirrors_match_c_layout(tmp_path):
@@ -38,7 +38,7 @@ def test_ctypes_mirrors_match_c_layout(tmp_path):
     fields = {
         "acct_fa_args": ["dtype", "q", "lse", "q_stride", "o_stride", "mask_kind", "attn_mask", "dropout_mask",
                          "dropout_dtype", "keep_prob", "alibi", "alibi_slopes", "prev_block_num", "scale",
-                         "seq_lens", "flags", "tri_block", "dropout_seed", "dropout_offset", "N_kv"],
+                         "seq_lens", "flags", "tri_block", "dropout_seed", "dropout_offset", "N_kv", "mask_tiles"],
         "acct_fa_bwd_io": ["d_o", "dq", "workspace", "workspace_bytes", "ev_kernel_start", "ev_kernel_stop"],
         "acct_infer_args": ["dtype", "rank", "D", "q", "y", "causal", "scale", "seq_lens", "N_kv"],
         "acct_decode_args": ["dtype", "D", "q", "kv_stride", "seq_lens", "y", "scale", "num_splits", "workspace",
@@ -88,6 +88,7 @@ def _args(**kw):
     (dict(mask_kind=1), 1),                  # full mask announced, pointer missing
     (dict(prev_block_num=-1), 2),
     (dict(tri_block=-5), 2),
+    (dict(mask_tiles=0x5000), 2),            # a tile summary without a full mask tensor
 ])
 def test_forward_validation_codes(lib, kw, code):
     a = _args(**kw)
@@ -115,6 +116,16 @@ def test_null_struct_pointers(lib):
     assert lib.acct_infer_decode(None, None) == 1
     assert lib.acct_fa_bwd_workspace_bytes(None) == 0
     assert lib.acct_infer_decode_workspace_bytes(None) == 0
+
+
+def test_mask_tile_summary_size_and_argument_checks(lib):
+    assert lib.acct_mask_tiles_bytes(2, 300, 1000) == 2 * 3 * 8        # one byte per 128x128 tile, edges rounded up
+    assert lib.acct_mask_tiles_bytes(1, 128, 128) == 1
+    assert lib.acct_mask_tiles_bytes(0, 128, 128) == 0
+    assert lib.acct_mask_classify_tiles(None, _lib.ACCT_U8, 1, 128, 128, 0x1000, None) == 1
+    assert lib.acct_mask_classify_tiles(0x1000, _lib.ACCT_U8, 1, 128, 128, None, None) == 1
+    assert lib.acct_mask_classify_tiles(0x1000, 7, 1, 128, 128, 0x2000, None) == 3      # ACCT_ERR_DTYPE
+    assert lib.acct_mask_classify_tiles(0x1000, _lib.ACCT_U8, 1, 0, 128, 0x2000, None) == 2
 
 
 def test_backward_workspace_size_and_rejection(lib):
@@ -204,7 +215,7 @@ int main(int argc, char** argv) {
     subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src),
                     "-ldl"], check=True)
     out = subprocess.run([str(exe), _lib.LIB_PATH], check=True, capture_output=True, text=True).stdout
-    assert "version 2 (header 2)" in out
+    assert "version 3 (header 3)" in out
     assert "null args -> 1" in out                      # ACCT_ERR_NULL
     assert "bad head_dim -> 4" in out                   # ACCT_ERR_UNSUPPORTED_D
     assert "null tensors -> 1" in out
