@@ -106,6 +106,60 @@ __device__ __forceinline__ uint32_t philox_keep_column(const ScoreMods& mods, in
   return bits;
 }
 
+// Pass over one half (64 query columns) of a thread's S^T row in tensor memory, for the tiles that need it: the
+// mask term is added in score units (the common code multiplies by the scale afterwards) and (key, query) pairs
+// outside the query's TriangleAttention row group become -inf.  Loads use clamped (always valid) addresses so
+// that they carry no branches: what they fetch for a key or query that does not exist meets a P that is exactly 0
+// there (bias = -inf / L = +inf).  Kept out of line: inlined, its registers disturb the allocation of the common
+// path of every tile, taken or not.
+__device__ __noinline__ void mask_prepass(const ScoreMods& mods, uint32_t t_st, int hf, int q_base, int kv_idx, int r,
+                                          int b, int S_q, int S_k, float scale, bool use_mask, bool tri_partial) {
+  const int kv_c = min(kv_idx, S_k - 1);
+  const float mask_unit = -10000.0f / scale;
+#pragma unroll 1
+  for (int cc = 0; cc < 2; ++cc) {
+    const int c = hf * 2 + cc;
+    const int q0 = q_base + c * 32;
+    uint32_t sc[32];
+    tmem_ld32(t_st + c * 32, sc);
+    uint32_t mraw[16];
+    if (use_mask) {
+      if (mods.mask_kind == 1)
+        load_col32_raw(mods.mask, mods.mask_dtype, static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * S_q, q0, S_q - 1,
+                       S_k, kv_c, mraw);
+      else   // the 128 x 128 tile: element (query in tile, key in tile)
+        load_col32_raw(mods.mask, mods.mask_dtype, 0, c * 32, kTile - 1, kTile, r, mraw);
+    }
+    tmem_wait_ld();
+    if (use_mask) {
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        sc[e] = __float_as_uint(fmaf(col_value(mraw[e >> 1], mods.mask_dtype, e & 1), mask_unit, __uint_as_float(sc[e])));
+    }
+    if (tri_partial) {
+      // first key that does not exist for query q0 + e: end of its row group
+      const int g0 = q0 / mods.tri_block;
+      const int rem0 = q0 - g0 * mods.tri_block;
+      const int end0 = (g0 + 1) * mods.tri_block;
+      if (mods.tri_block >= 32) {      // at most one group boundary inside the 32 queries
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int lim = rem0 + e < mods.tri_block ? end0 : end0 + mods.tri_block;
+          sc[e] = kv_idx >= lim ? __float_as_uint(kNegInf) : sc[e];
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int lim = ((q0 + e) / mods.tri_block + 1) * mods.tri_block;
+          sc[e] = kv_idx >= lim ? __float_as_uint(kNegInf) : sc[e];
+        }
+      }
+    }
+    tmem_st32(t_st + c * 32, sc);
+  }
+  tmem_wait_st();
+}
+
 }  // namespace
 
 // MASKED = a mask tensor or TriangleAttention row groups may be present: tiles that need them get a pass over S^T
@@ -440,56 +494,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       const bool tri_partial = MASKED && mods.tri_block > 0 &&
                                (j * kTile + kTile > (q_base / mods.tri_block + 1) * mods.tri_block);
 
-      if constexpr (MASKED) if (use_mask || tri_partial) {
-        // Pass over this half's S^T columns in tensor memory: the mask term is added in score units (the common
-        // code multiplies by the scale afterwards) and (key, query) pairs outside the query's row group become
-        // -inf.  Loads use clamped (always valid) addresses so that they carry no branches: what they fetch for a
-        // key or query that does not exist meets a P that is exactly 0 there (bias = -inf / L = +inf).
-        const int kv_c = min(kv_idx, p.S_k - 1);
-        const float mask_unit = -10000.0f / p.scale;
-#pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = hf * 2 + cc;
-          const int q0 = q_base + c * 32;
-          uint32_t sc[32];
-          tmem_ld32(t_st + c * 32, sc);
-          uint32_t mraw[16];
-          if (use_mask) {
-            if (mods.mask_kind == 1)
-              load_col32_raw(mods.mask, mods.mask_dtype, static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * p.S_q, q0,
-                             p.S_q - 1, p.S_k, kv_c, mraw);
-            else   // the 128 x 128 tile: element (query in tile, key in tile)
-              load_col32_raw(mods.mask, mods.mask_dtype, 0, c * 32, kTile - 1, kTile, r, mraw);
-          }
-          tmem_wait_ld();
-          if (use_mask) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e)
-              sc[e] = __float_as_uint(fmaf(col_value(mraw[e >> 1], mods.mask_dtype, e & 1), mask_unit, __uint_as_float(sc[e])));
-          }
-          if (tri_partial) {
-            // first key that does not exist for query q0 + e: end of its row group
-            const int g0 = q0 / mods.tri_block;
-            const int rem0 = q0 - g0 * mods.tri_block;
-            const int end0 = (g0 + 1) * mods.tri_block;
-            if (mods.tri_block >= 32) {      // at most one group boundary inside the 32 queries
-#pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                const int lim = rem0 + e < mods.tri_block ? end0 : end0 + mods.tri_block;
-                sc[e] = kv_idx >= lim ? __float_as_uint(kNegInf) : sc[e];
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                const int lim = ((q0 + e) / mods.tri_block + 1) * mods.tri_block;
-                sc[e] = kv_idx >= lim ? __float_as_uint(kNegInf) : sc[e];
-              }
-            }
-          }
-          tmem_st32(t_st + c * 32, sc);
-        }
-        tmem_wait_st();
-      }
+      if constexpr (MASKED) if (use_mask || tri_partial)
+        mask_prepass(mods, t_st, hf, q_base, kv_idx, r, b, p.S_q, p.S_k, p.scale, use_mask, tri_partial);
 
       // P^T (dropped) goes over the first 32 of this half's own 64 S^T columns, which the half has
       // finished reading by then.
