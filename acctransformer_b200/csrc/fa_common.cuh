@@ -218,10 +218,29 @@ struct DropoutRng {
 __device__ __forceinline__ uint32_t dropout_keep16(const DropoutRng& g, uint32_t bh, uint32_t q, uint32_t key16) {
   const uint4 r = philox4x32_10(q, key16, bh, g.offset, g.seed_lo, g.seed_hi);
   const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+  if (g.threshold >= 256u) return 0xffffu;         // keep everything (a byte is always below 256)
+  const uint32_t t4 = g.threshold * 0x01010101u;
   uint32_t bits = 0;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) bits |= (((w[i >> 2] >> (8 * (i & 3))) & 0xffu) < g.threshold ? 1u : 0u) << i;
+  for (int i = 0; i < 4; ++i) {
+    // four byte compares at once, then the four 0/1 bytes gathered into a nibble by one multiplication
+    // (the partial products land on distinct bits: 24..27 hold byte 0..3's decision)
+    const uint32_t ones = __vcmpltu4(w[i], t4) & 0x01010101u;
+    bits |= ((ones * 0x01020408u) >> 24 & 0xfu) << (4 * i);
+  }
   return bits;
+}
+
+// The same decisions as dropout_keep16, left as byte masks: byte i of word i / 4 ... i.e. m[w] has 0xff in byte k iff
+// key 4 * w + k of the 16 is kept.  One four-byte compare per word instead of sixteen extractions.
+__device__ __forceinline__ void dropout_keep16_bytes(const DropoutRng& g, uint32_t bh, uint32_t q, uint32_t key16,
+                                                     uint32_t (&m)[4]) {
+  const uint4 r = philox4x32_10(q, key16, bh, g.offset, g.seed_lo, g.seed_hi);
+  const uint32_t t4 = min(g.threshold, 255u) * 0x01010101u;   // (the kernels use the generator only below 256)
+  m[0] = __vcmpltu4(r.x, t4);
+  m[1] = __vcmpltu4(r.y, t4);
+  m[2] = __vcmpltu4(r.z, t4);
+  m[3] = __vcmpltu4(r.w, t4);
 }
 
 }  // namespace acct

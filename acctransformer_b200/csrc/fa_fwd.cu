@@ -385,27 +385,38 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         if constexpr (GENERIC) if (mods.drop != nullptr || mods.drop_philox) {
           dropped = true;
           const int col0 = col_base + c * 32;
-          float f[32];
           if (mods.drop_philox) {
-            // the mask is computed, not loaded: two generator calls give this row's 32 keep bits of the chunk
+            // the mask is computed, not loaded: two generator calls give this row's 32 keep decisions of the chunk
+            // as byte masks, which are widened to 16-bit lane masks and ANDed onto the packed, scaled probabilities
+            // (a dropped probability becomes +0, as p * 0 would)
             const DropoutRng rng = {mods.drop_seed_lo, mods.drop_seed_hi, mods.drop_offset, mods.drop_threshold};
             const uint32_t q_u = static_cast<uint32_t>(min(q_row, p.S_q - 1)), k16 = static_cast<uint32_t>(col0) >> 4;
-            const uint32_t bits = dropout_keep16(rng, static_cast<uint32_t>(bh), q_u, k16) |
-                                  (dropout_keep16(rng, static_cast<uint32_t>(bh), q_u, k16 + 1) << 16);
+            uint32_t km[8];
+            dropout_keep16_bytes(rng, static_cast<uint32_t>(bh), q_u, k16, *reinterpret_cast<uint32_t(*)[4]>(&km[0]));
+            dropout_keep16_bytes(rng, static_cast<uint32_t>(bh), q_u, k16 + 1, *reinterpret_cast<uint32_t(*)[4]>(&km[4]));
 #pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] = ((bits >> i) & 1u) ? mods.drop_scale : 0.f;
+            for (int i = 0; i < 16; ++i) {
+              float x0, x1;
+              f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])), mult2, negm2), x0, x1);
+              const float p0 = ex2(x0), p1 = ex2(x1);
+              l4[i & 3] = f2_add(l4[i & 3], f2_pack(p0, p1));
+              // elements 2i, 2i+1 of the chunk are bytes (2i & 3), (2i & 3) + 1 of word i / 2
+              const uint32_t lanes = __byte_perm(km[i >> 1], 0u, (i & 1) ? 0x3322u : 0x1100u);
+              pk[i] = pack2<BF16>(__fmul_rn(p0, mods.drop_scale), __fmul_rn(p1, mods.drop_scale)) & lanes;
+            }
           } else {
+            float f[32];
             const bool drop_vec = col_base + kTile <= p.S_k && (p.S_k & 15) == 0 &&
                                   (reinterpret_cast<uintptr_t>(mods.drop) & 15u) == 0;
             load_row32(mods.drop, mods.drop_dtype, drop_row + col0, p.S_k - col0, drop_vec, mods.drop_scale, f);
-          }
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float x0, x1;
-            f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])), mult2, negm2), x0, x1);
-            const float p0 = ex2(x0), p1 = ex2(x1);
-            l4[i & 3] = f2_add(l4[i & 3], f2_pack(p0, p1));
-            pk[i] = pack2<BF16>(p0 * f[2 * i], p1 * f[2 * i + 1]);
+            for (int i = 0; i < 16; ++i) {
+              float x0, x1;
+              f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])), mult2, negm2), x0, x1);
+              const float p0 = ex2(x0), p1 = ex2(x1);
+              l4[i & 3] = f2_add(l4[i & 3], f2_pack(p0, p1));
+              pk[i] = pack2<BF16>(__fmul_rn(p0, f[2 * i]), __fmul_rn(p1, f[2 * i + 1]));
+            }
           }
         }
         if (!dropped) {

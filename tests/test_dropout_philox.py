@@ -54,7 +54,8 @@ def dev():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("shape, keep, seed, offset", [((1, 2, 256, 256), 0.9, 42, 0), ((2, 3, 200, 333), 0.75, 2**40 + 5, 17),
-                                                       ((1, 1, 130, 17), 0.5, 7, 2**32 - 1)])
+                                                       ((1, 1, 130, 17), 0.5, 7, 2**32 - 1),
+                                                       ((1, 1, 64, 48), 1.0, 3, 0), ((1, 2, 40, 70), 0.002, 9, 1)])
 def test_materialised_mask_equals_the_oracle(dev, shape, keep, seed, offset):
     from acctransformer_b200 import ops
     B, N, S_q, S_k = shape
