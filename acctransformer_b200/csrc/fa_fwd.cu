@@ -75,9 +75,10 @@ struct FwdShared {
 
 }  // namespace
 
-// GENERIC = a mask tensor, alibi or a dropout mask may be present; the plain instantiation carries none of
-// that code, so its register allocation is not disturbed by it.
-template <int DPAD, bool BF16, bool GENERIC>
+// MODS: bit 0 = a mask tensor may be present, bit 1 = alibi may be present.  DROP: 0 no dropout, 1 in-kernel
+// generator, 2 dropout mask tensor.  Every instantiation carries only the code of what it may meet: code that is
+// compiled in but never run still costs the common path of every tile (register allocation, spills).
+template <int DPAD, bool BF16, int MODS, int DROP>
 __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_constant__ FwdParams p) {
   constexpr int NB = DPAD / 64;                 // 64-column (128-byte) blocks per row
   constexpr uint32_t kTileBytes = NB * 16384u;  // one 128-row tile
@@ -266,7 +267,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem + lane_base + kColS + qt * 128;
     const uint32_t t_o = tmem + lane_base + kColO + qt * DPAD;
-    const bool has_alibi = mods.alibi != nullptr || mods.alibi_slopes != nullptr;
+    constexpr bool GENERIC = MODS != 0;
+    const bool has_alibi = (MODS & 2) != 0 && (mods.alibi != nullptr || mods.alibi_slopes != nullptr);
     const float slope_l2 = mods.alibi_slopes != nullptr ? mods.alibi_slopes[h] * kLog2e : 0.f;
     const int64_t alibi_row = static_cast<int64_t>(bh) * p.S_k;
     const int64_t mask_row =
@@ -283,24 +285,35 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
     // Optional per-tile summary of a full mask tensor: the class of tile (q_tile, j) is fetched one tile ahead,
     // before the wait for S, so that its latency is not on the path.
     const uint8_t* tile_class = nullptr;
-    if constexpr (GENERIC) if (mods.mask_kind == 1 && mods.mask_tiles != nullptr)
+    if constexpr ((MODS & 1) != 0) if (mods.mask_kind == 1 && mods.mask_tiles != nullptr)
       tile_class = mods.mask_tiles + (static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * ((p.S_q + kTile - 1) / kTile) +
                                       min(q_tile, (p.S_q - 1) / kTile)) * ((p.S_k + kTile - 1) / kTile);
     int mask_class = 1, mask_class_next = 1;
     if (tile_class != nullptr && rng.lo <= rng.hi) mask_class_next = tile_class[rng.lo];
+    // alibi tensor: this thread's column of the next K/V tile, fetched one tile ahead and left raw until it is parked
+    // in shared memory (arithmetic on a fresh load would stall the warp for the whole memory latency)
+    const uint16_t* alibi_raw = reinterpret_cast<const uint16_t*>(mods.alibi) + alibi_row;
+    uint16_t al_raw = 0, al_raw_next = 0;
+    if constexpr ((MODS & 2) != 0) if (mods.alibi != nullptr && rng.lo <= rng.hi)
+      al_raw_next = alibi_raw[min(rng.lo * kTile + row_in_tile, p.S_k - 1)];
 
     float m_run = kNegInf, l_run = 0.f;
     int n = 0;
     for (int j = rng.lo; j <= rng.hi; ++j, ++n) {
       mask_class = mask_class_next;
       if (tile_class != nullptr && j < rng.hi) mask_class_next = tile_class[j + 1];
+      if constexpr ((MODS & 2) != 0) if (mods.alibi != nullptr) {
+        al_raw = al_raw_next;
+        if (j < rng.hi) al_raw_next = alibi_raw[min((j + 1) * kTile + row_in_tile, p.S_k - 1)];
+      }
       mbar_wait(&sh.s_full[qt], n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
       const int col_base = j * kTile;
       // a mask tile that is all 1 adds one constant to every score of the tile: without alibi it is folded into
       // the exponent's offset below and the tile takes the plain path
-      const bool mask_const = GENERIC && mods.mask_kind == 1 && mask_class == 2 && !has_alibi;
-      const bool use_mask = (mods.mask_kind == 1 && mask_class != 0 && !mask_const) || (mods.mask_kind == 2 && j == q_tile);
+      const bool mask_const = (MODS & 1) != 0 && mods.mask_kind == 1 && mask_class == 2 && !has_alibi;
+      const bool use_mask = (MODS & 1) != 0 && ((mods.mask_kind == 1 && mask_class != 0 && !mask_const) ||
+                                                (mods.mask_kind == 2 && j == q_tile));
       const float tile_add = mask_const ? -10000.0f * kLog2e : 0.f;
       const bool generic = GENERIC && (use_mask || has_alibi);
       const bool partial = col_base + kTile > bound_tile;   // some (row, key) pairs of this tile do not exist
@@ -312,14 +325,15 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         // the alibi row of this K/V tile goes through shared memory: one value per thread of the group,
         // double-buffered by tile parity so that one barrier per tile is enough
         float* al = sh.alibi[qt][n & 1];
-        if (mods.alibi != nullptr) {
-          const int col = col_base + row_in_tile;
-          al[row_in_tile] = col < p.S_k ? load16<BF16>(mods.alibi, alibi_row + col) * kLog2e : 0.f;
+        if constexpr ((MODS & 2) != 0) if (mods.alibi != nullptr) {
+          const float a = BF16 ? __uint_as_float(static_cast<uint32_t>(al_raw) << 16) : __half2float(__ushort_as_half(al_raw));
+          al[row_in_tile] = col_base + row_in_tile < p.S_k ? a * kLog2e : 0.f;
           named_barrier(1 + qt, 128);
         }
         // mask values are read 32 at a time (128-bit loads when the row segment is aligned and complete)
         const bool mask_vec = col_base + kTile <= p.S_k && (p.S_k & 15) == 0 &&
                               (reinterpret_cast<uintptr_t>(mods.mask) & 15u) == 0;
+        if constexpr ((MODS & 1) != 0) if (use_mask)
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {   // one 32-column chunk at a time, rewritten in place in tensor memory
           uint32_t sc[32];
@@ -341,13 +355,14 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
             for (int i = 0; i < 32; ++i) add[i] = 0.f;
           }
           // the branches are on tile-uniform conditions and sit outside the element loops
-          if (mods.alibi != nullptr) {
+          if constexpr ((MODS & 2) != 0) if (mods.alibi != nullptr) {
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
               const float4 a4 = *reinterpret_cast<const float4*>(al + c * 32 + 4 * i4);
               add[4 * i4] += a4.x; add[4 * i4 + 1] += a4.y; add[4 * i4 + 2] += a4.z; add[4 * i4 + 3] += a4.w;
             }
-          } else if (mods.alibi_slopes != nullptr) {
+          }
+          if constexpr ((MODS & 2) != 0) if (mods.alibi == nullptr && mods.alibi_slopes != nullptr) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) add[i] = fmaf(slope_l2, static_cast<float>(col_base + c * 32 + i), add[i]);
           }
@@ -359,7 +374,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
           }
           tmem_st32(t_s + c * 32, sc);
         }
-        tmem_wait_st();
+        if (use_mask) tmem_wait_st();
       }
 
       // the whole score row in registers, one wait
@@ -368,6 +383,34 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
       tmem_wait_ld();
 
+      if constexpr ((MODS & 2) != 0) if (generic && !use_mask) {
+        // alibi only: added in registers, in log2 units (no pass through tensor memory)
+        if (mods.alibi != nullptr) {
+          const float* al = sh.alibi[qt][n & 1];
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i4 = 0; i4 < 8; ++i4) {
+              const float4 a4 = *reinterpret_cast<const float4*>(al + c * 32 + 4 * i4);
+              const float a[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int i = 4 * i4 + u;
+                const float x = fmaf(__uint_as_float(s[c][i]), p.scale_log2, a[u]);
+                s[c][i] = __float_as_uint(col_base + c * 32 + i >= bound ? kNegInf : x);
+              }
+            }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float x = fmaf(__uint_as_float(s[c][i]), p.scale_log2,
+                                   slope_l2 * static_cast<float>(col_base + c * 32 + i));
+              s[c][i] = __float_as_uint(col_base + c * 32 + i >= bound ? kNegInf : x);
+            }
+        }
+      }
       if (!generic && partial) {
         // only positions that do not exist: one compare + select per element, no branches
 #pragma unroll
@@ -382,10 +425,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       const uint64_t mult2 = f2_pack(mult, mult);
       auto exp_chunk = [&](int c, uint64_t negm2, uint64_t (&l4)[4], uint32_t (&pk)[16]) {
         bool dropped = false;
-        if constexpr (GENERIC) if (mods.drop != nullptr || mods.drop_philox) {
+        if constexpr (DROP != 0) {
           dropped = true;
           const int col0 = col_base + c * 32;
-          if (mods.drop_philox) {
+          if constexpr (DROP == 1) {
             // the mask is computed, not loaded: two generator calls give this row's 32 keep decisions of the chunk
             // as byte masks, which are widened to 16-bit lane masks and ANDed onto the packed, scaled probabilities
             // (a dropped probability becomes +0, as p * 0 would)
@@ -441,7 +484,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       const bool speculate = n > 0;
       if (speculate) {
         float m_old = (m_run == kNegInf) ? 0.f : m_run;
-        if constexpr (GENERIC) m_old -= tile_add;
+        if constexpr ((MODS & 1) != 0) m_old -= tile_add;
         exp_chunk(0, f2_pack(-m_old, -m_old), l_part, pk0);
       }
       float mx[4];
@@ -452,7 +495,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         for (int i = 1; i < 31; i += 2) mx[c] = fmax3(mx[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
       }
       float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * mult;   // scale > 0
-      if constexpr (GENERIC) m_tile += tile_add;
+      if constexpr ((MODS & 1) != 0) m_tile += tile_add;
 
       const float m_new = fmaxf(m_run, m_tile);
       const bool grow = (m_new > m_run + kRescaleThreshold) || (m_run == kNegInf && m_new != kNegInf);
@@ -476,7 +519,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         }
       }
       float m_use = (m_run == kNegInf) ? 0.f : m_run;
-      if constexpr (GENERIC) m_use -= tile_add;
+      if constexpr ((MODS & 1) != 0) m_use -= tile_add;
       const uint64_t negm2 = f2_pack(-m_use, -m_use);
       if (!speculate || any_grow) {
 #pragma unroll
@@ -650,19 +693,23 @@ cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(nq + 2 * stages) * (dpad / 64) * 16384 + 1024;
   const int n_pairs = (p.S_q + nq * kTile - 1) / (nq * kTile);
   dim3 grid(static_cast<unsigned>(n_pairs) * static_cast<unsigned>(p.B * p.N));
-  const bool generic = p.mods.mask_kind != 0 || p.mods.alibi != nullptr || p.mods.alibi_slopes != nullptr ||
-                       p.mods.drop != nullptr || p.mods.drop_philox != 0;
+  int mods = (p.mods.mask_kind != 0 ? 1 : 0) | ((p.mods.alibi != nullptr || p.mods.alibi_slopes != nullptr) ? 2 : 0);
+  const int drop = p.mods.drop_philox != 0 ? 1 : (p.mods.drop != nullptr ? 2 : 0);
+  // head_dim 128 has every combination; the other two widths have "no mask, no alibi" and "both may be present"
+  if (dpad != 128 && mods != 0) mods = 3;
   void (*kern)(const FwdParams) = nullptr;
-  if (dpad == 64) {
-    if (generic) kern = bf16 ? fa_fwd_kernel<64, true, true> : fa_fwd_kernel<64, false, true>;
-    else kern = bf16 ? fa_fwd_kernel<64, true, false> : fa_fwd_kernel<64, false, false>;
-  } else if (dpad == 128) {
-    if (generic) kern = bf16 ? fa_fwd_kernel<128, true, true> : fa_fwd_kernel<128, false, true>;
-    else kern = bf16 ? fa_fwd_kernel<128, true, false> : fa_fwd_kernel<128, false, false>;
+#define ACCT_FWD_DROP(DP, BF, M) \
+  (drop == 0 ? fa_fwd_kernel<DP, BF, M, 0> : drop == 1 ? fa_fwd_kernel<DP, BF, M, 1> : fa_fwd_kernel<DP, BF, M, 2>)
+#define ACCT_FWD_BF(DP, M) (bf16 ? ACCT_FWD_DROP(DP, true, M) : ACCT_FWD_DROP(DP, false, M))
+  if (dpad == 128) {
+    kern = mods == 0 ? ACCT_FWD_BF(128, 0) : mods == 1 ? ACCT_FWD_BF(128, 1) : mods == 2 ? ACCT_FWD_BF(128, 2) : ACCT_FWD_BF(128, 3);
+  } else if (dpad == 64) {
+    kern = mods == 0 ? ACCT_FWD_BF(64, 0) : ACCT_FWD_BF(64, 3);
   } else {
-    if (generic) kern = bf16 ? fa_fwd_kernel<256, true, true> : fa_fwd_kernel<256, false, true>;
-    else kern = bf16 ? fa_fwd_kernel<256, true, false> : fa_fwd_kernel<256, false, false>;
+    kern = mods == 0 ? ACCT_FWD_BF(256, 0) : ACCT_FWD_BF(256, 3);
   }
+#undef ACCT_FWD_BF
+#undef ACCT_FWD_DROP
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   kern<<<grid, kFwdThreads, smem, stream>>>(p);
