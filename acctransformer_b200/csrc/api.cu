@@ -32,11 +32,12 @@ int fail_cuda(cudaError_t e, const char* what) {
 // per-device state
 // ---------------------------------------------------------------------------------------------
 __device__ unsigned int g_status_word = 0;
-__device__ unsigned int g_mask_mismatch;   // scratch of acct_mask_is_causal (one call at a time per device)
+__device__ unsigned int g_mask_mismatch;   // scratch of acct_mask_is_causal (calls are serialised by g_mask_mutex)
 
 namespace {
 constexpr int kMaxDevices = 64;
 std::mutex g_mutex;
+std::mutex g_mask_mutex;
 struct PerDevice {
   bool ready = false;
   int rc = 0;
@@ -307,6 +308,8 @@ int acct_mask_is_causal(const void* mask, int32_t mask_dtype, int32_t mask_batch
   if (mask_batch <= 0 || S_q <= 0 || S_k <= 0) return fail(ACCT_ERR_SHAPE, "mask_batch, S_q, S_k must be positive");
   if (device_status_ptr() == nullptr) return ACCT_ERR_NO_DEVICE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the scratch word is one per device: hold the lock until the answer has been read back
+  std::lock_guard<std::mutex> lock(g_mask_mutex);
   unsigned int* flag = nullptr;
   cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_mask_mismatch);
   if (e == cudaSuccess) e = cudaMemsetAsync(flag, 0, sizeof(unsigned int), s);

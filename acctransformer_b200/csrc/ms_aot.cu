@@ -15,8 +15,8 @@
 // Operator attributes (band limits, keep probability for uint8 masks, the scale) are not part of the call either:
 // acct_ms_set_fa_attrs() sets them for the process, as the reference bakes them into each primitive when it is built
 // (flash_attention_impl.py:146-152).
-#include <atomic>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/acct_b200.h"
 
@@ -30,7 +30,7 @@ struct FaAttrs {
   int causal = 0;
 };
 FaAttrs g_attrs;
-std::atomic<int> g_attrs_guard{0};   // bumped around updates; readers copy the struct (set-up time only)
+std::mutex g_attrs_mutex;            // set while a graph is built, copied by every call
 
 int dtype_code(const char* s) {
   if (s == nullptr) return -1;
@@ -88,7 +88,11 @@ bool fill_optionals(acct_fa_args& a, int first, int last, void** params, const i
 }
 
 void apply_attrs(acct_fa_args& a) {
-  const FaAttrs at = g_attrs;
+  FaAttrs at;
+  {
+    std::lock_guard<std::mutex> lock(g_attrs_mutex);
+    at = g_attrs;
+  }
   a.prev_block_num = at.prev_block_num;
   a.next_block_num = at.next_block_num;
   a.keep_prob = at.keep_prob;
@@ -102,13 +106,12 @@ extern "C" {
 
 // Process-wide operator attributes for the two training entry points below (set while the graph is built).
 ACCT_API void acct_ms_set_fa_attrs(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal) {
-  g_attrs_guard.fetch_add(1);
+  std::lock_guard<std::mutex> lock(g_attrs_mutex);
   g_attrs.prev_block_num = prev_block_num;
   g_attrs.next_block_num = next_block_num;
   g_attrs.keep_prob = keep_prob;
   g_attrs.scale = scale;
   g_attrs.causal = causal;
-  g_attrs_guard.fetch_add(1);
 }
 
 // inputs query, key, value, [attn_mask], [dropout_mask], [alibi_mask]; outputs output, rowsum
