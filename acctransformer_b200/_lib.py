@@ -29,7 +29,7 @@ EXPORTS = [
     "acct_infer_decode_workspace_bytes", "acct_infer_decode", "acct_infer_decode_static", "acct_device_status",
     "acct_last_error", "acct_abi_version",
     "acct_ms_set_fa_attrs", "acct_ms_fa_fwd", "acct_ms_fa_grad", "acct_ms_infer_fa", "acct_dropout_mask",
-    "acct_mask_is_causal", "acct_mask_tiles_bytes", "acct_mask_classify_tiles",
+    "acct_mask_is_causal", "acct_mask_tiles_bytes", "acct_mask_classify_tiles", "acct_mask_tiles_scratch",
 ]
 
 

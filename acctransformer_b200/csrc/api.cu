@@ -32,6 +32,9 @@ int fail_cuda(cudaError_t e, const char* what) {
 // per-device state
 // ---------------------------------------------------------------------------------------------
 __device__ unsigned int g_status_word = 0;
+// Scratch for a mask's per-tile summary, for callers that have nowhere to keep one (acct_mask_tiles_scratch).
+constexpr size_t kTilesScratchBytes = 1u << 20;
+__device__ uint8_t g_tiles_scratch[kTilesScratchBytes];
 __device__ unsigned int g_mask_mismatch;   // scratch of acct_mask_is_causal (calls are serialised by g_mask_mutex)
 
 namespace {
@@ -320,6 +323,13 @@ int acct_mask_is_causal(const void* mask, int32_t mask_dtype, int32_t mask_batch
   if (e != cudaSuccess) return fail_cuda(e, "checking the mask");
   *is_causal = host == 0 ? 1 : 0;
   return ACCT_OK;
+}
+
+uint8_t* acct_mask_tiles_scratch(size_t bytes) {
+  if (bytes == 0 || bytes > kTilesScratchBytes || device_status_ptr() == nullptr) return nullptr;
+  uint8_t* ptr = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_tiles_scratch) != cudaSuccess) return nullptr;
+  return ptr;
 }
 
 size_t acct_mask_tiles_bytes(int32_t mask_batch, int32_t S_q, int32_t S_k) {

@@ -87,6 +87,17 @@ bool fill_optionals(acct_fa_args& a, int first, int last, void** params, const i
   return true;
 }
 
+// A full attn_mask is summarised per 128x128 tile into the library's scratch buffer right before the call that reads
+// it (same stream), so that only the mask's mixed tiles are read; a mask too large for the buffer is read in full.
+int summarise_mask(acct_fa_args& a, void* stream) {
+  if (a.mask_kind != ACCT_MASK_FULL || a.attn_mask == nullptr) return ACCT_OK;
+  uint8_t* tiles = acct_mask_tiles_scratch(acct_mask_tiles_bytes(a.mask_batch, a.S_q, a.S_k));
+  if (tiles == nullptr) return ACCT_OK;
+  const int rc = acct_mask_classify_tiles(a.attn_mask, a.mask_dtype, a.mask_batch, a.S_q, a.S_k, tiles, stream);
+  if (rc == ACCT_OK) a.mask_tiles = tiles;
+  return rc;
+}
+
 void apply_attrs(acct_fa_args& a) {
   FaAttrs at;
   {
@@ -127,6 +138,7 @@ ACCT_API int acct_ms_fa_fwd(int nparam, void** params, int* ndims, int64_t** sha
   a.o = params[nparam - 2];
   a.lse = static_cast<float*>(params[nparam - 1]);
   apply_attrs(a);
+  if (const int rc = summarise_mask(a, stream)) return rc;
   return acct_fa_fwd(&a, stream);
 }
 
@@ -148,6 +160,7 @@ ACCT_API int acct_ms_fa_grad(int nparam, void** params, int* ndims, int64_t** sh
   a.o = params[3];
   a.lse = static_cast<float*>(params[5]);
   apply_attrs(a);
+  if (const int rc = summarise_mask(a, stream)) return rc;
   a.flags |= ACCT_FLAG_GRAD_F32;
   acct_fa_bwd_io g;
   std::memset(&g, 0, sizeof g);

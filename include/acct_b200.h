@@ -193,6 +193,12 @@ ACCT_API size_t acct_mask_tiles_bytes(int32_t mask_batch, int32_t S_q, int32_t S
 ACCT_API int acct_mask_classify_tiles(const void* mask, int32_t mask_dtype, int32_t mask_batch, int32_t S_q, int32_t S_k,
                                       uint8_t* tiles, void* stream);
 
+/* A device buffer of the library's own (1 MiB per GPU) for a summary of `bytes` bytes, or NULL if that does not fit:
+ * for a caller that has nowhere to keep one between calls and therefore makes it anew before every forward / backward
+ * (the entry points with MindSpore's calling convention do that).  One buffer per GPU: calls that use it must be
+ * ordered on one stream. */
+ACCT_API uint8_t* acct_mask_tiles_scratch(size_t bytes);
+
 /* Forward: writes o and (if non-NULL) lse. */
 ACCT_API int acct_fa_fwd(const acct_fa_args* a, void* stream);
 
