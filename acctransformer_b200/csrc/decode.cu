@@ -35,6 +35,26 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
   return v;
 }
 
+// two fp32 values in one 64-bit register and the two-wide fp32 instructions on them
+__device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2f(uint64_t r, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(r));
+}
+__device__ __forceinline__ uint64_t fma2f(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2f(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 template <bool BF16>
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -105,6 +125,21 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
 
   float m[G], l[G];
   float acc[G][8];
+  // G >= 4 (and at least G lanes per row): one head's softmax per lane, see the loop below
+  constexpr bool kScatter = G >= 4 && LPR >= G;
+  float m_own = -INFINITY, l_own = 0.f;
+  uint64_t acc2[G][4];                  // the accumulators as pairs (elements 2e, 2e+1)
+  uint64_t q2[(G + 1) / 2][8];          // the scaled queries of heads 2gp, 2gp+1 as pairs
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc2[g][e] = 0ull;
+  if constexpr (kScatter) {
+#pragma unroll
+    for (int gp = 0; gp < G / 2; ++gp)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q2[gp][e] = pack2f(qf[2 * gp][e], qf[2 * gp + 1][e]);
+  }
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     m[g] = -INFINITY;
@@ -113,8 +148,8 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
     for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
   }
 
-  for (int row0 = k0 + warp * (RPW * kCh); row0 < k1; row0 += kWarps * RPW * kCh) {
-    uint4 ku[kCh], vu[kCh];
+  // the K and V rows of one step of this warp (kCh row pairs), all loads issued back to back
+  auto issue_loads = [&](int row0, uint4 (&ku)[kCh], uint4 (&vu)[kCh]) {
     int64_t off[kCh];
 #pragma unroll
     for (int i = 0; i < kCh; ++i) {
@@ -131,46 +166,171 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
       const int row = row0 + i * RPW + rsub;
       vu[i] = (active && row < k1) ? ld_stream(vbase + off[i]) : make_uint4(0, 0, 0, 0);
     }
-    float s[G][kCh];
-    float cmax[G];
+  };
+  // With several heads of state per thread few CTAs fit an SM, and a warp that only loads, waits and then computes
+  // leaves the memory system idle while it computes: there the next step's rows are requested before this step's
+  // arithmetic (kAhead).  With one or two heads enough warps are resident for that to happen by itself.
+  constexpr int kStep = kWarps * RPW * kCh;
+  uint4 ku[kCh], vu[kCh], ku_next[kCh], vu_next[kCh];
+  const int row_first = k0 + warp * (RPW * kCh);
+  constexpr bool kAhead = kScatter && G >= 8;   // (at G = 4 the registers it takes cost a resident CTA: slower)
+  if constexpr (kAhead) { if (row_first < k1) issue_loads(row_first, ku, vu); }
+  for (int row0 = row_first; row0 < k1; row0 += kStep) {
+    if constexpr (kAhead) {
+      if (row0 + kStep < k1) issue_loads(row0 + kStep, ku_next, vu_next);
+    } else {
+      issue_loads(row0, ku, vu);
+    }
+    if constexpr (kScatter) {
+      // G >= 4: the G partial dot products of a lane are reduce-scattered over the LPR lanes of its row (halving
+      // exchanges on the high lane bits, then plain butterfly sums on the rest), so that a lane ends up with the
+      // complete score of ONE head, h_own: 8 shuffles instead of 32 per row at G = 8.  The lane runs that head's
+      // online softmax alone (one exponential per row instead of G) and hands the rescaling factor and the
+      // probabilities (rounded to 16 bits, two to a word, as the training kernels round P) round by shuffles.
+      float s_own[kCh];
 #pragma unroll
-    for (int g = 0; g < G; ++g) cmax[g] = -INFINITY;
+      for (int i = 0; i < kCh; ++i) {
+        float kf[8];
+        unpack8<BF16>(ku[i], kf);
+        uint64_t k2[8];
 #pragma unroll
-    for (int i = 0; i < kCh; ++i) {
-      float kf[8];
-      unpack8<BF16>(ku[i], kf);
-      const int row = row0 + i * RPW + rsub;
+        for (int e = 0; e < 8; ++e) k2[e] = pack2f(kf[e], kf[e]);
+        float v[G];
+#pragma unroll
+        for (int gp = 0; gp < G / 2; ++gp) {
+          uint64_t d2 = 0ull;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) d2 = fma2f(k2[e], q2[gp][e], d2);
+          unpack2f(d2, v[2 * gp], v[2 * gp + 1]);
+        }
+        int cnt = G;
+#pragma unroll
+        for (int bit = LPR / 2; bit >= 1; bit >>= 1) {
+          if (cnt > 1) {
+            const bool up = (sub & bit) != 0;
+            const int half = cnt / 2;
+#pragma unroll
+            for (int jj = 0; jj < G / 2; ++jj) {
+              if (jj < half) {
+                const float send = up ? v[jj] : v[jj + half];
+                const float keep = up ? v[jj + half] : v[jj];
+                v[jj] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+              }
+            }
+            cnt = half;
+          } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], bit);
+          }
+        }
+        const int row = row0 + i * RPW + rsub;
+        s_own[i] = row < k1 ? v[0] : -INFINITY;
+      }
+      float cmax_own = s_own[0];
+#pragma unroll
+      for (int i = 1; i < kCh; ++i) cmax_own = fmaxf(cmax_own, s_own[i]);
+      const float m_new = fmaxf(m_own, cmax_own);
+      const bool any = m_new != -INFINITY;
+      const float alpha_own = any ? ex2(m_own - m_new) : 1.0f;   // m_own = -inf gives 0; nothing accumulated then
+      float pr_own[kCh];
+      float psum = 0.f;
+#pragma unroll
+      for (int i = 0; i < kCh; ++i) {
+        pr_own[i] = any ? ex2(s_own[i] - m_new) : 0.f;
+        psum += pr_own[i];
+      }
+      l_own = fmaf(l_own, alpha_own, psum);
+      m_own = m_new;
+      uint32_t pr_pack[kCh / 2];
+#pragma unroll
+      for (int i = 0; i < kCh / 2; ++i) {
+        const __half2 h2 = __floats2half2_rn(pr_own[2 * i], pr_own[2 * i + 1]);
+        pr_pack[i] = *reinterpret_cast<const uint32_t*>(&h2);
+      }
+      float vf[kCh][8];
+#pragma unroll
+      for (int i = 0; i < kCh; ++i) unpack8<BF16>(vu[i], vf[i]);
+      uint64_t v2[kCh][4];
+#pragma unroll
+      for (int i = 0; i < kCh; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v2[i][e] = pack2f(vf[i][2 * e], vf[i][2 * e + 1]);
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        float d = 0.f;
+        const int src = (lane & ~(LPR - 1)) | (g * (LPR / G));   // first lane of my row that owns head g
+        const float alpha = __shfl_sync(0xffffffffu, alpha_own, src);
+        const uint64_t alpha2 = pack2f(alpha, alpha);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) d = fmaf(kf[e], qf[g][e], d);
+        for (int e = 0; e < 4; ++e) acc2[g][e] = mul2f(acc2[g][e], alpha2);
 #pragma unroll
-        for (int off = 1; off < LPR; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-        s[g][i] = row < k1 ? d : -INFINITY;
-        cmax[g] = fmaxf(cmax[g], s[g][i]);
-      }
-    }
-    float vf[kCh][8];
+        for (int i2 = 0; i2 < kCh / 2; ++i2) {
+          const uint32_t w = __shfl_sync(0xffffffffu, pr_pack[i2], src);
+          const float2 pp = __half22float2(*reinterpret_cast<const __half2*>(&w));
+          const uint64_t p0 = pack2f(pp.x, pp.x), p1 = pack2f(pp.y, pp.y);
 #pragma unroll
-    for (int i = 0; i < kCh; ++i) unpack8<BF16>(vu[i], vf[i]);
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float m_new = fmaxf(m[g], cmax[g]);
-      if (m_new != -INFINITY) {
-        const float alpha = ex2(m[g] - m_new);   // m = -inf gives 0
-        l[g] *= alpha;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[g][e] *= alpha;
-        m[g] = m_new;
-#pragma unroll
-        for (int i = 0; i < kCh; ++i) {
-          const float pr = ex2(s[g][i] - m_new);
-          l[g] += pr;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pr, vf[i][e], acc[g][e]);
+          for (int e = 0; e < 4; ++e) {
+            acc2[g][e] = fma2f(p0, v2[2 * i2][e], acc2[g][e]);
+            acc2[g][e] = fma2f(p1, v2[2 * i2 + 1][e], acc2[g][e]);
+          }
         }
       }
+      if constexpr (kAhead) if (row0 + kStep < k1) {
+#pragma unroll
+        for (int i = 0; i < kCh; ++i) { ku[i] = ku_next[i]; vu[i] = vu_next[i]; }
+      }
+    } else {
+      float s[G][kCh];
+      float cmax[G];
+  #pragma unroll
+      for (int g = 0; g < G; ++g) cmax[g] = -INFINITY;
+  #pragma unroll
+      for (int i = 0; i < kCh; ++i) {
+        float kf[8];
+        unpack8<BF16>(ku[i], kf);
+        const int row = row0 + i * RPW + rsub;
+  #pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float d = 0.f;
+  #pragma unroll
+          for (int e = 0; e < 8; ++e) d = fmaf(kf[e], qf[g][e], d);
+  #pragma unroll
+          for (int off = 1; off < LPR; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+          s[g][i] = row < k1 ? d : -INFINITY;
+          cmax[g] = fmaxf(cmax[g], s[g][i]);
+        }
+      }
+      float vf[kCh][8];
+  #pragma unroll
+      for (int i = 0; i < kCh; ++i) unpack8<BF16>(vu[i], vf[i]);
+  #pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float m_new = fmaxf(m[g], cmax[g]);
+        if (m_new != -INFINITY) {
+          const float alpha = ex2(m[g] - m_new);   // m = -inf gives 0
+          l[g] *= alpha;
+  #pragma unroll
+          for (int e = 0; e < 8; ++e) acc[g][e] *= alpha;
+          m[g] = m_new;
+  #pragma unroll
+          for (int i = 0; i < kCh; ++i) {
+            const float pr = ex2(s[g][i] - m_new);
+            l[g] += pr;
+  #pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pr, vf[i][e], acc[g][e]);
+          }
+        }
+      }
+  
+    }
+  }
+  if constexpr (kScatter) {
+    // back to the per-head state the merge below expects
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int src = (lane & ~(LPR - 1)) | (g * (LPR / G));
+      m[g] = __shfl_sync(0xffffffffu, m_own, src);
+      l[g] = __shfl_sync(0xffffffffu, l_own, src);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) unpack2f(acc2[g][e], acc[g][2 * e], acc[g][2 * e + 1]);
     }
   }
 

@@ -117,6 +117,26 @@ def test_prefill_and_decode_with_fewer_kv_heads(dev):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("D, N, N_kv, dtype", [(64, 8, 1, torch.float16), (64, 8, 2, torch.bfloat16), (256, 8, 1, torch.float16),
+                                               (256, 16, 4, torch.float16), (80, 8, 2, torch.float16)])
+def test_decode_group_sizes_at_other_head_dims(dev, D, N, N_kv, dtype):
+    """Groups of 4 and 8 query heads share their score reduction across the lanes of a cache row; the number of lanes
+    per row depends on head_dim (8, 16 or 32), so every width is checked."""
+    from acctransformer_b200 import ops
+    rs = np.random.RandomState(8)
+    B, S = 2, 1500
+    q = torch.tensor(rs.randn(B, N, 1, D).astype(np.float32)).to(dtype).to(dev)
+    kc = torch.tensor(rs.randn(B, N_kv, S, D).astype(np.float32)).to(dtype).to(dev)
+    vc = torch.tensor(rs.randn(B, N_kv, S, D).astype(np.float32)).to(dtype).to(dev)
+    lens = torch.tensor([1500, 77], dtype=torch.int32, device=dev)
+    scale = 1.0 / math.sqrt(D)
+    y = ops.infer_decode(q, kc, vc, lens, scale=scale)
+    y_ref = ref.decode_ref(_np(q), ref.expand_kv_heads(_np(kc), N), ref.expand_kv_heads(_np(vc), N), lens.cpu().numpy(), scale)
+    tol = 2e-3 if dtype == torch.float16 else 8e-3
+    assert np.max(np.abs(_np(y) - y_ref)) <= tol
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("N_kv, page", [(8, 16), (2, 64), (1, 256)])
 def test_decode_over_a_paged_cache(dev, N_kv, page):
     """Paged caches give the same bits as the contiguous cache they were cut from."""
