@@ -116,8 +116,14 @@ class FlashAttention(torch.nn.Module):
             else:
                 drop_mask = (torch.rand((bsz, head_num, seq_len, k.shape[2]), device=q.device,
                                         generator=self.generator) < self.keep_prob).to(torch.uint8)
-        implicit = (self.detect_causal_mask and attn_mask is not None and attn_mask.is_cuda
-                    and attn_mask.numel() != 128 * 128 and _ops.mask_is_causal(attn_mask))
+        implicit = False
+        if self.detect_causal_mask and attn_mask is not None and attn_mask.is_cuda:
+            if attn_mask.numel() != 128 * 128:
+                implicit = _ops.mask_is_causal(attn_mask)
+            elif self.flash_attention.next_block_num == 0 or max(seq_len, k.shape[2]) <= 128:
+                # the 128x128 tile form acts on the diagonal tiles only; with no tile above the diagonal in the band
+                # (next_block_num = 0), a tile that is exactly the strict upper triangle IS the causal mask
+                implicit = _ops.mask_is_causal(attn_mask.reshape(1, 128, 128))
         o, _ = self.flash_attention(q, k, v, attn_mask, drop_mask, alibi_mask, keep_prob=self.keep_prob,
                                     dropout_seed=seed, dropout_offset=offset, implicit_causal=implicit)
         return o

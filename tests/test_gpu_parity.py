@@ -439,3 +439,30 @@ def test_causal_mask_tensor_is_detected_and_not_read(dev):
         o_ref = ref.triangle_fwd(_np(qs), _np(k), _np(v), _np(mask), 128)
         _check_o(o, o_ref)
     _status()
+
+
+def test_cell_with_the_128x128_tile_mask_form(dev):
+    """have_attention_mask_batch=False: the [1,128,128] tile acts on the diagonal tiles only
+    (flash_attention_fwd.py:352-361).  With next_block_num = 0 a strict-upper-triangle tile is the causal mask and the
+    cell lets the kernels generate it; any other tile, or a band that reaches above the diagonal, is read."""
+    from acctransformer_b200.flash_attention.nn.layer.flash_attention import FlashAttention
+    B, N, S, D = 1, 2, 640, 64
+    scale = 1.0 / math.sqrt(D)
+    q, k, v = (_rand((B, N, S, D), s).to(dev).requires_grad_(True) for s in (31, 32, 33))
+    triu = torch.triu(torch.ones(1, 128, 128), 1).half().to(dev)
+    odd = triu.clone()
+    odd[0, 7, 3] = 1.0                           # not the causal tile: must be read
+    for tile, nxt in ((triu, 0), (odd, 0), (triu, 2)):
+        cell = FlashAttention(head_dim=D, next_block_num=nxt, have_attention_mask_batch=False)
+        o = cell(q, k, v, tile)
+        full = ref.expand_tile_mask(_np(tile), S, S)
+        o_ref, _ = ref.sa_fwd(_np(q), _np(k), _np(v), attn_mask=full, scale=scale, prev_block_num=65536, next_block_num=nxt)
+        _check_o(o, o_ref)
+        for t in (q, k, v):
+            t.grad = None
+        o.sum().backward()
+        g_ref = ref.sa_grad(_np(q), _np(k), _np(v), np.ones_like(o_ref), attn_mask=full, scale=scale,
+                            prev_block_num=65536, next_block_num=nxt)
+        for t, want, name in zip((q, k, v), g_ref, ("dq", "dk", "dv")):
+            _check_g(t.grad, want, name)
+    _status()
