@@ -255,6 +255,53 @@ def test_forward_head_dims_above_128(dev, D, S_q, S_k, causal):
         ops.fa_backward(q.to(dev), k.to(dev), v.to(dev), o, lse, o, causal=causal)
 
 
+@pytest.mark.parametrize("D, what, backward", [(64, "alibi", True), (64, "mask", True), (64, "slopes+dropout", True),
+                                               (128, "alibi", True), (128, "mask+philox", True), (128, "slopes", True),
+                                               (160, "mask", False), (160, "alibi+dropout", False), (256, "slopes", False)])
+def test_every_kernel_variant_of_every_width(dev, D, what, backward):
+    """The kernels are compiled per head_dim width (64 / 128 / 256) and per combination of mask, alibi and dropout
+    kind; head_dim 128 has every combination, the other widths fold mask and alibi into one variant.  One case per
+    family, ragged lengths, forward (and backward where head_dim allows) against the oracle."""
+    ops = _ops()
+    B, N, S_q, S_k = 2, 2, 200, 333
+    scale = 1.0 / math.sqrt(D)
+    q, k, v, do = (_rand((B, N, S, D), 150 + i, std=0.6) for i, S in enumerate((S_q, S_k, S_k, S_q)))
+    kw, okw = dict(scale=scale), dict(scale=scale)
+    mask = None
+    if "mask" in what:
+        m = (np.random.RandomState(3).random_sample((B, S_q, S_k)) < 0.3).astype(np.float32)
+        m[:, :, 0] = 0.0                                   # every row keeps a key
+        mask = torch.tensor(m).half().to(dev)
+        okw["attn_mask"] = m
+    if "alibi" in what:
+        al = ref.alibi_bias(B, N, S_k, np.float32)
+        kw["alibi"] = torch.tensor(al).half().to(dev)
+        okw["alibi"] = _np(kw["alibi"])
+    if "slopes" in what:
+        sl = np.asarray(ref.alibi_slopes(N), np.float32)
+        kw["alibi_slopes"] = torch.tensor(sl, device=dev)
+        okw["alibi"] = (sl[None, :, None, None] * np.arange(S_k, dtype=np.float32)[None, None, None, :]).repeat(B, 0)
+    if "dropout" in what:
+        dm = (np.random.RandomState(4).random_sample((B, N, S_q, S_k)) < 0.8).astype(np.uint8)
+        kw.update(dropout_mask=torch.tensor(dm).to(dev), keep_prob=0.8)
+        okw.update(drop_mask=dm, keep_prob=0.8)
+    if "philox" in what:
+        kw.update(keep_prob=0.75, dropout_seed=77, dropout_offset=5)
+        okw.update(drop_mask=ref.dropout_mask_philox(B, N, S_q, S_k, 0.75, 77, 5), keep_prob=ref.dropout_threshold(0.75) / 256.0)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    o, lse = ops.fa_forward(qd, kd, vd, mask, **kw)
+    _status()
+    o_ref, l_ref = ref.sa_fwd(q.numpy(), k.numpy(), v.numpy(), **okw)
+    _check_o(o, o_ref)
+    assert float(np.max(np.abs(_np(lse) - l_ref))) <= O_TOL
+    if backward:
+        grads = ops.fa_backward(qd, kd, vd, o, lse, do.to(dev), mask, **kw)
+        _status()
+        g_ref = ref.sa_grad(q.numpy(), k.numpy(), v.numpy(), do.numpy(), **okw)
+        for g, want, name in zip(grads, g_ref, ("dq", "dk", "dv")):
+            _check_g(g, want, name)
+
+
 # ---------------------------------------------------------------------------------------------
 # edge cases taken from the reference tests' shape lists, and ragged / mixed-option cases
 # ---------------------------------------------------------------------------------------------
