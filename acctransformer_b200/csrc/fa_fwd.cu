@@ -658,19 +658,38 @@ cudaError_t launch_mask_check(const void* mask, int dtype, int batch, int S_q, i
 }
 
 // One block per 128x128 tile of a [batch, S_q, S_k] mask: class 0 if every element of the tile is 0, 2 if every
-// element is 1, else 1.  Thread t reads column t % 128 of every second row, so that a warp reads 32 consecutive
-// elements of a row.
+// element is 1, else 1.  VEC: the tile's rows are whole 16-byte vectors (row length a multiple of 16 bytes, aligned
+// base, tile not cut by the right edge): a thread compares four 32-bit words per load with the bit pattern of 0 and
+// of 1 (-0.0 then counts as "not 0": the tile is read, which is always right).  Otherwise one element per load.
+template <bool VEC>
 __global__ void mask_classify_kernel(const void* mask, int dtype, int S_q, int S_k, uint8_t* tiles) {
-  const int col = blockIdx.x * kTile + (threadIdx.x & 127);
   const int64_t base = static_cast<int64_t>(blockIdx.z) * S_q * S_k;
   int nonzero = 0, notone = 0;
-  if (col < S_k) {
-    for (int r = threadIdx.x >> 7; r < kTile; r += 2) {
+  const bool full_width = blockIdx.x * kTile + kTile <= S_k;
+  if (VEC && full_width) {
+    const int esize = dtype == 2 ? 1 : 2;
+    const int vecs = kTile * esize / 16;                 // 16-byte vectors per tile row: 8 (u8) or 16
+    const uint32_t one = dtype == 2 ? 0x01010101u : (dtype == 1 ? 0x3f803f80u : 0x3c003c00u);
+    const int v = threadIdx.x % vecs;
+    const uint8_t* p0 = static_cast<const uint8_t*>(mask) + (base + static_cast<int64_t>(blockIdx.x) * kTile) * esize + v * 16;
+    for (int r = threadIdx.x / vecs; r < kTile; r += 256 / vecs) {
       const int row = blockIdx.y * kTile + r;
       if (row >= S_q) break;
-      const float v = load_mask_value(mask, dtype, base + static_cast<int64_t>(row) * S_k + col);
-      nonzero |= (v != 0.0f);
-      notone |= (v != 1.0f);
+      const uint4 u = *reinterpret_cast<const uint4*>(p0 + static_cast<int64_t>(row) * S_k * esize);
+      nonzero |= (u.x | u.y | u.z | u.w) != 0u;
+      notone |= (u.x != one) | (u.y != one) | (u.z != one) | (u.w != one);
+    }
+  } else {
+    // thread t reads column t % 128 of every second row: a warp reads 32 consecutive elements of a row
+    const int col = blockIdx.x * kTile + (threadIdx.x & 127);
+    if (col < S_k) {
+      for (int r = threadIdx.x >> 7; r < kTile; r += 2) {
+        const int row = blockIdx.y * kTile + r;
+        if (row >= S_q) break;
+        const float v = load_mask_value(mask, dtype, base + static_cast<int64_t>(row) * S_k + col);
+        nonzero |= (v != 0.0f);
+        notone |= (v != 1.0f);
+      }
     }
   }
   nonzero = __syncthreads_or(nonzero);
@@ -683,7 +702,10 @@ __global__ void mask_classify_kernel(const void* mask, int dtype, int S_q, int S
 cudaError_t launch_mask_classify(const void* mask, int dtype, int batch, int S_q, int S_k, uint8_t* tiles,
                                  cudaStream_t stream) {
   dim3 grid((S_k + kTile - 1) / kTile, (S_q + kTile - 1) / kTile, batch);
-  mask_classify_kernel<<<grid, 256, 0, stream>>>(mask, dtype, S_q, S_k, tiles);
+  const int esize = dtype == 2 ? 1 : 2;
+  const bool vec = (static_cast<int64_t>(S_k) * esize) % 16 == 0 && (reinterpret_cast<uintptr_t>(mask) & 15u) == 0;
+  if (vec) mask_classify_kernel<true><<<grid, 256, 0, stream>>>(mask, dtype, S_q, S_k, tiles);
+  else mask_classify_kernel<false><<<grid, 256, 0, stream>>>(mask, dtype, S_q, S_k, tiles);
   return cudaGetLastError();
 }
 
