@@ -723,7 +723,8 @@ cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : 128;
   const size_t smem = static_cast<size_t>(3 + kStages) * (dpad / 64) * 16384 + 2 * 32768 + sizeof(BwdShared);
   dim3 grid((p.S_k + kTile - 1) / kTile, p.B * (p.N / p.kv_group));
-  const bool masked = p.mods.mask_kind != 0 || p.mods.tri_block > 0;
+  // (row groups of a multiple of 128 rows never cut a tile: the tile ranges alone take care of them)
+  const bool masked = p.mods.mask_kind != 0 || (p.mods.tri_block > 0 && p.mods.tri_block % kTile != 0);
   const int drop = p.mods.drop_philox != 0 ? 1 : (p.mods.drop != nullptr ? 2 : 0);
   void (*kern)(const BwdParams) = nullptr;
 #define ACCT_BWD_PICK(DP, BF)                                                                          \
