@@ -116,46 +116,37 @@ __device__ __noinline__ void mask_prepass(const ScoreMods& mods, uint32_t t_st, 
                                           int b, int S_q, int S_k, float scale, bool use_mask, bool tri_partial) {
   const int kv_c = min(kv_idx, S_k - 1);
   const float mask_unit = -10000.0f / scale;
+  // sixteen queries at a time: the lighter this function is in registers, the less its call site costs the tiles
+  // that never come here
 #pragma unroll 1
-  for (int cc = 0; cc < 2; ++cc) {
-    const int c = hf * 2 + cc;
-    const int q0 = q_base + c * 32;
-    uint32_t sc[32];
-    tmem_ld32(t_st + c * 32, sc);
-    uint32_t mraw[16];
+  for (int piece = 0; piece < 4; ++piece) {
+    const int col = hf * 64 + piece * 16;           // first of the 16 S^T columns (queries) of this piece
+    const int q0 = q_base + col;
+    uint32_t sc[16];
+    tmem_ld16(t_st + col, sc);
+    uint32_t mraw[8];
     if (use_mask) {
       if (mods.mask_kind == 1)
-        load_col32_raw(mods.mask, mods.mask_dtype, static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * S_q, q0, S_q - 1,
-                       S_k, kv_c, mraw);
+        load_col_raw<8>(mods.mask, mods.mask_dtype, static_cast<int64_t>(mods.mask_batch > 1 ? b : 0) * S_q, q0, S_q - 1,
+                        S_k, kv_c, mraw);
       else   // the 128 x 128 tile: element (query in tile, key in tile)
-        load_col32_raw(mods.mask, mods.mask_dtype, 0, c * 32, kTile - 1, kTile, r, mraw);
+        load_col_raw<8>(mods.mask, mods.mask_dtype, 0, col, kTile - 1, kTile, r, mraw);
     }
     tmem_wait_ld();
     if (use_mask) {
 #pragma unroll
-      for (int e = 0; e < 32; ++e)
+      for (int e = 0; e < 16; ++e)
         sc[e] = __float_as_uint(fmaf(col_value(mraw[e >> 1], mods.mask_dtype, e & 1), mask_unit, __uint_as_float(sc[e])));
     }
     if (tri_partial) {
       // first key that does not exist for query q0 + e: end of its row group
-      const int g0 = q0 / mods.tri_block;
-      const int rem0 = q0 - g0 * mods.tri_block;
-      const int end0 = (g0 + 1) * mods.tri_block;
-      if (mods.tri_block >= 32) {      // at most one group boundary inside the 32 queries
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int lim = rem0 + e < mods.tri_block ? end0 : end0 + mods.tri_block;
-          sc[e] = kv_idx >= lim ? __float_as_uint(kNegInf) : sc[e];
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int lim = ((q0 + e) / mods.tri_block + 1) * mods.tri_block;
-          sc[e] = kv_idx >= lim ? __float_as_uint(kNegInf) : sc[e];
-        }
+      for (int e = 0; e < 16; ++e) {
+        const int lim = ((q0 + e) / mods.tri_block + 1) * mods.tri_block;
+        sc[e] = kv_idx >= lim ? __float_as_uint(kNegInf) : sc[e];
       }
     }
-    tmem_st32(t_st + c * 32, sc);
+    tmem_st16(t_st + col, sc);
   }
   tmem_wait_st();
 }

@@ -161,12 +161,13 @@ __device__ __forceinline__ void load_col32(const void* base, int dtype, int64_t 
 
 // The same 32 values as load_col32, left raw and packed two to a register (element e in the low or high half of
 // word e / 2), so that 32 loads can be in flight at a cost of 16 registers; col_value() converts one on use.
-__device__ __forceinline__ void load_col32_raw(const void* base, int dtype, int64_t row_base, int row0, int row_max,
-                                               int64_t row_stride, int col, uint32_t (&raw)[16]) {
+template <int NW>   // NW words = 2 * NW values
+__device__ __forceinline__ void load_col_raw(const void* base, int dtype, int64_t row_base, int row0, int row_max,
+                                             int64_t row_stride, int col, uint32_t (&raw)[NW]) {
   if (dtype == 2 /*U8*/) {
     const uint8_t* p = reinterpret_cast<const uint8_t*>(base) + col;
 #pragma unroll
-    for (int e = 0; e < 16; ++e) {
+    for (int e = 0; e < NW; ++e) {
       const uint32_t lo = p[(row_base + min(row0 + 2 * e, row_max)) * row_stride];
       const uint32_t hi = p[(row_base + min(row0 + 2 * e + 1, row_max)) * row_stride];
       raw[e] = lo | (hi << 16);
@@ -174,12 +175,16 @@ __device__ __forceinline__ void load_col32_raw(const void* base, int dtype, int6
   } else {
     const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + col;
 #pragma unroll
-    for (int e = 0; e < 16; ++e) {
+    for (int e = 0; e < NW; ++e) {
       const uint32_t lo = p[(row_base + min(row0 + 2 * e, row_max)) * row_stride];
       const uint32_t hi = p[(row_base + min(row0 + 2 * e + 1, row_max)) * row_stride];
       raw[e] = lo | (hi << 16);
     }
   }
+}
+__device__ __forceinline__ void load_col32_raw(const void* base, int dtype, int64_t row_base, int row0, int row_max,
+                                               int64_t row_stride, int col, uint32_t (&raw)[16]) {
+  load_col_raw<16>(base, dtype, row_base, row0, row_max, row_stride, col, raw);
 }
 
 // element `odd` (0 or 1) of a word written by load_col32_raw, as a float
