@@ -30,6 +30,7 @@ EXPORTS = [
     "acct_last_error", "acct_abi_version",
     "acct_ms_set_fa_attrs", "acct_ms_fa_fwd", "acct_ms_fa_grad", "acct_ms_infer_fa", "acct_dropout_mask",
     "acct_mask_is_causal", "acct_mask_tiles_bytes", "acct_mask_classify_tiles", "acct_mask_tiles_scratch",
+    "acct_selftest_wait_timeout",
 ]
 
 
@@ -130,6 +131,8 @@ def load():
     lib.acct_mask_tiles_bytes.restype = C.c_size_t
     lib.acct_mask_classify_tiles.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
     lib.acct_mask_classify_tiles.restype = C.c_int
+    lib.acct_selftest_wait_timeout.argtypes = [C.c_void_p]
+    lib.acct_selftest_wait_timeout.restype = C.c_int
     lib.acct_abi_version.argtypes = []
     lib.acct_abi_version.restype = C.c_int
     if lib.acct_abi_version() != ABI_VERSION:

@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "fa_kernels.cuh"
+#include "ptx.cuh"
 
 namespace acct {
 
@@ -36,6 +37,23 @@ __device__ unsigned int g_status_word = 0;
 constexpr size_t kTilesScratchBytes = 1u << 20;
 __device__ uint8_t g_tiles_scratch[kTilesScratchBytes];
 __device__ unsigned int g_mask_mismatch;   // scratch of acct_mask_is_causal (calls are serialised by g_mask_mutex)
+
+// One thread waits, with the same bounded wait the attention kernels use (poll limit 2^10 instead of 2^24), on a
+// barrier at which nothing ever arrives.  The wait runs out, the status word receives DEV_TIMEOUT_SYNC and the
+// kernel returns normally: what a real kernel does when a hand-off never comes, without any of its work.
+__global__ void wait_timeout_selftest_kernel(unsigned int* status) {
+  __shared__ uint64_t bar;
+  __shared__ volatile uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait<(1u << 10)>(&bar, 0, &abort_flag, status, DEV_TIMEOUT_SYNC);
+  __syncthreads();
+  linger_after_abort(&abort_flag);
+}
 
 namespace {
 constexpr int kMaxDevices = 64;
@@ -286,6 +304,15 @@ int acct_device_status(void* stream) {
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     return fail(ACCT_ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded wait (code %u: 1=TMA load, 2=MMA completion, 3=hand-off, 4=shared-memory base misaligned)", host);
   }
+  return ACCT_OK;
+}
+
+int acct_selftest_wait_timeout(void* stream) {
+  unsigned int* st = device_status_ptr();
+  if (st == nullptr) return ACCT_ERR_NO_DEVICE;
+  wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(st);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda(e, "launching the wait self-test kernel");
   return ACCT_OK;
 }
 

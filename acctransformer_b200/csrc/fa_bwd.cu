@@ -181,7 +181,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   const int n_kv = p.N / p.kv_group;
   const int bh_kv = blockIdx.y;
   const int b = bh_kv / n_kv, h_kv = bh_kv % n_kv;
-  const int j = blockIdx.x;                      // K/V tile
+  // K/V tile.  With an ordered dQ reduction the CTA of tile j waits for the CTAs of the later tiles (j' > j) that
+  // touch the same Q tile, so those must never be scheduled behind it: tiles are then handed out in descending
+  // order (thread blocks start in the order of their linear index), and every wait points at a CTA that is already
+  // running or finished, however many tiles a (batch, head) slice has and however few SMs are free.
+  const int j = p.dq_order != nullptr ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
   const ScoreMods& mods = p.mods;
 
   if ((smem_u32(smem) & 1023u) != 0u) {          // the swizzled tiles need a 1024-byte aligned base
@@ -649,6 +653,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     tc_fence_before_sync();
   }
 
+  linger_after_abort(abort_flag);
   __syncthreads();
   if (warp == kProducerWarp) {
     tc_fence_after_sync();

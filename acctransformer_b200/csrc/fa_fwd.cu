@@ -600,6 +600,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
     tc_fence_before_sync();
   }
 
+  linger_after_abort(abort_flag);
   __syncthreads();
   if (warp == 8) {
     tc_fence_after_sync();

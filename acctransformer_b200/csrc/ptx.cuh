@@ -70,6 +70,7 @@ constexpr long long kWaitCycleLimit = 2000000000LL;
 // takes from tens of cycles to a hardware-defined suspend time, so 2^24 polls are between a fraction of a
 // second and some tens of seconds.
 constexpr uint32_t kWaitPollLimit = 1u << 24;
+template <uint32_t kLimit = kWaitPollLimit>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned int* status, unsigned int code) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -77,7 +78,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   do {
     if ((++polls & 0x3fu) == 0u) {
       if (*abort_flag != 0u) return false;
-      if (polls >= kWaitPollLimit) {
+      if (polls >= kLimit) {
         *abort_flag = 1u;
         atomicMax(status, code);
         return false;
@@ -85,6 +86,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
   } while (!mbar_try_wait(bar, parity));
   return true;
+}
+
+// Called by every thread of a CTA right before its final barrier.  A CTA that gave up on a wait may still have TMA
+// loads of its own in flight; they would land in shared memory that the next CTA on the SM already owns.  Such a CTA
+// therefore idles for a bounded time (about a quarter of a millisecond, hundreds of times what a load needs) before
+// it retires.  The normal path pays one shared-memory read.
+__device__ __forceinline__ void linger_after_abort(volatile uint32_t* abort_flag) {
+  if (*abort_flag != 0u)
+    for (int i = 0; i < 128; ++i) __nanosleep(2000);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -11,8 +11,13 @@
  *     strides of B, N and S are given explicitly; 0 means "packed" (S stride D, N stride S*D,
  *     B stride N*S*D).  Every stride must be a multiple of 8 elements (16 bytes) and every base
  *     pointer 16-byte aligned.
+ *   - The device that `stream` belongs to must be the calling thread's current device (per-device
+ *     state, such as the status word and built-in scratch, is looked up through the current device).
  *   - Return value: 0 on success, otherwise one of the ACCT_ERR_* codes; acct_last_error() gives
  *     a message for the calling thread.  No C++ exception crosses this boundary.
+ *   - Calls return before the kernels run.  A kernel that gives up on a bounded wait leaves garbage
+ *     in its outputs and reports it ONLY through the device status word: call acct_device_status()
+ *     wherever the host synchronises anyway (end of a step, before results are consumed).
  *   - There is no CPU fallback: without a usable sm_100 device the entry points fail.
  *
  * Paths below are relative to the reference project (mindspore-ai/acctransformer).
@@ -308,6 +313,12 @@ ACCT_API int acct_ms_infer_fa(int nparam, void** params, int* ndims, int64_t** s
 /* Reads and clears the device-side status word of the current device (synchronises `stream`).
  * Returns ACCT_OK, or ACCT_ERR_DEVICE_TIMEOUT if some kernel gave up on a bounded wait since the last call. */
 ACCT_API int acct_device_status(void* stream);
+
+/* Failure-reporting self-test: enqueues a one-thread kernel whose bounded wait is certain to run out (it waits, with
+ * a small poll limit, on a barrier nothing arrives at), so that the next acct_device_status() returns
+ * ACCT_ERR_DEVICE_TIMEOUT.  The kernel returns normally; the context stays usable and later calls are unaffected.
+ * No counterpart in the reference (its kernels have no waits that can be observed from the host). */
+ACCT_API int acct_selftest_wait_timeout(void* stream);
 
 /* Message for the last non-zero return on the calling thread ("" if none). */
 ACCT_API const char* acct_last_error(void);

@@ -299,13 +299,18 @@ def dropout_threshold(keep_prob):
     return min(256, max(1, t))
 
 
-def dropout_mask_philox(B, N, S_q, S_k, keep_prob, seed, offset=0):
+def dropout_mask_philox(B, N, S_q, S_k, keep_prob, seed, offset=0, units=None):
     """uint8 {0,1} mask [B,N,S_q,S_k]: position (b,n,q,k) is kept iff byte (k & 15) of
-    Philox(counter = (q, k >> 4, b*N + n, offset), key = (seed low, seed high)) is below the threshold."""
+    Philox(counter = (q, k >> 4, b*N + n, offset), key = (seed low, seed high)) is below the threshold.
+    ``units``: a list of unit numbers b*N + n; the result is then [len(units), 1, S_q, S_k] for those units only."""
     groups = (S_k + 15) // 16
     q = np.arange(S_q, dtype=np.uint32).reshape(1, S_q, 1)
     g = np.arange(groups, dtype=np.uint32).reshape(1, 1, groups)
-    u = np.arange(B * N, dtype=np.uint32).reshape(B * N, 1, 1)
+    if units is not None:
+        u = np.asarray(units, dtype=np.uint32).reshape(-1, 1, 1)
+        B, N = u.shape[0], 1
+    else:
+        u = np.arange(B * N, dtype=np.uint32).reshape(B * N, 1, 1)
     shape = (B * N, S_q, groups)
     words = philox4x32_10([np.broadcast_to(q, shape), np.broadcast_to(g, shape), np.broadcast_to(u, shape),
                            np.full(shape, offset & 0xFFFFFFFF, dtype=np.uint32)],

@@ -3,8 +3,9 @@
 Some callers cannot call cudaMalloc when they need a decode step (their memory pool is fixed at
 start-up, or they sit inside a framework that forbids allocation mid-step), so the library also
 offers the decode step with its split-KV scratch built in.  This test drives both entry points
-through the C ABI on the same inputs, twice in a row with different inputs, so that whatever the
-first call left in the shared scratch is shown not to leak into the second.  It lives in its own
+through the C ABI on the same inputs, several times in a row with different inputs, so that whatever
+one call left in the shared scratch is shown not to leak into the next; the results must be
+bit-identical between the two entry points and within tolerance of the CPU oracle.  It lives in its own
 file, collected last, so a run that stops at the first failure has already run everything else.
 """
 import ctypes as C
@@ -13,15 +14,18 @@ import math
 import pytest
 import torch
 
+from oracle import attention_ref as ref
+
 pytestmark = pytest.mark.gpu
 
-TOL = 2e-3      # the decode tolerance used by the other GPU tests (max-abs on y)
+TOL = 2e-3      # the decode tolerance used by the other GPU tests (max-abs on y), here against the CPU oracle
 
 
 def _args(lib_mod, q, kc, vc, lens, y, scale, splits, ws=None):
     a = lib_mod.DecodeArgs()
-    a.dtype = lib_mod.ACCT_F16
+    a.dtype = lib_mod.ACCT_BF16 if q.dtype == torch.bfloat16 else lib_mod.ACCT_F16
     a.B, a.N, a.S_max, a.D = q.shape[0], q.shape[1], kc.shape[2], q.shape[3]
+    a.N_kv = kc.shape[1]
     a.q, a.k_cache, a.v_cache, a.y = q.data_ptr(), kc.data_ptr(), vc.data_ptr(), y.data_ptr()
     a.seq_lens = lens.data_ptr()
     a.scale = scale
@@ -41,11 +45,13 @@ def test_static_scratch_decode_matches_regular_decode_twice_in_a_row():
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     B, N, S, D = 4, 8, 4096, 128
     scale = 1.0 / math.sqrt(D)
-    for call, (seed, splits) in enumerate(((1, 0), (2, 5))):
+    # second and third call: other inputs, another split count, then grouped key/value heads in bf16
+    for call, (seed, splits, n_kv, dt) in enumerate(((1, 0, N, torch.float16), (2, 5, N, torch.float16),
+                                                      (3, 3, N // 4, torch.bfloat16))):
         g = torch.Generator(device=dev).manual_seed(seed)
-        q = torch.randn(B, N, 1, D, device=dev, generator=g).to(torch.float16)
-        kc = torch.randn(B, N, S, D, device=dev, generator=g).to(torch.float16)
-        vc = torch.randn(B, N, S, D, device=dev, generator=g).to(torch.float16)
+        q = torch.randn(B, N, 1, D, device=dev, generator=g).to(dt)
+        kc = torch.randn(B, n_kv, S, D, device=dev, generator=g).to(dt)
+        vc = torch.randn(B, n_kv, S, D, device=dev, generator=g).to(dt)
         lens = torch.randint(1, S + 1, (B,), device=dev, generator=g, dtype=torch.int32)
         y_ref = torch.zeros_like(q)
         y_new = torch.zeros_like(q)
@@ -56,9 +62,15 @@ def test_static_scratch_decode_matches_regular_decode_twice_in_a_row():
         _lib.check(lib.acct_infer_decode_static(C.byref(_args(_lib, q, kc, vc, lens, y_new, scale, splits)), stream))
         torch.cuda.synchronize()
         _lib.device_status()
-        err = float((y_new.float() - y_ref.float()).abs().max())
-        assert err <= TOL, f"call {call}: max|y_static - y| = {err}"
+        # the two entry points run the same kernels with the same split count: the results are the same bits
+        assert torch.equal(y_new, y_ref), f"call {call}: static-scratch decode differs from the regular decode"
         assert float(y_ref.float().abs().max()) > 0.0
+        # and both agree with the CPU oracle (key/value heads repeated for the grouped case, as the reference prescribes)
+        rep = N // n_kv
+        want = ref.decode_ref(q.float().cpu().numpy(), kc.float().cpu().numpy().repeat(rep, axis=1),
+                              vc.float().cpu().numpy().repeat(rep, axis=1), lens.cpu().numpy(), scale)
+        err = float((y_new.float().cpu() - torch.tensor(want)).abs().max())
+        assert err <= (TOL if dt == torch.float16 else 4 * TOL), f"call {call}: max|y_static - y_oracle| = {err}"
 
 
 def test_static_scratch_decode_refuses_what_does_not_fit():
