@@ -12,9 +12,12 @@
 //   rank 3 (or rank 2 128x128)            attn_mask  [1 or B, S_q, S_k] / [1,128,128]
 //   rank 4 with shape [B,N,1,S_k]         alibi_mask (when S_q != 1)
 //   rank 4 with shape [B,N,S_q,S_k]       dropout_mask
-// Operator attributes (band limits, keep probability for uint8 masks, the scale) are not part of the call either:
-// acct_ms_set_fa_attrs() sets them for the process, as the reference bakes them into each primitive when it is built
-// (flash_attention_impl.py:146-152).
+// Operator attributes (band limits, keep probability for uint8 masks, the scale) are not part of the call either.  The
+// reference bakes them into each primitive when it is built (flash_attention_impl.py:146-152), so that two layers of
+// one graph can differ; here a primitive is bound to one of kSlots numbered attribute slots by the NAME of the entry
+// point it calls: acct_ms_fa_attrs_slot() stores a tuple of attributes and returns its slot k, and the operator is
+// registered on acct_ms_fa_fwd_s<k> / acct_ms_fa_grad_s<k>.  The unnumbered entry points use the process-wide default
+// that acct_ms_set_fa_attrs() sets.
 #include <cstring>
 #include <mutex>
 
@@ -29,7 +32,10 @@ struct FaAttrs {
   float scale = 1.0f;   // the raw primitive does not scale (the cell pre-multiplies q and k)
   int causal = 0;
 };
-FaAttrs g_attrs;
+constexpr int kSlots = 32;
+FaAttrs g_attrs;                     // the process-wide default (slot -1)
+FaAttrs g_slot[kSlots];
+int g_slots_used = 0;
 std::mutex g_attrs_mutex;            // set while a graph is built, copied by every call
 
 int dtype_code(const char* s) {
@@ -41,21 +47,38 @@ int dtype_code(const char* s) {
   return -1;
 }
 
-// Fills the tensor part of `a` from q, k, v at params[0..2]; false if they are not rank-4 [B,N,S,D].
+// Fills the tensor part of `a` from q, k, v at params[0..2]; false if they are not rank-4 [B,N,S,D] tensors of one
+// 16-bit type that agree with one another: k and v of one shape [B, N_kv, S_k, D] with N_kv dividing N (the head
+// count of k and v is taken from THEIR shape, so a tensor with fewer heads is never read as if it had q's).
 bool fill_qkv(acct_fa_args& a, void** params, const int* ndims, int64_t** shapes, const char** dtypes) {
   if (ndims[0] != 4 || ndims[1] != 4 || ndims[2] != 4) return false;
   const int dt = dtype_code(dtypes[0]);
   if (dt != ACCT_F16 && dt != ACCT_BF16) return false;
+  if (dtype_code(dtypes[1]) != dt || dtype_code(dtypes[2]) != dt) return false;
+  const int64_t* q = shapes[0];
+  const int64_t* k = shapes[1];
+  const int64_t* v = shapes[2];
+  for (int i = 0; i < 4; ++i)
+    if (q[i] <= 0 || k[i] <= 0 || q[i] > 0x7fffffff || k[i] > 0x7fffffff || v[i] != k[i]) return false;
+  if (k[0] != q[0] || k[3] != q[3] || q[1] % k[1] != 0) return false;
   a.dtype = dt;
-  a.B = static_cast<int32_t>(shapes[0][0]);
-  a.N = static_cast<int32_t>(shapes[0][1]);
-  a.S_q = static_cast<int32_t>(shapes[0][2]);
-  a.D = static_cast<int32_t>(shapes[0][3]);
-  a.S_k = static_cast<int32_t>(shapes[1][2]);
+  a.B = static_cast<int32_t>(q[0]);
+  a.N = static_cast<int32_t>(q[1]);
+  a.S_q = static_cast<int32_t>(q[2]);
+  a.D = static_cast<int32_t>(q[3]);
+  a.S_k = static_cast<int32_t>(k[2]);
+  a.N_kv = static_cast<int32_t>(k[1]);
   a.q = params[0];
   a.k = params[1];
   a.v = params[2];
   return true;
+}
+
+// true iff tensor i has exactly the given rank-4 shape and type
+bool is_shape4(int i, const int* ndims, int64_t** shapes, const char** dtypes, int64_t d0, int64_t d1, int64_t d2, int64_t d3,
+               int dt) {
+  return ndims[i] == 4 && shapes[i][0] == d0 && shapes[i][1] == d1 && shapes[i][2] == d2 && shapes[i][3] == d3 &&
+         dtype_code(dtypes[i]) == dt;
 }
 
 // Classifies params[first .. last) as attn_mask / dropout_mask / alibi_mask; false on an input it cannot place.
@@ -69,6 +92,11 @@ bool fill_optionals(acct_fa_args& a, int first, int last, void** params, const i
       if (a.attn_mask != nullptr || dt < 0 || dt == ACCT_F32) return false;
       const bool tile = (r == 3 && s[0] == 1 && s[1] == 128 && s[2] == 128 && !(a.S_q == 128 && a.S_k == 128)) ||
                         (r == 2 && s[0] == 128 && s[1] == 128);
+      if (!tile) {   // a full mask is [1 or B, S_q, S_k] (or [S_q, S_k]): anything else would be read out of bounds
+        const int64_t mq = r == 3 ? s[1] : s[0], mk = r == 3 ? s[2] : s[1];
+        if (mq != a.S_q || mk != a.S_k) return false;
+        if (r == 3 && s[0] != 1 && s[0] != a.B) return false;
+      }
       a.attn_mask = params[i];
       a.mask_dtype = dt;
       a.mask_kind = tile ? ACCT_MASK_TILE128 : ACCT_MASK_FULL;   // attention.py:279-285
@@ -98,11 +126,11 @@ int summarise_mask(acct_fa_args& a, void* stream) {
   return rc;
 }
 
-void apply_attrs(acct_fa_args& a) {
+void apply_attrs(acct_fa_args& a, int slot) {
   FaAttrs at;
   {
     std::lock_guard<std::mutex> lock(g_attrs_mutex);
-    at = g_attrs;
+    at = (slot >= 0 && slot < kSlots) ? g_slot[slot] : g_attrs;
   }
   a.prev_block_num = at.prev_block_num;
   a.next_block_num = at.next_block_num;
@@ -125,9 +153,12 @@ ACCT_API void acct_ms_set_fa_attrs(int prev_block_num, int next_block_num, float
   g_attrs.causal = causal;
 }
 
+}  // extern "C"
+
+namespace {
+
 // inputs query, key, value, [attn_mask], [dropout_mask], [alibi_mask]; outputs output, rowsum
-ACCT_API int acct_ms_fa_fwd(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
-                            void* /*extra*/) {
+int ms_fa_fwd(int slot, int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream) {
   if (nparam < 5 || nparam > 8 || params == nullptr || ndims == nullptr || shapes == nullptr || dtypes == nullptr)
     return ACCT_ERR_SHAPE;
   acct_fa_args a;
@@ -135,9 +166,13 @@ ACCT_API int acct_ms_fa_fwd(int nparam, void** params, int* ndims, int64_t** sha
   if (!fill_qkv(a, params, ndims, shapes, dtypes)) return ACCT_ERR_SHAPE;
   if (!fill_optionals(a, 3, nparam - 2, params, ndims, shapes, dtypes)) return ACCT_ERR_SHAPE;
   if (dtype_code(dtypes[nparam - 1]) != ACCT_F32) return ACCT_ERR_DTYPE;   // rowsum is fp32 (impl.py:134-136)
+  // output is shaped and typed like q, rowsum is [B, N, S_q]
+  if (!is_shape4(nparam - 2, ndims, shapes, dtypes, a.B, a.N, a.S_q, a.D, a.dtype)) return ACCT_ERR_SHAPE;
+  if (ndims[nparam - 1] != 3 || shapes[nparam - 1][0] != a.B || shapes[nparam - 1][1] != a.N || shapes[nparam - 1][2] != a.S_q)
+    return ACCT_ERR_SHAPE;
   a.o = params[nparam - 2];
   a.lse = static_cast<float*>(params[nparam - 1]);
-  apply_attrs(a);
+  apply_attrs(a, slot);
   if (const int rc = summarise_mask(a, stream)) return rc;
   return acct_fa_fwd(&a, stream);
 }
@@ -145,8 +180,7 @@ ACCT_API int acct_ms_fa_fwd(int nparam, void** params, int* ndims, int64_t** sha
 // inputs query, key, value, output, do, rowsum, [attn_mask], [dropout_mask], [alibi_mask];
 // outputs dq, dk, dv (fp32, as the reference's grad primitive returns them) and a uint8 workspace tensor of
 // acct_fa_bwd_workspace_bytes() bytes, declared as a fourth output so that the framework allocates it.
-ACCT_API int acct_ms_fa_grad(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
-                             void* /*extra*/) {
+int ms_fa_grad(int slot, int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream) {
   if (nparam < 10 || nparam > 13 || params == nullptr || ndims == nullptr || shapes == nullptr || dtypes == nullptr)
     return ACCT_ERR_SHAPE;
   acct_fa_args a;
@@ -157,9 +191,15 @@ ACCT_API int acct_ms_fa_grad(int nparam, void** params, int* ndims, int64_t** sh
   for (int i = first_out; i < first_out + 3; ++i)
     if (dtype_code(dtypes[i]) != ACCT_F32) return ACCT_ERR_DTYPE;
   if (ndims[nparam - 1] != 1) return ACCT_ERR_WORKSPACE;
+  // output and do are shaped and typed like q; dq like q, dk and dv like k (fp32)
+  for (int i = 3; i <= 4; ++i)
+    if (!is_shape4(i, ndims, shapes, dtypes, a.B, a.N, a.S_q, a.D, a.dtype)) return ACCT_ERR_SHAPE;
+  if (!is_shape4(first_out, ndims, shapes, dtypes, a.B, a.N, a.S_q, a.D, ACCT_F32)) return ACCT_ERR_SHAPE;
+  for (int i = first_out + 1; i < first_out + 3; ++i)
+    if (!is_shape4(i, ndims, shapes, dtypes, a.B, a.N_kv, a.S_k, a.D, ACCT_F32)) return ACCT_ERR_SHAPE;
   a.o = params[3];
   a.lse = static_cast<float*>(params[5]);
-  apply_attrs(a);
+  apply_attrs(a, slot);
   if (const int rc = summarise_mask(a, stream)) return rc;
   a.flags |= ACCT_FLAG_GRAD_F32;
   acct_fa_bwd_io g;
@@ -172,6 +212,54 @@ ACCT_API int acct_ms_fa_grad(int nparam, void** params, int* ndims, int64_t** sh
   g.workspace_bytes = static_cast<size_t>(shapes[nparam - 1][0]);
   return acct_fa_bwd(&a, &g, stream);
 }
+
+}  // namespace
+
+extern "C" {
+
+ACCT_API int acct_ms_fa_fwd(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
+                            void* /*extra*/) {
+  return ms_fa_fwd(-1, nparam, params, ndims, shapes, dtypes, stream);
+}
+ACCT_API int acct_ms_fa_grad(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
+                             void* /*extra*/) {
+  return ms_fa_grad(-1, nparam, params, ndims, shapes, dtypes, stream);
+}
+
+// Stores a tuple of attributes and returns the number k of its slot (an identical tuple gets the slot it already
+// has); -1 when all slots hold other tuples.  Operators registered on acct_ms_fa_fwd_s<k> / acct_ms_fa_grad_s<k> use it.
+ACCT_API int acct_ms_fa_attrs_slot(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal) {
+  std::lock_guard<std::mutex> lock(g_attrs_mutex);
+  for (int i = 0; i < g_slots_used; ++i) {
+    const FaAttrs& t = g_slot[i];
+    if (t.prev_block_num == prev_block_num && t.next_block_num == next_block_num && t.keep_prob == keep_prob &&
+        t.scale == scale && t.causal == causal)
+      return i;
+  }
+  if (g_slots_used >= kSlots) return -1;
+  FaAttrs& t = g_slot[g_slots_used];
+  t.prev_block_num = prev_block_num;
+  t.next_block_num = next_block_num;
+  t.keep_prob = keep_prob;
+  t.scale = scale;
+  t.causal = causal;
+  return g_slots_used++;
+}
+
+#define ACCT_MS_SLOT(k)                                                                                               \
+  ACCT_API int acct_ms_fa_fwd_s##k(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes,      \
+                                   void* stream, void*) {                                                             \
+    return ms_fa_fwd(k, nparam, params, ndims, shapes, dtypes, stream);                                               \
+  }                                                                                                                   \
+  ACCT_API int acct_ms_fa_grad_s##k(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes,     \
+                                    void* stream, void*) {                                                            \
+    return ms_fa_grad(k, nparam, params, ndims, shapes, dtypes, stream);                                              \
+  }
+ACCT_MS_SLOT(0) ACCT_MS_SLOT(1) ACCT_MS_SLOT(2) ACCT_MS_SLOT(3) ACCT_MS_SLOT(4) ACCT_MS_SLOT(5) ACCT_MS_SLOT(6) ACCT_MS_SLOT(7)
+ACCT_MS_SLOT(8) ACCT_MS_SLOT(9) ACCT_MS_SLOT(10) ACCT_MS_SLOT(11) ACCT_MS_SLOT(12) ACCT_MS_SLOT(13) ACCT_MS_SLOT(14) ACCT_MS_SLOT(15)
+ACCT_MS_SLOT(16) ACCT_MS_SLOT(17) ACCT_MS_SLOT(18) ACCT_MS_SLOT(19) ACCT_MS_SLOT(20) ACCT_MS_SLOT(21) ACCT_MS_SLOT(22) ACCT_MS_SLOT(23)
+ACCT_MS_SLOT(24) ACCT_MS_SLOT(25) ACCT_MS_SLOT(26) ACCT_MS_SLOT(27) ACCT_MS_SLOT(28) ACCT_MS_SLOT(29) ACCT_MS_SLOT(30) ACCT_MS_SLOT(31)
+#undef ACCT_MS_SLOT
 
 // inputs q, k, v (rank 3 [B*N,S,D] or rank 4 [B,N,S,D]); output y shaped like q
 // (infer/flash_attention/tik/op_proto/flash_attention_tik.cpp:163-191)

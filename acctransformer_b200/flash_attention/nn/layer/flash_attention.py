@@ -14,6 +14,9 @@ Differences that do not change results beyond rounding:
   with torch's CUDA generator and ``keep_prob`` is passed as a scalar.
 * ``alibi=True`` is accepted (the reference raises, :107-108): ``alibi_mask`` ``[B,N,1,S_k]`` is
   added to every score row as the op contract declares (ops/flash_attention/attention.py:347-355).
+* Dropout follows ``torch.nn.Module`` practice and is applied in training mode only (``layer.train()``);
+  the reference cell applies its DropoutGenMask whenever ``dropout_rate > 0`` (:198-203) and leaves it to
+  the caller to build the cell with rate 0 for evaluation.
 * ``dp`` / ``mp`` / ``shard()`` are recorded and otherwise ignored: every (batch, head) slice is
   independent, so a data/model-parallel caller just passes its local slice.
 """
@@ -24,10 +27,22 @@ import math
 import torch
 
 from .... import ops as _ops
-from ...ops.flash_attention.flash_attention_impl import get_flash_attention
+from ...ops.flash_attention.flash_attention_impl import _is_tile_mask, get_flash_attention
 
 __all__ = ['FlashAttention']
 HEAD_DIM_MAX_LIMIT = 256
+
+
+def _draw_dropout_key(generator=None):
+    """(seed, offset) of one forward call's in-kernel dropout, drawn from ``generator`` (default: torch's CPU
+    generator).  Both values come from the generator's state and from nothing else, so whatever replays that state
+    replays the mask: ``torch.utils.checkpoint`` restores the RNG state before it recomputes a forward, and the
+    recomputed call then drops the same positions as the original one.  (A counter kept on the layer would not be
+    restored and the recomputed forward would disagree with the loss that was computed.)  With a CPU generator the
+    draw involves no device synchronisation."""
+    dev = generator.device if generator is not None else "cpu"
+    pair = torch.randint(0, 2 ** 31, (3,), generator=generator, device=dev).tolist()
+    return (pair[0] << 31) | pair[1], pair[2]
 
 
 class FlashAttention(torch.nn.Module):
@@ -72,8 +87,6 @@ class FlashAttention(torch.nn.Module):
         # A full attn_mask is inspected once per tensor (not per step): if it is exactly the causal mask, the kernels
         # generate the triangle themselves, read no mask and skip the tiles above the diagonal.
         self.detect_causal_mask = True
-        self._dropout_seed = None
-        self._dropout_step = 0
 
     def shard(self, in_strategy=None, out_strategy=None):
         """Records the split strategy (reference :132-177).  Nothing else to do: the op needs no
@@ -107,18 +120,16 @@ class FlashAttention(torch.nn.Module):
         drop_mask, seed, offset = None, None, 0
         if self.enable_dropout and self.training:
             if self.dropout_in_kernel:
-                if self._dropout_seed is None:      # one 64-bit seed per layer, drawn from the generator once
-                    gen = self.generator
-                    dev = gen.device if gen is not None else "cpu"
-                    self._dropout_seed = int(torch.randint(0, 2 ** 62, (1,), generator=gen, device=dev).item())
-                seed, offset = self._dropout_seed, self._dropout_step
-                self._dropout_step = (self._dropout_step + 1) % (2 ** 32)
+                seed, offset = _draw_dropout_key(self.generator)
             else:
                 drop_mask = (torch.rand((bsz, head_num, seq_len, k.shape[2]), device=q.device,
                                         generator=self.generator) < self.keep_prob).to(torch.uint8)
         implicit = False
-        if self.detect_causal_mask and attn_mask is not None and attn_mask.is_cuda:
-            if attn_mask.numel() != 128 * 128:
+        # (the check reads the mask on the GPU and synchronises once per mask tensor: it is skipped while a CUDA graph
+        # is being captured, where the mask then simply stays a tensor)
+        if (self.detect_causal_mask and attn_mask is not None and attn_mask.is_cuda
+                and not torch.cuda.is_current_stream_capturing()):
+            if not _is_tile_mask(attn_mask):
                 implicit = _ops.mask_is_causal(attn_mask)
             elif self.flash_attention.next_block_num == 0 or max(seq_len, k.shape[2]) <= 128:
                 # the 128x128 tile form acts on the diagonal tiles only; with no tile above the diagonal in the band

@@ -19,6 +19,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops as _ops
+from ..flash_attention.nn.layer.flash_attention import _draw_dropout_key
 from ..flash_attention.ops.flash_attention.flash_attention_impl import _FlashAttentionFunction
 
 __all__ = ["TriangleAttention"]
@@ -46,8 +47,6 @@ class TriangleAttention(torch.nn.Module):
         self.detect_causal_mask = True
         self.generator = None
         self.dropout_in_kernel = True   # dropout decided inside the kernels from (seed, step); False: a mask tensor
-        self._dropout_seed = None
-        self._dropout_step = 0
 
     def tiles_skipped_fraction(self, seq_length):
         """Fraction of the 128x128 score tiles the kernel never touches for this sequence length."""
@@ -66,12 +65,7 @@ class TriangleAttention(torch.nn.Module):
         drop_mask, seed, offset = None, None, 0
         if self.enable_dropout and self.training:
             if self.dropout_in_kernel:
-                if self._dropout_seed is None:
-                    gen = self.generator
-                    dev = gen.device if gen is not None else "cpu"
-                    self._dropout_seed = int(torch.randint(0, 2 ** 62, (1,), generator=gen, device=dev).item())
-                seed, offset = self._dropout_seed, self._dropout_step
-                self._dropout_step = (self._dropout_step + 1) % (2 ** 32)
+                seed, offset = _draw_dropout_key(self.generator)
             else:
                 drop_mask = (torch.rand((bsz, head_num, seq_length, key.shape[2]), device=query.device,
                                         generator=self.generator) < self.keep_prob).to(torch.uint8)
@@ -79,7 +73,8 @@ class TriangleAttention(torch.nn.Module):
         # inside that range the mask tensor decides (or the in-kernel triangle when assume_causal).
         # (under the in-kernel triangle the group bound excludes nothing more, so it is not passed)
         causal = self.assume_causal or (self.detect_causal_mask and attention_mask is not None
-                                        and attention_mask.is_cuda and _ops.mask_is_causal(attention_mask))
+                                        and attention_mask.is_cuda and not torch.cuda.is_current_stream_capturing()
+                                        and _ops.mask_is_causal(attention_mask))
         cfg = dict(prev_block_num=65536, next_block_num=65536, scale=1.0, causal=causal,
                    keep_prob=self.keep_prob, tri_block=0 if causal else self.block_size,
                    dropout_seed=seed, dropout_offset=offset)

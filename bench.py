@@ -79,17 +79,21 @@ def cpu_step(c, q, k, v, do):
     return time.perf_counter() - t0
 
 
-def cpu_baseline(name, steps=1, warmup=0):
+def cpu_baseline(name, steps=1, warmup=0, min_seconds=0.0):
+    """Times the oracle on (batch, head) units at full sequence length: ``steps`` units, and then further units
+    until ``min_seconds`` of CPU work have been spent (at most 16 units in all)."""
     from acctransformer_b200.workloads import fwd_bwd_flops
     c, q, k, v, do = cpu_sample(name)
     for _ in range(warmup):
         cpu_step(c, q, k, v, do)
     times = [cpu_step(c, q, k, v, do) for _ in range(steps)]
+    while sum(times) < min_seconds and len(times) < 16:
+        times.append(cpu_step(c, q, k, v, do))
     sec = sum(times) / len(times)
     flops = fwd_bwd_flops(c, B=1, N=1)
     return {"value": flops / sec / 1e12, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-            "sample": f"1 of {c['B'] * c['N']} (batch, head) units at full S={c['S']}, fp32 NumPy "
-                      f"standard attention fwd+grad, {sec:.2f} s per unit, mean of {len(times)}"}, sec
+            "sample": f"{len(times)} of {c['B'] * c['N']} (batch, head) units at full S={c['S']}, one after the other, "
+                      f"fp32 NumPy standard attention fwd+grad, {sec:.2f} s per unit ({sum(times):.1f} s of CPU work)"}, sec
 
 
 def run_reference(args):
@@ -188,6 +192,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     from acctransformer_b200 import _lib, ops
+    from acctransformer_b200.sharding import unit_slice
     from acctransformer_b200.workloads import CONFIGS, fwd_bwd_flops, fwd_flops, make_inputs
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -202,7 +207,12 @@ def run_ours(args):
     _lib.load()
 
     cfg = CONFIGS[args.workload]
-    inp = make_inputs(args.workload, dev, seed_offset=rank)
+    # Weak scaling: the job is a batch `world` times as large; its (batch, head) units are dealt out in contiguous
+    # runs (sharding.unit_slice) and every rank draws its own run, seeded by the run's first unit.
+    units_per_rank = cfg["B"] * cfg["N"]
+    u0, u1 = unit_slice(world * units_per_rank, rank, world)
+    assert u1 - u0 == units_per_rank
+    inp = make_inputs(args.workload, dev, seed_offset=u0 // units_per_rank)
     q, k, v, do = inp["q"], inp["k"], inp["v"], inp["do"]
     scale = inp["scale"]
 
@@ -319,22 +329,70 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms_e2e = float(t.item())
         nbytes = sum(t.numel() * t.element_size() for t in host_in)
+
+        # What the box's host path allows: the same pinned uploads and read-backs per step on the same two copy
+        # streams, all ranks at once, with no kernel in between.
+        outs0 = keep_alive[-1]
+
+        def copy_only_step():
+            i = counter[0] & 1
+            counter[0] += 1
+            with torch.cuda.stream(h2d_stream):
+                for d, h in zip(dev_in[i], host_in):
+                    d.copy_(h, non_blocking=True)
+            with torch.cuda.stream(d2h_stream):
+                for h, d in zip(host_out, outs0):
+                    h.copy_(d, non_blocking=True)
+
+        def join_both():
+            torch.cuda.current_stream().wait_stream(h2d_stream)
+            return d2h_stream
+
+        copy_only_step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        h2d_stream.wait_event(e0)
+        d2h_stream.wait_event(e0)
+        for _ in range(e2e_iters):
+            copy_only_step()
+        torch.cuda.current_stream().wait_stream(h2d_stream)
+        torch.cuda.current_stream().wait_stream(d2h_stream)
+        e1.record()
+        barrier()
+        ms_copy = e0.elapsed_time(e1) / e2e_iters
+        if world > 1:
+            t = torch.tensor([ms_copy], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_copy = float(t.item())
         e2e = {"value": world * flops_step / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": nbytes,
-               "d2h_bytes_per_step": nbytes, "ms_per_step": ms_e2e, "steps": e2e_iters}
+               "d2h_bytes_per_step": nbytes, "ms_per_step": ms_e2e, "steps": e2e_iters,
+               # the copies alone, same bytes, same streams, every rank at once: the floor the host path sets
+               "copy_ceiling_ms": ms_copy, "frac_of_copy_ceiling": ms_copy / ms_e2e,
+               "copy_gbs_per_direction_per_gpu": nbytes / (ms_copy * 1e-3) / 1e9}
         torch.cuda.synchronize()
         del host_in, host_out, dev_in, keep_alive
 
     peaks = measured_peaks()
     bwd_tflops = 2.5 * fwd_flops(cfg) / (ms_bwd_kernel * 1e-3) / 1e12
     fwd_tflops = fwd_flops(cfg) / (ms_fwd * 1e-3) / 1e12
+    mhz = (clocks or {}).get("sm_mhz")
+    # The kernel is timed alone by an event pair, so the burst figure is the denominator; the sustained one (a
+    # seconds-long GEMM loop under the power cap) is given beside it.  kcycles = ms x median SM MHz sampled during
+    # the timed legs: runs that the power cap held at different clocks compare on that.
     roofline = {"kernel": "fa_bwd_kernel (CUDA events recorded by the library directly around its launch)",
-                "bound": "tensor", "achieved": bwd_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": bwd_tflops / peaks["tflops"], "peak_source": f"{peaks['which']} bf16_tflops_sustained",
+                "bound": "tensor", "achieved": bwd_tflops, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
+                "frac": bwd_tflops / peaks["tflops_burst"], "peak_source": f"{peaks['which']} bf16_tflops (burst)",
+                "frac_of_sustained": bwd_tflops / peaks["tflops"], "peak_sustained": peaks["tflops"],
+                "kcycles": ms_bwd_kernel * mhz if mhz else None,
                 "ms_whole_backward_call": ms_bwd,   # + row-sum kernel, zero-fill, dQ conversion
                 # DRAM read + write bytes of one backward-kernel launch: ncu capture on workload P (203.8 + 89.3 MB,
                 # profiles/fa_bwd_kernel_P_ncu_full.md) scaled by the units x sequence ratio of the workload
                 "traffic": 293.1e6 * (cfg["B"] * cfg["N"] * cfg["S"]) / (2 * 16 * 4096), "ms": ms_bwd_kernel,
-                "fwd": {"kernel": "fa_fwd_kernel", "achieved": fwd_tflops, "frac": fwd_tflops / peaks["tflops"], "ms": ms_fwd},
+                "fwd": {"kernel": "fa_fwd_kernel", "achieved": fwd_tflops, "frac": fwd_tflops / peaks["tflops_burst"],
+                        "frac_of_sustained": fwd_tflops / peaks["tflops"], "ms": ms_fwd,
+                        "kcycles": ms_fwd * mhz if mhz else None},
                 "step_frac_of_sustained": (flops_step / (ms_step * 1e-3) / 1e12) / peaks["tflops"],
                 "step_frac_of_burst": (flops_step / (ms_step * 1e-3) / 1e12) / peaks["tflops_burst"],
                 "step_frac_of_datasheet_2250": (flops_step / (ms_step * 1e-3) / 1e12) / 2250.0}
@@ -343,8 +401,10 @@ def run_ours(args):
     torch.cuda.empty_cache()
 
     decode = None
-    if not args.no_decode and rank == 0:
-        decode = bench_decode(torch, ops, dev, peaks)
+    if not args.no_decode:
+        # configuration 5b is ONE job of 1 024 (sequence, head) units: with several GPUs the heads are dealt out
+        # (every GPU keeps all 32 sequences, so the ragged lengths load them equally) and no data crosses
+        decode = bench_decode(torch, ops, dev, peaks, rank=rank, world=world, dist=dist if world > 1 else None)
     other = None
     if not args.no_aux and rank == 0 and world == 1 and args.workload == "H":
         other = bench_other_configs(torch, ops, dev, peaks)
@@ -356,12 +416,23 @@ def run_ours(args):
             "other_configs": other}
     if rank == 0:
         if world == 1 and not args.no_cpu:
-            line["cpu_baseline"], _ = cpu_baseline(args.workload)
-        print(json.dumps(line), flush=True)
+            line["cpu_baseline"], _ = cpu_baseline(args.workload, min_seconds=12.0)
+        print(json.dumps(_rounded(line)), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+def _rounded(x):
+    """Floats to five significant digits: keeps the one JSON line short enough to be read whole."""
+    if isinstance(x, float):
+        return float(f"{x:.5g}")
+    if isinstance(x, dict):
+        return {k: _rounded(v) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return [_rounded(v) for v in x]
+    return x
 
 
 def bench_other_configs(torch, ops, dev, peaks):
@@ -461,17 +532,37 @@ def bench_other_configs(torch, ops, dev, peaks):
             del o2, lse2
         del inp, q, k, v, o, lse
         torch.cuda.empty_cache()
-    return out
+    # compact form for the JSON line: algorithmic TFLOP/s (forward + backward, or forward alone for the prefill),
+    # fraction of the measured sustained GEMM rate, and the two times
+    short = {"legend": "tf = fwd+bwd TFLOP/s (cfg5a: fwd only), frac = of sustained bf16 GEMM, f_ms / b_ms = forward / "
+                       "backward call; cfg3 = uint8 dropout tensor, cfg3_in_kernel = Philox in the kernels; cfg4 = mask "
+                       "tensor read in full, cfg4_mask_tiles = with its per-tile summary, cfg4_mask_elided = recognised "
+                       "as causal"}
+    for name, rec in out.items():
+        name = name.replace("cfg3_in_kernel_dropout", "cfg3_in_kernel")
+        tf = rec.get("fwd_bwd_tflops", rec["fwd_tflops"])
+        short[name] = {"tf": round(tf, 1), "frac": round(tf / peaks["tflops"], 3), "f_ms": round(rec["fwd_ms"], 3)}
+        if "bwd_ms" in rec:
+            short[name]["b_ms"] = round(rec["bwd_ms"], 3)
+        for extra in ("detect_once_ms", "classify_once_ms", "mixed_tile_fraction"):
+            if extra in rec:
+                short[name][extra] = round(rec[extra], 3)
+    return short
 
 
-def bench_decode(torch, ops, dev, peaks, small=False):
+def bench_decode(torch, ops, dev, peaks, small=False, rank=0, world=1, dist=None):
     """Decode step of configuration 5b (B=32 N=32 KV<=16384 D=128 fp16, per-sequence lengths): achieved HBM GB/s
     counting only the valid K and V rows.  Three cache sets (25.8 GB) are rotated so that no step finds its
-    cache in L2.  ``small``: B=8 (3 x 2.1 GB, still far above L2), few iterations, for a profiler capture."""
+    cache in L2.  ``small``: B=8 (3 x 2.1 GB, still far above L2), few iterations, for a profiler capture.
+    With ``world`` > 1 the job's 32 heads are dealt out over the ranks (sharding.unit_slice): every rank streams its
+    heads of all sequences, the time is the max over ranks and the figure is the job's bytes over that time."""
+    from acctransformer_b200.sharding import unit_slice
     from acctransformer_b200.workloads import CONFIGS
     c = CONFIGS["cfg5b"]
-    B, N, S, D = (8 if small else c["B"]), c["N"], c["S"], c["D"]
-    g = torch.Generator(device=dev).manual_seed(6)
+    B, N_job, S, D = (8 if small else c["B"]), c["N"], c["S"], c["D"]
+    h0, h1 = unit_slice(N_job, rank, world)
+    N = h1 - h0
+    g = torch.Generator(device=dev).manual_seed(6 + 100 * h0)
     sets = []
     for _ in range(3):
         kc = torch.empty(B, N, S, D, device=dev, dtype=torch.float16)
@@ -488,18 +579,27 @@ def bench_decode(torch, ops, dev, peaks, small=False):
         ops.infer_decode(qd, sets[i % 3][0], sets[i % 3][1], lens, workspace=ws, out=y)
     iters = 6 if small else 30
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
     torch.cuda.synchronize()
     e0.record()
     for i in range(iters):
         ops.infer_decode(qd, sets[i % 3][0], sets[i % 3][1], lens, workspace=ws, out=y)
     e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / iters
-    nbytes = float(lens.sum().item()) * N * D * 2 * 2
+    ms_rank = e0.elapsed_time(e1) / iters
+    ms = ms_rank
+    if dist is not None:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    nbytes_rank = float(lens.sum().item()) * N * D * 2 * 2
+    nbytes = float(lens.sum().item()) * N_job * D * 2 * 2
     gbps = nbytes / (ms * 1e-3) / 1e9
-    return {"workload": f"cfg5b decode B={B} N=32 q_len=1 KV<=16384 D=128 fp16", "ms": ms, "bytes": nbytes,
-            "achieved_gbs": gbps, "peak_gbs": peaks["hbm_gbs"], "frac": gbps / peaks["hbm_gbs"],
-            "peak_source": f"{peaks['which']} hbm_gbs"}
+    return {"workload": f"cfg5b decode B={B} N={N_job} q_len=1 KV<=16384 D=128 fp16, {N} heads per GPU on {world} GPU(s)",
+            "ms": ms, "bytes": nbytes, "achieved_gbs": gbps, "peak_gbs": world * peaks["hbm_gbs"],
+            "frac": gbps / (world * peaks["hbm_gbs"]), "per_gpu_gbs_rank0": nbytes_rank / (ms_rank * 1e-3) / 1e9,
+            "peak_source": f"{peaks['which']} hbm_gbs x {world}"}
 
 
 def main():

@@ -299,10 +299,32 @@ ACCT_API int acct_infer_decode_static(const acct_decode_args* a, void* stream);
  *                    declared as a fourth output so that the framework allocates it
  *   acct_ms_infer_fa FlashAttentionTik(q, k, v) -> y, flash_attention_tik.h:22-27 (rank 3 or 4)
  * Optional inputs are recognised by rank and shape (rank 3 / 128x128: attn_mask; [B,N,1,S_k]: alibi_mask;
- * [B,N,S_q,S_k]: dropout_mask).  The attributes the reference bakes into each primitive (band limits; plus the keep
- * probability for uint8 dropout masks, a scale and an implicit causal mask, which are this library's additions)
- * are process-wide and set with acct_ms_set_fa_attrs; the defaults are "no band, keep_prob 1, scale 1, not causal". */
+ * [B,N,S_q,S_k]: dropout_mask; with S_q = 1 a lone [B,N,1,S_k] tensor is taken for the dropout mask).  Shapes are
+ * checked against one another (k and v of one shape whose head count divides q's, masks and outputs of the sizes
+ * that follow from q and k); a mismatch returns ACCT_ERR_SHAPE before anything is read.
+ * The attributes the reference bakes into each primitive (flash_attention_impl.py:146-152: band limits; plus the keep
+ * probability for uint8 dropout masks, a scale and an implicit causal mask, which are this library's additions) do
+ * not travel with such a call.  A primitive is therefore bound to a numbered attribute slot through the NAME of the
+ * entry point it is registered on: acct_ms_fa_attrs_slot() stores a tuple and returns its slot k in [0, 32) (an
+ * identical tuple gets the slot it already has; -1 when all slots hold other tuples), and the operator pair is
+ * registered on acct_ms_fa_fwd_s<k> / acct_ms_fa_grad_s<k>.  Layers of one graph with different band widths, dropout
+ * rates or scales thus keep their own values.  The unnumbered entry points use one process-wide tuple, set with
+ * acct_ms_set_fa_attrs; its defaults are "no band, keep_prob 1, scale 1, not causal". */
 ACCT_API void acct_ms_set_fa_attrs(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal);
+ACCT_API int acct_ms_fa_attrs_slot(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal);
+#define ACCT_MS_SLOT_ENTRY(k)                                                                                       \
+  ACCT_API int acct_ms_fa_fwd_s##k(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes,    \
+                                   void* stream, void* extra);                                                      \
+  ACCT_API int acct_ms_fa_grad_s##k(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes,   \
+                                    void* stream, void* extra);
+ACCT_MS_SLOT_ENTRY(0) ACCT_MS_SLOT_ENTRY(1) ACCT_MS_SLOT_ENTRY(2) ACCT_MS_SLOT_ENTRY(3) ACCT_MS_SLOT_ENTRY(4)
+ACCT_MS_SLOT_ENTRY(5) ACCT_MS_SLOT_ENTRY(6) ACCT_MS_SLOT_ENTRY(7) ACCT_MS_SLOT_ENTRY(8) ACCT_MS_SLOT_ENTRY(9)
+ACCT_MS_SLOT_ENTRY(10) ACCT_MS_SLOT_ENTRY(11) ACCT_MS_SLOT_ENTRY(12) ACCT_MS_SLOT_ENTRY(13) ACCT_MS_SLOT_ENTRY(14)
+ACCT_MS_SLOT_ENTRY(15) ACCT_MS_SLOT_ENTRY(16) ACCT_MS_SLOT_ENTRY(17) ACCT_MS_SLOT_ENTRY(18) ACCT_MS_SLOT_ENTRY(19)
+ACCT_MS_SLOT_ENTRY(20) ACCT_MS_SLOT_ENTRY(21) ACCT_MS_SLOT_ENTRY(22) ACCT_MS_SLOT_ENTRY(23) ACCT_MS_SLOT_ENTRY(24)
+ACCT_MS_SLOT_ENTRY(25) ACCT_MS_SLOT_ENTRY(26) ACCT_MS_SLOT_ENTRY(27) ACCT_MS_SLOT_ENTRY(28) ACCT_MS_SLOT_ENTRY(29)
+ACCT_MS_SLOT_ENTRY(30) ACCT_MS_SLOT_ENTRY(31)
+#undef ACCT_MS_SLOT_ENTRY
 ACCT_API int acct_ms_fa_fwd(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,
                             void* extra);
 ACCT_API int acct_ms_fa_grad(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes, void* stream,

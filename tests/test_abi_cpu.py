@@ -25,6 +25,11 @@ def test_library_exports_every_declared_symbol(lib):
     with open(HEADER) as f:
         text = f.read()
     declared = re.findall(r"ACCT_API\s+[\w\s\*]+?\b(acct_\w+)\s*\(", text)
+    # the numbered MindSpore entry points are declared through a macro, one pair per slot
+    slots = [int(k) for k in re.findall(r"ACCT_MS_SLOT_ENTRY\((\d+)\)", text)]
+    assert slots == list(range(32))
+    declared = [d for d in declared if "##" not in d and not d.endswith("_s")]
+    declared += [f"acct_ms_fa_{kind}_s{k}" for k in slots for kind in ("fwd", "grad")]
     assert len(declared) >= 9
     for name in declared:
         assert hasattr(lib, name), name

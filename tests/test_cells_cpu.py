@@ -93,3 +93,42 @@ def test_triangle_skipped_tiles_match_the_row_group_bounds():
             q_end = max(min(S, (r // block + 1) * block) for r in rows)
             computed += sum(1 for j in range(nt) if j * 128 < q_end)
         assert abs(ta.tiles_skipped_fraction(S) - (1.0 - computed / float(nt * nt))) < 1e-12
+
+
+def test_reference_import_paths_resolve_to_the_same_objects():
+    """A user of the reference imports through ``acctransformer.*`` (train/setup.py:22-31 installs that package);
+    the same statements work here and give this library's classes."""
+    from acctransformer.flash_attention.nn.layer.flash_attention import FlashAttention
+    from acctransformer.flash_attention.ops.flash_attention.flash_attention_impl import (get_flash_attention,
+                                                                                         get_flash_attention_grad)
+    from acctransformer.triangle_attention.triangle_attention import TriangleAttention
+    import acctransformer_b200 as mine
+    assert FlashAttention is mine.FlashAttention and TriangleAttention is mine.TriangleAttention
+    assert get_flash_attention is mine.get_flash_attention and get_flash_attention_grad is mine.get_flash_attention_grad
+    layer = FlashAttention(head_dim=128, dropout_rate=0.1, prev_block_num=4, next_block_num=0, dp=2, mp=4,
+                           have_attention_mask_batch=False)
+    assert layer.flash_attention.prev_block_num == 4 and layer.flash_attention.next_block_num == 0
+    with pytest.raises(ValueError):
+        FlashAttention(head_dim=512)
+    with pytest.raises(ValueError):
+        TriangleAttention(block_size=0)
+
+
+def test_dropout_key_is_a_function_of_the_generator_state_alone():
+    """Replaying the RNG state replays (seed, offset): a forward recomputed under torch.utils.checkpoint, which
+    restores the RNG state first, gets the mask of the original forward."""
+    import torch
+    from acctransformer_b200.flash_attention.nn.layer.flash_attention import _draw_dropout_key
+    g = torch.Generator().manual_seed(7)
+    state = g.get_state()
+    first = _draw_dropout_key(g)
+    second = _draw_dropout_key(g)
+    assert first != second
+    g.set_state(state)
+    assert _draw_dropout_key(g) == first
+    # the default generator, which checkpointing saves and restores
+    state = torch.get_rng_state()
+    a = _draw_dropout_key()
+    torch.set_rng_state(state)
+    assert _draw_dropout_key() == a
+    assert 0 <= a[0] < 2 ** 62 and 0 <= a[1] < 2 ** 32

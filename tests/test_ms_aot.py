@@ -153,3 +153,104 @@ def test_forward_and_grad_through_the_aot_convention():
     torch.cuda.synchronize()
     y_ref = ref.infer_fwd(_np(q3), _np(k3), _np(v3))
     assert np.max(np.abs(_np(y3) - y_ref)) <= 2e-3
+
+
+# ------------------------------------------------------------------------------------------ attribute slots, shapes
+def test_attribute_slots_are_per_tuple_and_reused(lib):
+    lib.acct_ms_fa_attrs_slot.argtypes = [C.c_int, C.c_int, C.c_float, C.c_float, C.c_int]
+    lib.acct_ms_fa_attrs_slot.restype = C.c_int
+    a = lib.acct_ms_fa_attrs_slot(4, 4, 0.9, 0.125, 0)
+    b = lib.acct_ms_fa_attrs_slot(65536, 0, 1.0, 0.125, 1)
+    assert a >= 0 and b >= 0 and a != b
+    assert lib.acct_ms_fa_attrs_slot(4, 4, 0.9, 0.125, 0) == a        # the same tuple keeps its slot
+    for k in (a, b):
+        assert hasattr(lib, f"acct_ms_fa_fwd_s{k}") and hasattr(lib, f"acct_ms_fa_grad_s{k}")
+
+
+def test_mismatched_key_value_and_mask_shapes_are_rejected_before_any_read(lib):
+    q = ((2, 4, 256, 64), b"float16")
+    o, l = ((2, 4, 256, 64), b"float16"), ((2, 4, 256), b"float32")
+    ok_k = ((2, 4, 384, 64), b"float16")
+    # (the device pointers are fake: a call that got past the checks would reach the CUDA layer, never these tensors)
+    bad = [
+        [q, ((2, 4, 384, 32), b"float16"), ((2, 4, 384, 32), b"float16"), o, l],        # head_dim differs
+        [q, ok_k, ((2, 4, 256, 64), b"float16"), o, l],                                   # v shaped unlike k
+        [q, ((2, 3, 384, 64), b"float16"), ((2, 3, 384, 64), b"float16"), o, l],          # 3 heads do not divide 4
+        [q, ((1, 4, 384, 64), b"float16"), ((1, 4, 384, 64), b"float16"), o, l],          # batch differs
+        [q, ok_k, ((2, 4, 384, 64), b"bfloat16"), o, l],                                  # v of another type
+        [q, ok_k, ok_k, ((2, 100, 384), b"float16"), o, l],                               # mask rows != S_q
+        [q, ok_k, ok_k, ((3, 256, 384), b"float16"), o, l],                               # mask batch neither 1 nor B
+        [q, ok_k, ok_k, ((2, 4, 256, 32), b"float16"), l],                                # output shaped unlike q
+        [q, ok_k, ok_k, o, ((2, 4, 128), b"float32")],                                    # rowsum shaped unlike [B,N,S_q]
+    ]
+    for tensors in bad:
+        assert aot_call(lib.acct_ms_fa_fwd, tensors) == ERR_SHAPE, tensors
+    # grouped key/value heads are derived from k's own shape: dk and dv must then have k's shape
+    kv2 = ((2, 2, 384, 64), b"float16")
+    g32 = lambda shp: (shp, b"float32")
+    grad = [q, kv2, kv2, o, o, l, g32((2, 4, 256, 64)), g32((2, 4, 384, 64)), g32((2, 4, 384, 64)), ((1024,), b"uint8")]
+    assert aot_call(lib.acct_ms_fa_grad, grad) == ERR_SHAPE
+
+
+def test_mindspore_adapter_shape_inference_and_strategy_tables():
+    """The parts of the MindSpore adapter that are plain Python: output shapes and dtypes of the two primitives
+    (flash_attention_impl.py:99-105,132-140) and the attributes the cell's shard() sets
+    (nn/layer/flash_attention.py:132-177)."""
+    from acctransformer_b200 import mindspore_adapter as ad
+    assert ad.forward_out_shape((2, 8, 512, 128), (2, 8, 512, 128), (2, 8, 512, 128)) == ((2, 8, 512, 128), (2, 8, 512))
+    assert ad.forward_out_dtype("float16", "float16", "float16") == ("float16", "float32")
+    dq, dk, dv, ws = ad.grad_out_shape((2, 8, 512, 128), (2, 4, 640, 128), (2, 4, 640, 128), None, None, None)
+    assert (dq, dk, dv) == ((2, 8, 512, 128), (2, 4, 640, 128), (2, 4, 640, 128))
+    assert ws == (ad.bwd_workspace_bytes((2, 8, 512, 128)),) and ws[0] >= 2 * 8 * 512 * 4
+    assert ad.grad_out_dtype(*["float16"] * 6) == ("float32", "float32", "float32", "uint8")
+    s = ad.attrs_slot(4, 4, 0.9, 0.125, False)
+    assert ad.attrs_slot(4, 4, 0.9, 0.125, False) == s
+    assert ad.aot_func("fwd", s).endswith(f"libacct_b200.so:acct_ms_fa_fwd_s{s}")
+    assert ad.aot_func("grad", s).endswith(f":acct_ms_fa_grad_s{s}")
+    at = ad.shard_attrs(((2, 4, 1, 1), (2, 4, 1, 1), (2, 4, 1, 1)), have_attention_mask_batch=True, enable_dropout=True)
+    assert at["dev_matrix_shape"] == [2, 4, 1, 1]
+    assert at["inputs_tensor_map"] == [[3, 2, 1, 0]] * 3 + [[3, 1, 0], [3, 2, 1, 0]]
+    assert at["outputs_tensor_map"] == [[3, 2, 1, 0], [3, 2, 1]] and at["empty_mirror_ops"] == 1
+    at = ad.shard_attrs(None, have_attention_mask_batch=False, alibi=True, enable_dropout=True)
+    assert at["inputs_tensor_map"][3] == [-1, 1, 0] and at["empty_mirror_ops"] == 0 and at["dev_matrix_shape"] == [1, 1, 1, 1]
+    try:
+        import mindspore  # noqa: F401
+    except ImportError:
+        with pytest.raises(ImportError):
+            ad.get_flash_attention()
+
+
+@pytest.mark.gpu
+def test_two_primitives_with_different_attributes_in_one_process():
+    """Two layers of one graph with different band widths and scales: each is bound to its own attribute slot and
+    keeps its own values, as primitives of the reference do (flash_attention_impl.py:146-152)."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from acctransformer_b200 import mindspore_adapter as ad
+    lb = _lib.load()
+    sig = [C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.POINTER(C.POINTER(C.c_int64)), C.POINTER(C.c_char_p),
+           C.c_void_p, C.c_void_p]
+    dev = torch.device("cuda", 0)
+    B, N, S, D = 1, 2, 512, 64
+    rs = np.random.RandomState(12)
+    q, k, v = (torch.tensor(rs.randn(B, N, S, D).astype(np.float32)).half().to(dev) for _ in range(3))
+    layers = [dict(prev_block_num=1, next_block_num=0, scale=0.125, causal=True),
+              dict(prev_block_num=65536, next_block_num=65536, scale=0.05, causal=False)]
+    slots = [ad.attrs_slot(keep_prob=1.0, **kw) for kw in layers]
+    assert slots[0] != slots[1]
+    outs = []
+    stream = torch.cuda.current_stream().cuda_stream
+    for slot in slots + slots[:1]:          # interleaved: the first layer again after the second
+        fn = getattr(lb, f"acct_ms_fa_fwd_s{slot}")
+        fn.argtypes, fn.restype = sig, C.c_int
+        o = torch.empty_like(q)
+        lse = torch.empty(B, N, S, dtype=torch.float32, device=dev)
+        assert aot_call(fn, [q, k, v, o, lse], stream) == 0
+        outs.append(o)
+    torch.cuda.synchronize()
+    _lib.device_status()
+    for o, kw in zip(outs, layers + layers[:1]):
+        o_ref, _ = ref.sa_fwd(_np(q), _np(k), _np(v), scale=kw["scale"], causal=kw["causal"],
+                              prev_block_num=kw["prev_block_num"], next_block_num=kw["next_block_num"])
+        assert np.max(np.abs(_np(o) - o_ref)) <= 2e-3
+    assert torch.equal(outs[0], outs[2]) and not torch.equal(outs[0], outs[1])
