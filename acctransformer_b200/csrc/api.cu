@@ -148,7 +148,7 @@ namespace {
 
 constexpr int kMaxHeadDimCell = 256;   // the reference cell's limit (nn/layer/flash_attention.py:26,105-106)
 constexpr int kMaxHeadDimFwd = 256;    // forward / prefill kernels: tiles padded to 64, 128 or 256 columns
-constexpr int kMaxHeadDimBwd = 128;    // backward kernel: dK and dV accumulators fill tensor memory at 128
+constexpr int kMaxHeadDimBwd = 256;    // backward: one kernel up to 128, the split-width kernel above that
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -265,13 +265,14 @@ ScoreMods make_mods(const acct_fa_args* a) {
   return m;
 }
 
-int make_qkv_maps(const acct_fa_args* a, const Strides& st, CUtensorMap* mq, CUtensorMap* mk, CUtensorMap* mv) {
+int make_qkv_maps(const acct_fa_args* a, const Strides& st, CUtensorMap* mq, CUtensorMap* mk, CUtensorMap* mv,
+                  int q_box_rows = kTile) {
   TensorDesc4 t;
   t.dtype = a->dtype;
   int rc;
   t.ptr = a->q; t.dims[0] = a->D; t.dims[1] = a->S_q; t.dims[2] = a->N; t.dims[3] = a->B;
   t.strides[0] = st.q[2]; t.strides[1] = st.q[1]; t.strides[2] = st.q[0];
-  if ((rc = make_tmap_4d(mq, t, kTile))) return rc;
+  if ((rc = make_tmap_4d(mq, t, q_box_rows))) return rc;
   t.ptr = a->k; t.dims[1] = a->S_k; t.dims[2] = kv_heads(a);
   t.strides[0] = st.k[2]; t.strides[1] = st.k[1]; t.strides[2] = st.k[0];
   if ((rc = make_tmap_4d(mk, t, kTile))) return rc;
@@ -410,7 +411,8 @@ int acct_fa_fwd(const acct_fa_args* a, void* stream) {
 size_t acct_fa_bwd_workspace_bytes(const acct_fa_args* a) {
   if (a == nullptr || a->B <= 0 || a->N <= 0 || a->S_q <= 0 || a->D <= 0) return 0;
   const size_t rows = static_cast<size_t>(a->B) * a->N * a->S_q;
-  const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile);
+  // (two counters per Q tile above head_dim 128, where two CTAs share a K/V tile by halves of head_dim)
+  const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile) * (a->D > 128 ? 2 : 1);
   // delta [rows] fp32 | turn counters of the ordered dQ reduction [B*N*ceil(S_q/128)] u32 | dQ accumulator
   // [rows, D] fp32; the first two padded to 256 bytes.  With fp32 gradients dq itself is the accumulator.
   const size_t acc = (a->flags & ACCT_FLAG_GRAD_F32) ? 0 : rows * static_cast<size_t>(a->D) * 4;
@@ -435,7 +437,8 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   const bool bf16 = a->dtype == ACCT_BF16;
   const size_t rows = static_cast<size_t>(a->B) * a->N * a->S_q;
   float* delta = static_cast<float*>(g->workspace);
-  const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile);
+  const bool wide = a->D > 128;      // the split-width kernel: 64-row Q / dO boxes, 64-row dQ box, 2 counters per tile
+  const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile) * (wide ? 2 : 1);
   const size_t order_bytes = ((q_tiles * 4 + 255) / 256) * 256;
   unsigned int* dq_order = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(g->workspace) + ((rows * 4 + 255) / 256) * 256);
   // fp32 gradients: the kernel's reduce-add lands in the caller's dq directly, no copy afterwards
@@ -445,17 +448,17 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
 
   BwdParams p;
   memset(&p, 0, sizeof(p));
-  if ((rc = make_qkv_maps(a, st, &p.map_q, &p.map_k, &p.map_v))) return rc;
+  if ((rc = make_qkv_maps(a, st, &p.map_q, &p.map_k, &p.map_v, wide ? 64 : kTile))) return rc;
   TensorDesc4 t;
   t.dtype = a->dtype; t.ptr = g->d_o;
   t.dims[0] = a->D; t.dims[1] = a->S_q; t.dims[2] = a->N; t.dims[3] = a->B;
   t.strides[0] = st.o[2]; t.strides[1] = st.o[1]; t.strides[2] = st.o[0];
-  if ((rc = make_tmap_4d(&p.map_do, t, kTile))) return rc;
+  if ((rc = make_tmap_4d(&p.map_do, t, wide ? 64 : kTile))) return rc;
   // the fp32 dQ accumulator, packed [B,N,S_q,D]: target of the kernel's TMA reduce-add
   t.dtype = ACCT_F32; t.ptr = dq_acc;
   t.strides[0] = a->D; t.strides[1] = static_cast<int64_t>(a->S_q) * a->D;
   t.strides[2] = static_cast<int64_t>(a->N) * a->S_q * a->D;
-  if ((rc = make_tmap_4d(&p.map_dq, t, kTile))) return rc;
+  if ((rc = make_tmap_4d(&p.map_dq, t, wide ? 64 : kTile))) return rc;
 
   // one zero-fill covers the turn counters and the accumulator behind them in the workspace
   const size_t acc_bytes = rows * static_cast<size_t>(a->D) * 4;
@@ -477,7 +480,7 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
     e = cudaEventRecord(static_cast<cudaEvent_t>(g->ev_kernel_start), s);
     if (e != cudaSuccess) return fail_cuda(e, "recording the kernel-start event");
   }
-  e = launch_fa_bwd(p, bf16, s);
+  e = wide ? launch_fa_bwd_wide(p, bf16, s) : launch_fa_bwd(p, bf16, s);
   if (e != cudaSuccess) return fail_cuda(e, "launching the backward kernel");
   if (g->ev_kernel_stop != nullptr) {
     e = cudaEventRecord(static_cast<cudaEvent_t>(g->ev_kernel_stop), s);

@@ -47,7 +47,8 @@ struct alignas(64) BwdParams {
   const float* lse;                 // [B,N,S_q]
   const float* delta;               // [B,N,S_q]  rowsum(dO * O)
   float* dq_acc;                    // [B,N,S_q,D] fp32, zeroed before launch
-  unsigned int* dq_order;           // [B,N,ceil(S_q/128)] turn counters, zeroed before launch; nullptr = any order
+  unsigned int* dq_order;           // [B,N,ceil(S_q/128)] turn counters (x 2 for head_dim > 128), zeroed before launch;
+                                    // nullptr = any order
   void* dk;
   void* dv;
   int grads_f32;
@@ -88,6 +89,8 @@ cudaError_t launch_mask_classify(const void* mask, int dtype, int batch, int S_q
 // Launchers: return cudaGetLastError() of the launch.
 cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream);
 cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream);
+// head_dim in (128, 256]: Q / dO maps with 64-row boxes, the dQ map with a 32 x 64 box, two turn counters per Q tile
+cudaError_t launch_fa_bwd_wide(const BwdParams& p, bool bf16, cudaStream_t stream);
 // writes the {0,1} mask the kernels' in-kernel dropout uses, [units, S_q, S_k] uint8 (units = B*N)
 cudaError_t launch_dropout_mask(unsigned char* mask, int units, int S_q, int S_k, unsigned int seed_lo, unsigned int seed_hi,
                                 unsigned int offset, unsigned int threshold, cudaStream_t stream);

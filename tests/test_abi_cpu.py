@@ -102,16 +102,23 @@ def test_forward_validation_codes(lib, kw, code):
     assert lib.acct_last_error() != b""
 
 
-def test_head_dim_limits_differ_for_forward_and_backward(lib):
-    # forward / prefill take head_dim up to 256 (the reference cell's limit); the backward stops at 128
+def test_head_dim_limit_is_the_reference_cells_for_forward_and_backward(lib):
+    # forward, prefill and backward all take head_dim up to 256, the reference cell's limit
+    # (nn/layer/flash_attention.py:26,105-106); above it, or not a multiple of 8, is refused
     a = _args(D=160, lse=0x2000)
-    rc = lib.acct_fa_fwd(C.byref(a), None)
-    assert rc in (0, 9)          # passes validation; 9 = no sm_100 device on this machine
+    assert lib.acct_fa_fwd(C.byref(a), None) in (0, 9)          # passes validation; 9 = no sm_100 device on this machine
     g = _lib.FaBwdIO()
     g.d_o = g.dq = g.dk = g.dv = 0x3000
     g.workspace, g.workspace_bytes = 0x4000, 1 << 30
-    assert lib.acct_fa_bwd(C.byref(a), C.byref(g), None) == 4
-    assert b"backward" in lib.acct_last_error()
+    assert lib.acct_fa_bwd(C.byref(a), C.byref(g), None) in (0, 9)
+    for bad in (264, 100):
+        a = _args(D=bad, lse=0x2000)
+        assert lib.acct_fa_fwd(C.byref(a), None) == 4
+        assert lib.acct_fa_bwd(C.byref(a), C.byref(g), None) == 4
+    # two turn counters per Q tile above head_dim 128 (two CTAs share a K/V tile there)
+    lo, hi = _args(D=128, S_q=128 * 1024), _args(D=136, S_q=128 * 1024)
+    extra = lib.acct_fa_bwd_workspace_bytes(C.byref(hi)) - lib.acct_fa_bwd_workspace_bytes(C.byref(lo))
+    assert extra == 128 * 1024 * 8 * 4 + 1024 * 4
 
 
 def test_null_struct_pointers(lib):

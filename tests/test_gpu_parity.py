@@ -250,18 +250,23 @@ def test_forward_head_dims_above_128(dev, D, S_q, S_k, causal):
     _status()
     _, l_ref = ref.sa_fwd(q.numpy(), k.numpy(), v.numpy(), causal=causal, scale=1.0 / math.sqrt(D))
     assert float(np.max(np.abs(_np(lse) - l_ref))) <= O_TOL
-    from acctransformer_b200._lib import AcctError
-    with pytest.raises(AcctError, match="UNSUPPORTED_D"):
-        ops.fa_backward(q.to(dev), k.to(dev), v.to(dev), o, lse, o, causal=causal)
+    # and the backward at these widths (two CTAs per K/V tile, one per half of head_dim)
+    do = _rand((B, N, S_q, D), 143, std=0.5)
+    grads = ops.fa_backward(q.to(dev), k.to(dev), v.to(dev), o, lse, do.to(dev), causal=causal, scale=1.0 / math.sqrt(D))
+    _status()
+    g_ref = ref.sa_grad(q.numpy(), k.numpy(), v.numpy(), do.numpy(), causal=causal, scale=1.0 / math.sqrt(D))
+    for g, want, name in zip(grads, g_ref, ("dq", "dk", "dv")):
+        _check_g(g, want, name)
 
 
 @pytest.mark.parametrize("D, what, backward", [(64, "alibi", True), (64, "mask", True), (64, "slopes+dropout", True),
                                                (128, "alibi", True), (128, "mask+philox", True), (128, "slopes", True),
-                                               (160, "mask", False), (160, "alibi+dropout", False), (256, "slopes", False)])
+                                               (160, "mask", True), (160, "alibi+dropout", True), (256, "slopes", True),
+                                               (192, "mask+philox", True)])
 def test_every_kernel_variant_of_every_width(dev, D, what, backward):
     """The kernels are compiled per head_dim width (64 / 128 / 256) and per combination of mask, alibi and dropout
     kind; head_dim 128 has every combination, the other widths fold mask and alibi into one variant.  One case per
-    family, ragged lengths, forward (and backward where head_dim allows) against the oracle."""
+    family, ragged lengths, forward and backward against the oracle."""
     ops = _ops()
     B, N, S_q, S_k = 2, 2, 200, 333
     scale = 1.0 / math.sqrt(D)
@@ -513,3 +518,71 @@ def test_cell_with_the_128x128_tile_mask_form(dev):
         for t, want, name in zip((q, k, v), g_ref, ("dq", "dk", "dv")):
             _check_g(t.grad, want, name)
     _status()
+
+
+@pytest.mark.parametrize("D, dtype, kw", [(160, torch.float16, dict(causal=True)),
+                                          (256, torch.bfloat16, dict(prev_block_num=1, next_block_num=1)),
+                                          (200, torch.float16, dict(tri_block=300)),
+                                          (256, torch.float16, dict(causal=True, kv_heads=1))])
+def test_backward_head_dims_above_128(dev, D, dtype, kw):
+    """The reference cell accepts head_dim up to 256 (nn/layer/flash_attention.py:26,105-106; its Wukong shapes use
+    40, 80 and 160).  Forward + backward at such widths, ragged lengths, fp32 and 16-bit gradients, grouped heads,
+    deterministic dQ, and the cell itself."""
+    ops = _ops()
+    kw = dict(kw)
+    n_kv = kw.pop("kv_heads", None)
+    B, N, S_q, S_k = 2, 2, 333, 451
+    if kw.get("causal") or "tri_block" in kw:
+        S_k = S_q
+    std = 0.5
+    q, do = _rand((B, N, S_q, D), 160, dtype, std), _rand((B, N, S_q, D), 163, dtype, std)
+    k, v = _rand((B, n_kv or N, S_k, D), 161, dtype, std), _rand((B, n_kv or N, S_k, D), 162, dtype, std)
+    scale = 1.0 / math.sqrt(D)
+    qd, kd, vd, dod = (t.to(dev) for t in (q, k, v, do))
+    o, lse = ops.fa_forward(qd, kd, vd, scale=scale, **kw)
+    qn, kn, vn, don = (_to_np16(t) for t in (q, k, v, do))
+    okw = dict(kw)
+    tri = okw.pop("tri_block", None)
+    if tri:     # the oracle's TriangleAttention takes the group bound as an all-zero mask plus the block size
+        o_ref = ref.triangle_fwd(qn * scale, kn, vn, np.zeros((B, S_q, S_k), np.float32), block_size=tri)
+        gmask = (np.arange(S_k)[None, :] >= ((np.arange(S_q)[:, None] // tri + 1) * tri)).astype(np.float32)
+        okw = dict(attn_mask=np.broadcast_to(gmask * 1e4, (B, S_q, S_k)))     # far below any score: excluded
+        _check_o(o, o_ref, O_TOL if dtype == torch.float16 else BF16_O_TOL)
+        g_ref = ref.sa_grad(qn, kn, vn, don, scale=scale, **okw)
+    elif n_kv:
+        g_ref = ref.gqa_grad(qn, kn, vn, don, scale=scale, **okw)
+    else:
+        o_ref, _ = ref.sa_fwd(qn, kn, vn, scale=scale, **okw)
+        _check_o(o, o_ref, O_TOL if dtype == torch.float16 else BF16_O_TOL)
+        g_ref = ref.sa_grad(qn, kn, vn, don, scale=scale, **okw)
+    for fp32 in (False, True):
+        grads = ops.fa_backward(qd, kd, vd, o, lse, dod, scale=scale, grads_fp32=fp32, **kw)
+        _status()
+        assert grads[0].dtype == (torch.float32 if fp32 else dtype)
+        for g, want, name in zip(grads, g_ref, ("dq", "dk", "dv")):
+            rel = float(np.max(np.abs(_np(g) - want)) / np.max(np.abs(want)))
+            assert rel <= (G_TOL if dtype == torch.float16 or fp32 else 2e-2), f"{name} fp32={fp32}: {rel}"
+    runs = [ops.fa_backward(qd, kd, vd, o, lse, dod, scale=scale, deterministic=True, **kw) for _ in range(2)]
+    _status()
+    for a, b_ in zip(*runs):
+        assert torch.equal(a, b_)
+    for a, b_ in zip(runs[0], grads):
+        assert float((a.float() - b_.float()).abs().max()) <= 1e-2 * float(b_.float().abs().max())
+
+
+def test_cell_trains_at_head_dim_160(dev):
+    from acctransformer_b200 import FlashAttention
+    B, N, S, D = 1, 2, 384, 160
+    q, k, v, do = (_rand((B, N, S, D), 170 + i, std=0.5) for i in range(4))
+    mask = torch.triu(torch.ones(1, S, S, dtype=torch.float16), diagonal=1)
+    layer = FlashAttention(head_dim=D)
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    o = layer(qd, kd, vd, mask.to(dev))
+    o.backward(do.to(dev))
+    _status()
+    scale = 1.0 / math.sqrt(D)
+    o_ref, _ = ref.sa_fwd(q.numpy(), k.numpy(), v.numpy(), mask.numpy(), scale=scale)
+    _check_o(o, o_ref)
+    for g, want, name in zip((qd.grad, kd.grad, vd.grad),
+                             ref.sa_grad(q.numpy(), k.numpy(), v.numpy(), do.numpy(), mask.numpy(), scale=scale), ("dq", "dk", "dv")):
+        _check_g(g, want, name)
