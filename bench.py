@@ -321,7 +321,9 @@ def run_ours(args):
             if len(keep_alive) > 2:
                 keep_alive.pop(0)
 
-        e2e_iters = max(2, min(args.steps, 5))
+        # enough steps for the three-stage pipeline (upload, kernels, read-back) to reach its steady state: its
+        # fill and drain (one upload + one read-back, ~2 steps' worth of copying) are inside the timed region
+        e2e_iters = max(4, min(args.steps, 40))
         e2e_step()
         ms_e2e = timed(e2e_step, e2e_iters, join=d2h_stream)
         if world > 1:
