@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(HERE, "libacct_b200.so")
 
-SOURCES = ["api.cu", "fa_fwd.cu", "fa_bwd.cu", "fa_bwd_wide.cu", "decode.cu", "decode_static.cu", "ms_aot.cu"]
+SOURCES = ["api.cu", "fa_fwd.cu", "fa_bwd.cu", "fa_bwd_wide.cu", "decode.cu", "decode_gqa.cu", "decode_static.cu", "ms_aot.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

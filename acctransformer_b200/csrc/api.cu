@@ -536,8 +536,9 @@ int acct_infer_decode(const acct_decode_args* a, void* stream) {
     return fail(ACCT_ERR_SHAPE, "N_kv = %d must be 0 or a divisor of N = %d", a->N_kv, a->N);
   const int n_kv = a->N_kv > 0 ? a->N_kv : a->N;
   const int group = a->N / n_kv;
-  if (group != 1 && group != 2 && group != 4 && group != 8)
-    return fail(ACCT_ERR_SHAPE, "decode takes N / N_kv in {1, 2, 4, 8}, got %d", group);
+  if (!((a->D <= 128 && group <= 16) || group == 1 || group == 2 || group == 4 || group == 8))
+    return fail(ACCT_ERR_SHAPE, "decode takes N / N_kv up to 16 at head_dim <= 128 and in {1, 2, 4, 8} above, got %d at head_dim %d",
+                group, a->D);
   int page_shift = 0;
   if (a->block_table != nullptr) {
     if (a->page_size < 16 || (a->page_size & (a->page_size - 1)) != 0)

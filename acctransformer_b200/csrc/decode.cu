@@ -390,6 +390,13 @@ __global__ void decode_merge_kernel(const DecodeParams p) {
   }
 }
 
+cudaError_t launch_merge(const DecodeParams& p, bool bf16, cudaStream_t stream) {
+  const int threads = p.D <= 64 ? 64 : (p.D <= 128 ? 128 : 256);
+  if (bf16) decode_merge_kernel<true><<<p.B * p.N, threads, 0, stream>>>(p);
+  else decode_merge_kernel<false><<<p.B * p.N, threads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
 template <int LPR, int G>
 cudaError_t launch_decode_g(const DecodeParams& p, bool bf16, cudaStream_t stream) {
   dim3 grid(p.splits, p.B * (p.N / G));
@@ -397,10 +404,7 @@ cudaError_t launch_decode_g(const DecodeParams& p, bool bf16, cudaStream_t strea
   else decode_split_kernel<LPR, false, G><<<grid, kDecodeThreads, 0, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  const int threads = p.D <= 64 ? 64 : (p.D <= 128 ? 128 : 256);
-  if (bf16) decode_merge_kernel<true><<<p.B * p.N, threads, 0, stream>>>(p);
-  else decode_merge_kernel<false><<<p.B * p.N, threads, 0, stream>>>(p);
-  return cudaGetLastError();
+  return launch_merge(p, bf16, stream);
 }
 
 template <int LPR>
@@ -417,6 +421,12 @@ cudaError_t launch_decode_lpr(const DecodeParams& p, bool bf16, cudaStream_t str
 }  // namespace
 
 cudaError_t launch_decode(const DecodeParams& p, bool bf16, cudaStream_t stream) {
+  // several query heads per cache head, head_dim <= 128: the group goes on the rows of a tensor-core MMA
+  if (p.kv_group >= kDecodeGqaMinGroup && p.D <= 128) {
+    cudaError_t e = launch_decode_gqa_split(p, bf16, stream);
+    if (e != cudaSuccess) return e;
+    return launch_merge(p, bf16, stream);
+  }
   if (p.D <= 64) return launch_decode_lpr<8>(p, bf16, stream);
   if (p.D <= 128) return launch_decode_lpr<16>(p, bf16, stream);
   return launch_decode_lpr<32>(p, bf16, stream);

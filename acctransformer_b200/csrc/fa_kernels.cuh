@@ -70,7 +70,7 @@ struct DecodeParams {
   float* part_ml;                   // [B*N, splits, 2]
   int64_t kv_stride_b, kv_stride_h, kv_stride_s;
   int B, N, S_max, D;
-  int kv_group;                     // query heads per key/value head: 1, 2, 4 or 8
+  int kv_group;                     // query heads per key/value head: 1..16 (head_dim <= 128), else 1, 2, 4 or 8
   const int* block_table;           // [B, max_pages] page numbers, or nullptr: contiguous caches
   int page_shift, max_pages;        // rows per page = 1 << page_shift; kv_stride_b is then the page stride
   int splits;
@@ -100,5 +100,11 @@ cudaError_t launch_bwd_delta(const void* o, const void* d_o, float* delta, int64
 cudaError_t launch_bwd_convert_dq(const float* dq_acc, void* dq, int64_t n_elems, bool bf16, bool f32_out,
                                   cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams& p, bool bf16, cudaStream_t stream);
+// split kernel for 2..16 query heads per cache head at head_dim <= 128 (tensor-core path, decode_gqa.cu)
+cudaError_t launch_decode_gqa_split(const DecodeParams& p, bool bf16, cudaStream_t stream);
+#ifndef ACCT_DECODE_GQA_MIN_GROUP
+#define ACCT_DECODE_GQA_MIN_GROUP 2
+#endif
+constexpr int kDecodeGqaMinGroup = ACCT_DECODE_GQA_MIN_GROUP;   // groups of at least this many heads take that path
 
 }  // namespace acct

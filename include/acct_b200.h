@@ -260,8 +260,9 @@ typedef struct acct_decode_args {
   int32_t num_splits;       /* 0 = choose from the device's SM count */
   void* workspace;          /* device, >= acct_infer_decode_workspace_bytes() */
   size_t workspace_bytes;
-  int32_t N_kv;             /* heads of the caches: 0 or N, or a divisor of N with N / N_kv <= 8 (grouped-query
-                               attention: the query heads of a group share one pass over their key/value head) */
+  int32_t N_kv;             /* heads of the caches: 0 or N, or a divisor of N (grouped-query attention: the query heads
+                               of a group share one pass over their key/value head): N / N_kv up to 16 at head_dim <= 128,
+                               one of 2, 4, 8 above */
   /* Paged caches (block_table != NULL): k_cache / v_cache are page pools [num_pages, N_kv, page_size, D] (kv_stride =
    * element strides of page, head, row; 0 = packed), and key position s of sequence b lives in row s % page_size of
    * page block_table[b * max_pages + s / page_size].  S_max is then max_pages * page_size.  No counterpart in the

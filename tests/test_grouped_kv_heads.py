@@ -109,11 +109,35 @@ def test_prefill_and_decode_with_fewer_kv_heads(dev):
     yp_ref = ref.infer_fwd(_np(qp), ref.expand_kv_heads(_np(kp), 8), ref.expand_kv_heads(_np(vp), 8), scale=0.125,
                            causal=True)
     assert np.max(np.abs(_np(yp) - yp_ref)) <= 2e-3
-    # a group of 3 query heads per cache head is not built for decode
+    # above head_dim 128 the groups are 2, 4 or 8 heads; 3 is refused there
     with pytest.raises(Exception):
-        ops.infer_decode(torch.zeros(1, 6, 1, 64, dtype=torch.float16, device=dev),
-                         torch.zeros(1, 2, 64, 64, dtype=torch.float16, device=dev),
-                         torch.zeros(1, 2, 64, 64, dtype=torch.float16, device=dev))
+        ops.infer_decode(torch.zeros(1, 6, 1, 160, dtype=torch.float16, device=dev),
+                         torch.zeros(1, 2, 64, 160, dtype=torch.float16, device=dev),
+                         torch.zeros(1, 2, 64, 160, dtype=torch.float16, device=dev))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D, N, N_kv, dtype, S", [(128, 32, 4, torch.float16, 5000), (128, 12, 4, torch.float16, 333),
+                                                   (128, 16, 1, torch.bfloat16, 2100), (64, 10, 2, torch.float16, 1000),
+                                                   (40, 6, 2, torch.float16, 777), (80, 14, 1, torch.float16, 4097),
+                                                   (128, 4, 2, torch.float16, 16)])
+def test_decode_with_the_group_on_tensor_cores(dev, D, N, N_kv, dtype, S):
+    """Groups of 2 to 16 query heads per cache head at head_dim <= 128 (3, 5, 7, 14 and 16 included), ragged lengths
+    that end inside a 16-row tile, a length of 1, every split count, head_dim that is not a multiple of 16."""
+    from acctransformer_b200 import ops
+    rs = np.random.RandomState(18)
+    B = 3
+    q = torch.tensor(rs.randn(B, N, 1, D).astype(np.float32)).to(dtype).to(dev)
+    kc = torch.tensor(rs.randn(B, N_kv, S, D).astype(np.float32)).to(dtype).to(dev)
+    vc = torch.tensor(rs.randn(B, N_kv, S, D).astype(np.float32)).to(dtype).to(dev)
+    lens = torch.tensor([S, 1, max(1, S // 3 + 5)], dtype=torch.int32, device=dev)
+    scale = 1.0 / math.sqrt(D)
+    y_ref = ref.decode_ref(_np(q), ref.expand_kv_heads(_np(kc), N), ref.expand_kv_heads(_np(vc), N), lens.cpu().numpy(), scale)
+    tol = 2e-3 if dtype == torch.float16 else 8e-3
+    for splits in (0, 1, 5):
+        y = ops.infer_decode(q, kc, vc, lens, scale=scale, num_splits=splits)
+        torch.cuda.synchronize()
+        assert np.max(np.abs(_np(y) - y_ref)) <= tol, splits
 
 
 @pytest.mark.gpu
