@@ -460,12 +460,9 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   t.strides[2] = static_cast<int64_t>(a->N) * a->S_q * a->D;
   if ((rc = make_tmap_4d(&p.map_dq, t, wide ? 64 : kTile))) return rc;
 
-  // one zero-fill covers the turn counters and the accumulator behind them in the workspace
-  const size_t acc_bytes = rows * static_cast<size_t>(a->D) * 4;
-  cudaError_t e = cudaMemsetAsync(dq_order, 0, order_bytes + (dq_in_place ? 0 : acc_bytes), s);
-  if (e == cudaSuccess && dq_in_place) e = cudaMemsetAsync(dq_acc, 0, acc_bytes, s);
-  if (e != cudaSuccess) return fail_cuda(e, "zero-filling the dQ accumulator");
-  e = launch_bwd_delta(a->o, g->d_o, delta, static_cast<int64_t>(rows), a->D, st.o[0], st.o[1], st.o[2], a->N, a->S_q, bf16, s);
+  // one helper pass before the main kernel: row sums, and the zero-fill of the accumulator and the turn counters
+  cudaError_t e = launch_bwd_delta(a->o, g->d_o, delta, static_cast<int64_t>(rows), a->D, st.o[0], st.o[1], st.o[2], a->N,
+                                   a->S_q, bf16, s, dq_acc, dq_order, static_cast<int64_t>(q_tiles));
   if (e != cudaSuccess) return fail_cuda(e, "launching the row-sum kernel");
   p.lse = a->lse; p.delta = delta; p.dq_acc = dq_acc;
   p.dq_order = (a->flags & ACCT_FLAG_DETERMINISTIC) ? dq_order : nullptr;

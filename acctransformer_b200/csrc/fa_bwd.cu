@@ -42,6 +42,7 @@ constexpr int kDrainWarp0 = 8;
 constexpr int kProducerWarp = 12;
 constexpr int kMmaWarp = 13;
 constexpr int kStages = 2;              // Q stages (dO has one)
+constexpr int kBwdUnitGroup = 8;        // (batch, head) slices whose thread blocks are interleaved, heaviest tiles first
 // Register budget per thread after the warpgroups re-split the register file (512 x 128 at launch):
 // 256 x 152 + 128 x 152 + 128 x 56 = 65536.
 constexpr int kRegsCompute = 152, kRegsDrain = 152, kRegsControl = 56;
@@ -153,16 +154,29 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  // blockIdx.y = (batch, key/value head).  With grouped-query attention the CTA walks the Q tiles of every query
-  // head of its group in turn (dK and dV sum over them); head_of(n) / tile_of(n) name the n-th step.
+  // Linear thread-block number -> ((batch, key/value head) slice, K/V tile).  Thread blocks start in the order of
+  // their number and cost as many steps as their K/V tile has Q tiles, so the heaviest tiles of ALL slices of a group
+  // go first (under a causal mask tile 0 walks every Q tile, the last tile one): the SMs then finish together, which
+  // matters most when a slice has few tiles.  Groups of kBwdUnitGroup slices keep the Q, dO and dQ tiles that the
+  // running thread blocks share within L2.
+  // With grouped-query attention the CTA walks the Q tiles of every query head of its group in turn (dK and dV sum
+  // over them); head_of(n) / tile_of(n) name the n-th step.
+  // With an ordered dQ reduction the CTA of tile j waits for the CTAs of the later tiles (j' > j) that touch the same
+  // Q tile, so those must never be scheduled behind it: tiles are then handed out in descending order, and every wait
+  // points at a CTA that is already running or finished, however many tiles a slice has and however few SMs are free.
   const int n_kv = p.N / p.kv_group;
-  const int bh_kv = blockIdx.y;
+  const int n_j = (p.S_k + kTile - 1) / kTile;
+  int bh_kv, j;
+  {
+    const int n_units = p.B * n_kv;
+    const int per_group = n_j * kBwdUnitGroup;
+    const int grp = blockIdx.x / per_group, within = blockIdx.x % per_group;
+    const int g_units = min(kBwdUnitGroup, n_units - grp * kBwdUnitGroup);
+    const int jj = within / g_units;
+    bh_kv = grp * kBwdUnitGroup + within % g_units;
+    j = p.dq_order != nullptr ? n_j - 1 - jj : jj;
+  }
   const int b = bh_kv / n_kv, h_kv = bh_kv % n_kv;
-  // K/V tile.  With an ordered dQ reduction the CTA of tile j waits for the CTAs of the later tiles (j' > j) that
-  // touch the same Q tile, so those must never be scheduled behind it: tiles are then handed out in descending
-  // order (thread blocks start in the order of their linear index), and every wait points at a CTA that is already
-  // running or finished, however many tiles a (batch, head) slice has and however few SMs are free.
-  const int j = p.dq_order != nullptr ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
   const ScoreMods& mods = p.mods;
 
   if ((smem_u32(smem) & 1023u) != 0u) {          // the swizzled tiles need a 1024-byte aligned base
@@ -640,18 +654,30 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
 
 // D[row] = sum_d dO[row,d] * O[row,d]  (fp32).  LPR lanes x 16 bytes cover one row, so a warp takes 32 / LPR rows per
 // step and every lane loads; a thread block walks rows with a grid stride.
+// The same pass zero-fills what the main kernel adds into: row `row` of the packed fp32 dQ accumulator [rows, D] and
+// the turn counters (the reference leaves that to its runtime, which zero-fills "atomic add" outputs before the
+// launch: flash_attention_bwd.py:55-57).
 template <bool BF16, int LPR>
 __global__ void bwd_delta_kernel(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t sb,
-                                 int64_t sh_, int64_t ss, int N, int S_q) {
+                                 int64_t sh_, int64_t ss, int N, int S_q, float* zero_acc, unsigned int* counters,
+                                 int64_t n_counters) {
   constexpr int RPW = 32 / LPR;
   const int lane = threadIdx.x & 31;
   const int sub = lane % LPR, rsub = lane / LPR;
   const int64_t warp_global = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + (threadIdx.x >> 5);
   const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x / 32);
+  for (int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < n_counters;
+       c += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    counters[c] = 0u;
   for (int64_t row0 = warp_global * RPW; row0 < rows; row0 += warps_total * RPW) {
     const int64_t row = row0 + rsub;
     float acc = 0.f;
     if (row < rows && sub * 8 < D) {
+      if (zero_acc != nullptr) {
+        float4* z = reinterpret_cast<float4*>(zero_acc + row * D + sub * 8);
+        z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
       const int64_t bh = row / S_q;
       const int64_t off = (bh / N) * sb + (bh % N) * sh_ + (row % S_q) * ss;
       const uint4 a = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(o) + off + sub * 8);
@@ -695,7 +721,7 @@ __global__ void bwd_convert_kernel(const float* __restrict__ src, void* __restri
 cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : 128;
   const size_t smem = static_cast<size_t>(3 + kStages) * (dpad / 64) * 16384 + 2 * 32768 + sizeof(BwdShared);
-  dim3 grid((p.S_k + kTile - 1) / kTile, p.B * (p.N / p.kv_group));
+  dim3 grid(static_cast<unsigned>((p.S_k + kTile - 1) / kTile) * static_cast<unsigned>(p.B * (p.N / p.kv_group)));
   // (row groups of a multiple of 128 rows never cut a tile: the tile ranges alone take care of them)
   const bool masked = p.mods.mask_kind != 0 || (p.mods.tri_block > 0 && p.mods.tri_block % kTile != 0);
   const int drop = p.mods.drop_philox != 0 ? 1 : (p.mods.drop != nullptr ? 2 : 0);
@@ -716,24 +742,30 @@ cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
 
 template <int LPR>
 static cudaError_t launch_bwd_delta_lpr(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t sb,
-                                        int64_t sh_, int64_t ss, int N, int S_q, bool bf16, cudaStream_t stream) {
+                                        int64_t sh_, int64_t ss, int N, int S_q, bool bf16, cudaStream_t stream,
+                                        float* zero_acc, unsigned int* counters, int64_t n_counters) {
   const int warps = 8;
   const int64_t rows_per_block = static_cast<int64_t>(warps) * (32 / LPR);
   int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
   const int64_t cap = 148 * 32;   // a few waves of blocks; the grid stride covers the rest
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  if (bf16) bwd_delta_kernel<true, LPR><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(o, d_o, delta, rows, D, sb, sh_, ss, N, S_q);
-  else bwd_delta_kernel<false, LPR><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(o, d_o, delta, rows, D, sb, sh_, ss, N, S_q);
+  if (bf16) bwd_delta_kernel<true, LPR><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(o, d_o, delta, rows, D, sb, sh_, ss, N, S_q, zero_acc, counters, n_counters);
+  else bwd_delta_kernel<false, LPR><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(o, d_o, delta, rows, D, sb, sh_, ss, N, S_q, zero_acc, counters, n_counters);
   return cudaGetLastError();
 }
 
 cudaError_t launch_bwd_delta(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t o_stride_b,
                              int64_t o_stride_h, int64_t o_stride_s, int N, int S_q, bool bf16,
-                             cudaStream_t stream) {
-  if (D <= 64) return launch_bwd_delta_lpr<8>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q, bf16, stream);
-  if (D <= 128) return launch_bwd_delta_lpr<16>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q, bf16, stream);
-  return launch_bwd_delta_lpr<32>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q, bf16, stream);
+                             cudaStream_t stream, float* zero_acc, unsigned int* counters, int64_t n_counters) {
+  if (D <= 64)
+    return launch_bwd_delta_lpr<8>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q, bf16, stream, zero_acc,
+                                   counters, n_counters);
+  if (D <= 128)
+    return launch_bwd_delta_lpr<16>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q, bf16, stream, zero_acc,
+                                    counters, n_counters);
+  return launch_bwd_delta_lpr<32>(o, d_o, delta, rows, D, o_stride_b, o_stride_h, o_stride_s, N, S_q, bf16, stream, zero_acc,
+                                  counters, n_counters);
 }
 
 cudaError_t launch_bwd_convert_dq(const float* dq_acc, void* dq, int64_t n_elems, bool bf16, bool f32_out,

@@ -94,9 +94,10 @@ cudaError_t launch_fa_bwd_wide(const BwdParams& p, bool bf16, cudaStream_t strea
 // writes the {0,1} mask the kernels' in-kernel dropout uses, [units, S_q, S_k] uint8 (units = B*N)
 cudaError_t launch_dropout_mask(unsigned char* mask, int units, int S_q, int S_k, unsigned int seed_lo, unsigned int seed_hi,
                                 unsigned int offset, unsigned int threshold, cudaStream_t stream);
+// delta = rowsum(dO * O); the same pass zero-fills the packed fp32 dQ accumulator zero_acc[rows, D] and the counters
 cudaError_t launch_bwd_delta(const void* o, const void* d_o, float* delta, int64_t rows, int D, int64_t o_stride_b,
                              int64_t o_stride_h, int64_t o_stride_s, int N, int S_q, bool bf16,
-                             cudaStream_t stream);
+                             cudaStream_t stream, float* zero_acc, unsigned int* counters, int64_t n_counters);
 cudaError_t launch_bwd_convert_dq(const float* dq_acc, void* dq, int64_t n_elems, bool bf16, bool f32_out,
                                   cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams& p, bool bf16, cudaStream_t stream);

@@ -132,3 +132,19 @@ def test_dropout_key_is_a_function_of_the_generator_state_alone():
     torch.set_rng_state(state)
     assert _draw_dropout_key() == a
     assert 0 <= a[0] < 2 ** 62 and 0 <= a[1] < 2 ** 32
+
+
+def test_packaging_lists_both_packages_and_the_library():
+    """setup.py installs the implementation, the reference's import paths and the shared library (reference:
+    train/setup.py:22-31 installs a package named acctransformer)."""
+    import ast
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = open(os.path.join(root, "setup.py")).read()
+    ast.parse(src)
+    from setuptools import find_packages
+    pk = find_packages(where=root, include=["acctransformer", "acctransformer.*", "acctransformer_b200", "acctransformer_b200.*"])
+    for want in ("acctransformer", "acctransformer.flash_attention.nn.layer", "acctransformer.triangle_attention",
+                 "acctransformer_b200", "acctransformer_b200.infer", "acctransformer_b200.flash_attention.ops.flash_attention"):
+        assert want in pk, want
+    assert "libacct_b200.so" in src and "build_ext" in src
