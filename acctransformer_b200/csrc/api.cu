@@ -412,7 +412,8 @@ size_t acct_fa_bwd_workspace_bytes(const acct_fa_args* a) {
   if (a == nullptr || a->B <= 0 || a->N <= 0 || a->S_q <= 0 || a->D <= 0) return 0;
   const size_t rows = static_cast<size_t>(a->B) * a->N * a->S_q;
   // (two counters per Q tile above head_dim 128, where two CTAs share a K/V tile by halves of head_dim)
-  const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile) * (a->D > 128 ? 2 : 1);
+  const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile) * (a->D > 128 ? 2 : 1) + 1;
+  // (+ 1: the work counter of the persistent thread blocks)
   // delta [rows] fp32 | turn counters of the ordered dQ reduction [B*N*ceil(S_q/128)] u32 | dQ accumulator
   // [rows, D] fp32; the first two padded to 256 bytes.  With fp32 gradients dq itself is the accumulator.
   const size_t acc = (a->flags & ACCT_FLAG_GRAD_F32) ? 0 : rows * static_cast<size_t>(a->D) * 4;
@@ -438,7 +439,7 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   const size_t rows = static_cast<size_t>(a->B) * a->N * a->S_q;
   float* delta = static_cast<float*>(g->workspace);
   const bool wide = a->D > 128;      // the split-width kernel: 64-row Q / dO boxes, 64-row dQ box, 2 counters per tile
-  const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile) * (wide ? 2 : 1);
+  const size_t q_tiles = static_cast<size_t>(a->B) * a->N * ((a->S_q + kTile - 1) / kTile) * (wide ? 2 : 1) + 1;   // + work counter
   const size_t order_bytes = ((q_tiles * 4 + 255) / 256) * 256;
   unsigned int* dq_order = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(g->workspace) + ((rows * 4 + 255) / 256) * 256);
   // fp32 gradients: the kernel's reduce-add lands in the caller's dq directly, no copy afterwards
@@ -467,6 +468,7 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   p.lse = a->lse; p.delta = delta; p.dq_acc = dq_acc;
   p.dq_order = (a->flags & ACCT_FLAG_DETERMINISTIC) ? dq_order : nullptr;
   p.dk = g->dk; p.dv = g->dv;
+  p.work_counter = dq_order + (q_tiles - 1);
   p.grads_f32 = (a->flags & ACCT_FLAG_GRAD_F32) ? 1 : 0;
   p.B = a->B; p.N = a->N; p.S_q = a->S_q; p.S_k = a->S_k; p.D = a->D;
   p.kv_group = a->N / kv_heads(a);

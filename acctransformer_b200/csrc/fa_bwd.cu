@@ -48,7 +48,11 @@ constexpr int kBwdUnitGroup = 8;        // (batch, head) slices whose thread blo
 constexpr int kRegsCompute = 152, kRegsDrain = 152, kRegsControl = 56;
 
 struct BwdShared {
+  uint64_t item_full[2];         // producer -> everyone: the number of the CTA's next work item is in item[]
+  uint64_t item_empty[2];        // everyone -> producer: the slot has been read by the MMA, drain and compute threads
   uint64_t kv_full;
+  uint64_t kv_empty;             // MMA -> producer: every product of the work item has finished, K and V may be replaced
+  uint64_t acc_free;             // compute -> MMA: dK and dV of the work item have been read out of tensor memory
   uint64_t q_full[kStages];
   uint64_t q_empty[kStages];     // MMA -> producer: the dK product reading this Q stage has finished
   uint64_t do_full;
@@ -61,6 +65,7 @@ struct BwdShared {
   uint64_t stats_ready;          // compute -> compute: lse2 / delta of this Q tile are in shared memory
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
+  int item[2];
   alignas(16) float lse2[2][kTile];   // L * log2(e) per query of the tile (+inf for rows past S_q); read as float4
   alignas(16) float delta[2][kTile];
 };
@@ -129,6 +134,70 @@ __device__ __noinline__ void mask_prepass(const ScoreMods& mods, uint32_t t_st, 
   tmem_wait_st();
 }
 
+// One work item: a 128-row K/V tile of one (batch, key/value head) slice and the Q tiles that touch it.
+struct BwdItem {
+  int b, h_kv, bh_kv, j;
+  int i_lo, n_per, n_iter;     // first Q tile, Q tiles per query head, steps (n_per x query heads of the group)
+  int kv_len;
+};
+
+// Work item number -> item.  Items are numbered so that, inside a group of kBwdUnitGroup slices, the heaviest
+// K/V tiles of ALL slices come first (under a causal mask tile 0 walks every Q tile, the last tile one): the CTAs take
+// items in that order, so the SMs finish together, which matters most when a slice has few tiles, while the Q, dO
+// and dQ tiles that the running CTAs share stay within L2.
+// With an ordered dQ reduction the CTA of tile j waits for the CTAs of the later tiles (j' > j) that touch the same Q
+// tile, so those must never be started after it: tiles are then handed out in descending order, and every wait
+// points at an item that was taken earlier, i.e. is being worked on or finished, however many tiles a slice has.
+__device__ __forceinline__ BwdItem decode_item(const BwdParams& p, int w) {
+  const ScoreMods& mods = p.mods;
+  BwdItem it;
+  const int n_kv = p.N / p.kv_group;
+  const int n_j = (p.S_k + kTile - 1) / kTile;
+  const int n_units = p.B * n_kv;
+  const int per_group = n_j * kBwdUnitGroup;
+  const int grp = w / per_group, within = w % per_group;
+  const int g_units = min(kBwdUnitGroup, n_units - grp * kBwdUnitGroup);
+  const int jj = within / g_units;
+  it.bh_kv = grp * kBwdUnitGroup + within % g_units;
+  it.j = p.dq_order != nullptr ? n_j - 1 - jj : jj;
+  it.b = it.bh_kv / n_kv;
+  it.h_kv = it.bh_kv % n_kv;
+  it.kv_len = p.S_k;
+  if (mods.seq_lens != nullptr) it.kv_len = min(p.S_k, max(0, mods.seq_lens[it.b]));
+  // Q tiles i that need K/V tile j:  j - next <= i <= j + prev, i >= j under the causal triangle
+  int i_lo = 0, i_hi = (p.S_q + kTile - 1) / kTile - 1;
+  if (mods.next_block_num < 65536) i_lo = max(i_lo, it.j - mods.next_block_num);
+  if (mods.prev_block_num < 65536) i_hi = min(i_hi, it.j + mods.prev_block_num);
+  if (mods.causal) i_lo = max(i_lo, it.j);
+  if (mods.tri_block > 0) i_lo = max(i_lo, (((it.j * kTile) / mods.tri_block) * mods.tri_block) / kTile);
+  if (it.j * kTile >= it.kv_len) i_hi = i_lo - 1;
+  it.i_lo = i_lo;
+  it.n_per = max(0, i_hi - i_lo + 1);
+  it.n_iter = it.n_per * p.kv_group;
+  return it;
+}
+
+// Every role learns the number of its CTA's k-th work item here.  This wait does not look at the abort flag: the
+// producer's own waits are all bounded, so it always gets to publish the next number (after a failure: the end
+// marker), and all threads of a role must see the SAME number -- their loops, named barriers and warp-collective
+// instructions depend on it.  Its own limit is generous and is not expected to be reached.
+__device__ __forceinline__ int next_item(uint64_t* item_full, uint64_t* item_empty, const int* item, int k,
+                                         volatile uint32_t* abort_flag, unsigned int* status) {
+  uint64_t* bar = &item_full[k & 1];
+  const uint32_t parity = (k >> 1) & 1;
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if (++polls >= (kWaitPollLimit << 2)) {
+      *abort_flag = 1u;
+      atomicMax(status, DEV_TIMEOUT_SYNC);
+      break;
+    }
+  }
+  const int w = item[k & 1];
+  mbar_arrive(&item_empty[k & 1]);     // the slot may be reused once every consumer has read it
+  return w;
+}
+
 }  // namespace
 
 // MASKED = a mask tensor or TriangleAttention row groups may be present: tiles that need them get a pass over S^T
@@ -154,53 +223,27 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  // Linear thread-block number -> ((batch, key/value head) slice, K/V tile).  Thread blocks start in the order of
-  // their number and cost as many steps as their K/V tile has Q tiles, so the heaviest tiles of ALL slices of a group
-  // go first (under a causal mask tile 0 walks every Q tile, the last tile one): the SMs then finish together, which
-  // matters most when a slice has few tiles.  Groups of kBwdUnitGroup slices keep the Q, dO and dQ tiles that the
-  // running thread blocks share within L2.
-  // With grouped-query attention the CTA walks the Q tiles of every query head of its group in turn (dK and dV sum
-  // over them); head_of(n) / tile_of(n) name the n-th step.
-  // With an ordered dQ reduction the CTA of tile j waits for the CTAs of the later tiles (j' > j) that touch the same
-  // Q tile, so those must never be scheduled behind it: tiles are then handed out in descending order, and every wait
-  // points at a CTA that is already running or finished, however many tiles a slice has and however few SMs are free.
-  const int n_kv = p.N / p.kv_group;
-  const int n_j = (p.S_k + kTile - 1) / kTile;
-  int bh_kv, j;
-  {
-    const int n_units = p.B * n_kv;
-    const int per_group = n_j * kBwdUnitGroup;
-    const int grp = blockIdx.x / per_group, within = blockIdx.x % per_group;
-    const int g_units = min(kBwdUnitGroup, n_units - grp * kBwdUnitGroup);
-    const int jj = within / g_units;
-    bh_kv = grp * kBwdUnitGroup + within % g_units;
-    j = p.dq_order != nullptr ? n_j - 1 - jj : jj;
-  }
-  const int b = bh_kv / n_kv, h_kv = bh_kv % n_kv;
+  // The CTA is persistent: it takes work items (decode_item) one after the other from a global counter until none is
+  // left.  Its tensor memory, barriers and warp roles live for the whole kernel; the K/V tiles of the next item are
+  // requested as soon as the last product of the current one has finished, so that their latency falls under the
+  // current item's dK / dV write-out.  `g0` counts the steps of the items done so far: every barrier that completes
+  // once per step keeps one running phase across items.  `live` counts the items done so far that had any step.
   const ScoreMods& mods = p.mods;
+  const int total_items = ((p.S_k + kTile - 1) / kTile) * p.B * (p.N / p.kv_group);
 
   if ((smem_u32(smem) & 1023u) != 0u) {          // the swizzled tiles need a 1024-byte aligned base
     if (tid == 0) atomicMax(p.status, DEV_BAD_SMEM_BASE);
     return;
   }
 
-  int kv_len = p.S_k;
-  if (mods.seq_lens != nullptr) kv_len = min(p.S_k, max(0, mods.seq_lens[b]));
-
-  // Q tiles i that need K/V tile j:  j - next <= i <= j + prev, i >= j under the causal triangle
-  int i_lo = 0, i_hi = (p.S_q + kTile - 1) / kTile - 1;
-  if (mods.next_block_num < 65536) i_lo = max(i_lo, j - mods.next_block_num);
-  if (mods.prev_block_num < 65536) i_hi = min(i_hi, j + mods.prev_block_num);
-  if (mods.causal) i_lo = max(i_lo, j);
-  if (mods.tri_block > 0) i_lo = max(i_lo, (((j * kTile) / mods.tri_block) * mods.tri_block) / kTile);
-  if (j * kTile >= kv_len) i_hi = i_lo - 1;
-  const int n_per = max(0, i_hi - i_lo + 1);       // Q tiles per query head
-  const int n_iter = n_per * p.kv_group;
-  auto head_of = [&](int n) { return h_kv * p.kv_group + n / max(n_per, 1); };
-  auto tile_of = [&](int n) { return i_lo + n % max(n_per, 1); };
-
   if (tid == 0) {
+    mbar_init(&sh.item_full[0], 1);
+    mbar_init(&sh.item_full[1], 1);
+    mbar_init(&sh.item_empty[0], 1 + kTile + kComputeThreads);
+    mbar_init(&sh.item_empty[1], 1 + kTile + kComputeThreads);
     mbar_init(&sh.kv_full, 1);
+    mbar_init(&sh.kv_empty, 1);
+    mbar_init(&sh.acc_free, kComputeThreads);
     for (int s = 0; s < kStages; ++s) { mbar_init(&sh.q_full[s], 1); mbar_init(&sh.q_empty[s], 1); }
     mbar_init(&sh.do_full, 1);
     mbar_init(&sh.do_empty, 1);
@@ -225,33 +268,54 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     // ------------------------------------------------------------------ control warpgroup
     reg_dealloc<kRegsControl>();
     if (warp == kProducerWarp) {
-      // ---------------------------------------------------------------- TMA producer
-      if (lane == 0 && n_iter > 0) {
+      // ---------------------------------------------------------------- TMA producer (and keeper of the work list)
+      if (lane == 0) {
         prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_do);
         prefetch_tmap(&p.map_dq);
-        mbar_expect_tx(&sh.kv_full, 2 * kTileBytes);
-        for (int nb = 0; nb < NB; ++nb) tma_load_4d(sK + nb * 16384, &p.map_k, &sh.kv_full, nb * 64, j * kTile, h_kv, b);
-        for (int nb = 0; nb < NB; ++nb) tma_load_4d(sV + nb * 16384, &p.map_v, &sh.kv_full, nb * 64, j * kTile, h_kv, b);
-        for (int n = 0; n < n_iter; ++n) {
-          const int i = tile_of(n), h = head_of(n);
-          const int st = n % kStages;
-          // the Q stage is free once the dK product of two tiles ago has finished
-          if (n >= kStages) mbar_wait(&sh.q_empty[st], ((n / kStages) - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-          mbar_expect_tx(&sh.q_full[st], kTileBytes);
-          for (int nb = 0; nb < NB; ++nb)
-            tma_load_4d(sQ + st * kTileBytes + nb * 16384, &p.map_q, &sh.q_full[st], nb * 64, i * kTile, h, b);
-          // dO has one buffer: it is free once the dV product of the previous tile has finished, and is not
-          // needed again before the dP^T product of this tile, most of an iteration later
-          if (n >= 1) mbar_wait(&sh.do_empty, (n - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-          mbar_expect_tx(&sh.do_full, kTileBytes);
-          for (int nb = 0; nb < NB; ++nb)
-            tma_load_4d(sDO + nb * 16384, &p.map_do, &sh.do_full, nb * 64, i * kTile, h, b);
+        int g0 = 0, live = 0;
+        int w = static_cast<int>(atomicAdd(p.work_counter, 1u));
+        sh.item[0] = w;
+        mbar_arrive(&sh.item_full[0]);
+        for (int k = 0; w < total_items; ++k) {
+          const BwdItem it = decode_item(p, w);
+          if (it.n_iter > 0 && *abort_flag == 0u) {
+            // K and V of the previous item are free once all of its products have finished
+            if (live > 0) mbar_wait(&sh.kv_empty, (live - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+            mbar_expect_tx(&sh.kv_full, 2 * kTileBytes);
+            for (int nb = 0; nb < NB; ++nb) tma_load_4d(sK + nb * 16384, &p.map_k, &sh.kv_full, nb * 64, it.j * kTile, it.h_kv, it.b);
+            for (int nb = 0; nb < NB; ++nb) tma_load_4d(sV + nb * 16384, &p.map_v, &sh.kv_full, nb * 64, it.j * kTile, it.h_kv, it.b);
+            for (int n = 0; n < it.n_iter; ++n) {
+              const int i = it.i_lo + n % it.n_per, h = it.h_kv * p.kv_group + n / it.n_per;
+              const int gn = g0 + n;
+              const int st = gn % kStages;
+              // the Q stage is free once the dK product of two tiles ago has finished
+              if (gn >= kStages) mbar_wait(&sh.q_empty[st], ((gn / kStages) - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+              mbar_expect_tx(&sh.q_full[st], kTileBytes);
+              for (int nb = 0; nb < NB; ++nb)
+                tma_load_4d(sQ + st * kTileBytes + nb * 16384, &p.map_q, &sh.q_full[st], nb * 64, i * kTile, h, it.b);
+              // dO has one buffer: it is free once the dV product of the previous tile has finished, and is not
+              // needed again before the dP^T product of this tile, most of an iteration later
+              if (gn >= 1) mbar_wait(&sh.do_empty, (gn - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+              mbar_expect_tx(&sh.do_full, kTileBytes);
+              for (int nb = 0; nb < NB; ++nb)
+                tma_load_4d(sDO + nb * 16384, &p.map_do, &sh.do_full, nb * 64, i * kTile, h, it.b);
+            }
+            g0 += it.n_iter;
+            ++live;
+          }
+          // the next item, once every consumer has read item k-1 out of the slot it goes into (items of one or two
+          // steps let this thread run ahead); after a failure the end marker, so that every role leaves its loop at
+          // the same item
+          if (k >= 1) mbar_wait(&sh.item_empty[(k + 1) & 1], ((k - 1) >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+          w = *abort_flag == 0u ? static_cast<int>(atomicAdd(p.work_counter, 1u)) : total_items;
+          sh.item[(k + 1) & 1] = w;
+          mbar_arrive(&sh.item_full[(k + 1) & 1]);
         }
       }
     } else if (warp == kMmaWarp) {
       // ---------------------------------------------------------------- MMA issuer
       // Tensor-pipe order per Q tile n:  dP^T(n) | dV(n), S^T(n+1) | dK(n), dQ(n).
-      if (lane == 0 && n_iter > 0) {
+      if (lane == 0) {
         const uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);     // S^T, dP^T
         const uint32_t idesc_kv = make_idesc(BF16, 128, DPAD, false, true);    // dV, dK
         const uint32_t idesc_dq = make_idesc(BF16, 128, DPAD, true, true);     // dQ
@@ -276,51 +340,65 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
           umma_commit(&sh.st_full);
         };
 
-        mbar_wait(&sh.kv_full, 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
-        mbar_wait(&sh.q_full[0], 0, abort_flag, p.status, DEV_TIMEOUT_TMA);
-        tc_fence_after_sync();
-        issue_st(0);
-        for (int n = 0; n < n_iter; ++n) {
-          const int st = n % kStages;
-          const int stn = (n + 1) % kStages;
-          const uint32_t mQ = mQ0 + st * kTileUnits;
-          // dP^T = V dO^T as early as possible: it only needs dO and the previous dQ out of its columns
-          mbar_wait(&sh.do_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
-          if (n > 0) mbar_wait(&sh.dq_read, (n - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+        int g0 = 0, live = 0;
+        for (int k = 0;; ++k) {
+          const int w = next_item(sh.item_full, sh.item_empty, sh.item, k, abort_flag, p.status);
+          if (w >= total_items) break;
+          const BwdItem it = decode_item(p, w);
+          if (it.n_iter == 0) continue;
+          const int n_iter = it.n_iter;
+          mbar_wait(&sh.kv_full, live & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+          mbar_wait(&sh.q_full[g0 % kStages], (g0 / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
           tc_fence_after_sync();
-#pragma unroll
-          for (int kk = 0; kk < DPAD / 16; ++kk) {
-            const uint32_t off = (kk >> 2) * 1024u + (kk & 3) * 2u;
-            umma_ss_lohi(tmem + kColDP, kV + off, k_hi, kDO + off, k_hi, idesc_s, kk > 0);
-          }
-          umma_commit(&sh.dp_full);
-          // dV += P^T dO as soon as P^T is in tensor memory (the compute warps go on to dS meanwhile);
-          // P^T of query columns [64h, 64h+64) sits in S^T columns [64h, 64h+32)
-          mbar_wait(&sh.p_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-          tc_fence_after_sync();
-#pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ts_lohi(tmem + kColDV, tmem + kColST + (kk >> 2) * 64 + (kk & 3) * 8, mDO + kk * 128u, mn_hi,
-                         idesc_kv, n > 0 || kk > 0);
-          umma_commit(&sh.do_empty);
-          // S^T of the next Q tile right behind it (the tensor pipe runs in order, so P^T has been consumed)
-          if (n + 1 < n_iter) {
-            mbar_wait(&sh.q_full[stn], ((n + 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+          issue_st(g0 % kStages);
+          for (int n = 0; n < n_iter; ++n) {
+            const int gn = g0 + n;
+            const int st = gn % kStages;
+            const int stn = (gn + 1) % kStages;
+            const uint32_t mQ = mQ0 + st * kTileUnits;
+            // dP^T = V dO^T as early as possible: it only needs dO and the previous dQ out of its columns
+            mbar_wait(&sh.do_full, gn & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+            if (gn > 0) mbar_wait(&sh.dq_read, (gn - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
             tc_fence_after_sync();
-            issue_st(stn);
+#pragma unroll
+            for (int kk = 0; kk < DPAD / 16; ++kk) {
+              const uint32_t off = (kk >> 2) * 1024u + (kk & 3) * 2u;
+              umma_ss_lohi(tmem + kColDP, kV + off, k_hi, kDO + off, k_hi, idesc_s, kk > 0);
+            }
+            umma_commit(&sh.dp_full);
+            // dV += P^T dO as soon as P^T is in tensor memory (the compute warps go on to dS meanwhile);
+            // P^T of query columns [64h, 64h+64) sits in S^T columns [64h, 64h+32)
+            mbar_wait(&sh.p_ready, gn & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+            // the first products of an item overwrite dK and dV: the previous item's must have been read out
+            if (n == 0 && live > 0) mbar_wait(&sh.acc_free, (live - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+            tc_fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)
+              umma_ts_lohi(tmem + kColDV, tmem + kColST + (kk >> 2) * 64 + (kk & 3) * 8, mDO + kk * 128u, mn_hi,
+                           idesc_kv, n > 0 || kk > 0);
+            umma_commit(&sh.do_empty);
+            // S^T of the next Q tile right behind it (the tensor pipe runs in order, so P^T has been consumed)
+            if (n + 1 < n_iter) {
+              mbar_wait(&sh.q_full[stn], ((gn + 1) / kStages) & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
+              tc_fence_after_sync();
+              issue_st(stn);
+            }
+            // dK += dS^T Q and dQ = dS K once dS^T is in shared memory
+            mbar_wait(&sh.ds_ready, gn & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+            tc_fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)   // dK: A = dS^T packed over the dP^T columns, like P^T over S^T
+              umma_ts_lohi(tmem + kColDK, tmem + kColDP + (kk >> 2) * 64 + (kk & 3) * 8, mQ + kk * 128u, mn_hi,
+                           idesc_kv, n > 0 || kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)
+              umma_ss_lohi(tmem + kColDP, mDS + kk * 128u, mn_hi, mK + kk * 128u, mn_hi, idesc_dq, kk > 0);
+            umma_commit(&sh.dq_full);
+            umma_commit(&sh.q_empty[st]);
           }
-          // dK += dS^T Q and dQ = dS K once dS^T is in shared memory
-          mbar_wait(&sh.ds_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-          tc_fence_after_sync();
-#pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)   // dK: A = dS^T packed over the dP^T columns, like P^T over S^T
-            umma_ts_lohi(tmem + kColDK, tmem + kColDP + (kk >> 2) * 64 + (kk & 3) * 8, mQ + kk * 128u, mn_hi,
-                         idesc_kv, n > 0 || kk > 0);
-#pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ss_lohi(tmem + kColDP, mDS + kk * 128u, mn_hi, mK + kk * 128u, mn_hi, idesc_dq, kk > 0);
-          umma_commit(&sh.dq_full);
-          umma_commit(&sh.q_empty[st]);
+          umma_commit(&sh.kv_empty);
+          g0 += n_iter;
+          ++live;
         }
       }
     }
@@ -332,11 +410,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     const int r = tid - kDrainWarp0 * 32;
     const uint32_t t_dq = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kColDP;
     const bool elected = (r == 0);
-    for (int n = 0; n < n_iter; ++n) {
+    int g0 = 0;
+    for (int k = 0;; ++k) {
+    const int w = next_item(sh.item_full, sh.item_empty, sh.item, k, abort_flag, p.status);
+    if (w >= total_items) break;
+    const BwdItem it = decode_item(p, w);
+    const int b = it.b, j = it.j, kv_len = it.kv_len;
+    auto head_of = [&](int n) { return it.h_kv * p.kv_group + n / max(it.n_per, 1); };
+    auto tile_of = [&](int n) { return it.i_lo + n % max(it.n_per, 1); };
+    for (int n = 0; n < it.n_iter; ++n) {
       const int q_base = tile_of(n) * kTile;
       const int h = head_of(n);
       const int bh = b * p.N + h;
-      mbar_wait(&sh.dq_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      mbar_wait(&sh.dq_full, (g0 + n) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
       uint32_t dq[kChunks][32];
 #pragma unroll
@@ -394,18 +480,29 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         }
       }
     }
+    g0 += it.n_iter;
+    }
     if (elected) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ compute warps
     reg_alloc<kRegsCompute>();
     const int hf = warp >> 2;                            // which half of the query columns / of head_dim
     const int r = (warp & 3) * 32 + lane;                // key row inside the tile (and dQ row when draining)
-    const int kv_idx = j * kTile + r;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_st = tmem + lane_base + kColST;
     const uint32_t t_dp = tmem + lane_base + kColDP;
-    const bool kv_ok = kv_idx < kv_len;
     uint8_t* my_ds = sDS + hf * 16384u;                  // this half's dS^T block
+    int g0 = 0;
+    for (int k = 0;; ++k) {
+    const int item_no = next_item(sh.item_full, sh.item_empty, sh.item, k, abort_flag, p.status);
+    if (item_no >= total_items) break;
+    const BwdItem it = decode_item(p, item_no);
+    const int b = it.b, j = it.j, kv_len = it.kv_len, i_lo = it.i_lo, n_per = it.n_per, n_iter = it.n_iter;
+    const int bh_kv = it.bh_kv;
+    auto head_of = [&](int n) { return it.h_kv * p.kv_group + n / max(n_per, 1); };
+    auto tile_of = [&](int n) { return i_lo + n % max(n_per, 1); };
+    const int kv_idx = j * kTile + r;
+    const bool kv_ok = kv_idx < kv_len;
     // alibi term of this key row in log2 units for query head h; -inf removes a key row that does not exist
     auto bias_of = [&](int h) {
       float v = kNegInf;
@@ -426,9 +523,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     if (hf == 0 && n_iter > 0) {
       const int q_row = i_lo * kTile + r;
       const bool q_ok = q_row < p.S_q;
-      const int64_t idx = (static_cast<int64_t>(b) * p.N + head_of(0)) * p.S_q + q_row;
-      sh.lse2[0][r] = q_ok ? p.lse[idx] * kLog2e : INFINITY;
-      sh.delta[0][r] = q_ok ? p.delta[idx] : 0.f;
+      const int64_t idx = (static_cast<int64_t>(b) * p.N + head_of(0)) * p.S_q + min(q_row, p.S_q - 1);
+      // (buffer g0 & 1 was last read for the step before last, whose dS part every thread finished before the
+      // products this thread has since waited for could be issued)
+      sh.lse2[g0 & 1][r] = q_ok ? p.lse[idx] * kLog2e : INFINITY;
+      sh.delta[g0 & 1][r] = q_ok ? p.delta[idx] : 0.f;
       mbar_arrive(&sh.stats_ready);
     }
 
@@ -444,18 +543,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       const int i = tile_of(n);
       const int q_base = i * kTile;
       const int bh = b * p.N + head_of(n);
+      const int gn = g0 + n;                                    // running step number: the phase of the per-step barriers
       if (n % max(n_per, 1) == 0) bias = bias_of(head_of(n));   // first tile of a query head
       mask_class = mask_class_next;
       if (tile_class != nullptr && n + 1 < n_iter) mask_class_next = tile_class[static_cast<int64_t>(tile_of(n + 1)) * tiles_k];
       // ---- P part: needs S^T only
-      mbar_wait(&sh.st_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      mbar_wait(&sh.st_full, gn & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
       // Park this tile's statistics (fetched during the previous tile).  S^T(n) was issued after all 256
       // compute threads arrived at p_ready(n-1), i.e. after they passed the previous stats_ready wait and
       // finished the dS part that read the buffer being overwritten.
       if (hf == 0 && n > 0) {
-        sh.lse2[n & 1][r] = nxt_ok ? nxt_lse * kLog2e : INFINITY;
-        sh.delta[n & 1][r] = nxt_ok ? nxt_dlt : 0.f;
+        sh.lse2[gn & 1][r] = nxt_ok ? nxt_lse * kLog2e : INFINITY;
+        sh.delta[gn & 1][r] = nxt_ok ? nxt_dlt : 0.f;
         mbar_arrive(&sh.stats_ready);
       }
       // fetch the next tile's statistics now
@@ -466,9 +566,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         nxt_lse = p.lse[idx];      // (clamped, always valid address: no branch around the loads)
         nxt_dlt = p.delta[idx];
       }
-      mbar_wait(&sh.stats_ready, n & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-      const float* lse2 = sh.lse2[n & 1];
-      const float* dlt = sh.delta[n & 1];
+      mbar_wait(&sh.stats_ready, gn & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+      const float* lse2 = sh.lse2[gn & 1];
+      const float* dlt = sh.delta[gn & 1];
       // A mask tile that is all 0 is not read; one that is all 1 adds one constant to every score of the tile,
       // which joins the key row's bias; any other tile is read.
       const bool mask_const = MASKED && mods.mask_kind == 1 && mask_class == 2;
@@ -525,7 +625,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       mbar_arrive(&sh.p_ready);
 
       // ---- dS part: dS^T = P^T * (dP^T * M - D) into this half's shared-memory block
-      mbar_wait(&sh.dp_full, n & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+      mbar_wait(&sh.dp_full, gn & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
       {
         uint32_t dp[2][32];
@@ -596,7 +696,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
 
     // epilogue: dK (scaled) and dV rows of this tile; each half writes its half of head_dim.
     // (the tensor-memory loads are warp-collective: every lane runs them, only the stores are guarded)
-    if (n_iter > 0) mbar_wait(&sh.dq_full, (n_iter - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
+    if (n_iter > 0) mbar_wait(&sh.dq_full, (g0 + n_iter - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
     tc_fence_after_sync();
     const bool row_ok = kv_idx < p.S_k;
     const int64_t row_off = (static_cast<int64_t>(bh_kv) * p.S_k + kv_idx) * p.D;
@@ -642,6 +742,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       }
     }
     tc_fence_before_sync();
+    // dK and dV are out of tensor memory: the next item's first products may overwrite them
+    if (n_iter > 0) mbar_arrive(&sh.acc_free);
+    g0 += n_iter;
+    }
   }
 
   linger_after_abort(abort_flag);
@@ -721,7 +825,13 @@ __global__ void bwd_convert_kernel(const float* __restrict__ src, void* __restri
 cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   const int dpad = p.D <= 64 ? 64 : 128;
   const size_t smem = static_cast<size_t>(3 + kStages) * (dpad / 64) * 16384 + 2 * 32768 + sizeof(BwdShared);
-  dim3 grid(static_cast<unsigned>((p.S_k + kTile - 1) / kTile) * static_cast<unsigned>(p.B * (p.N / p.kv_group)));
+  // persistent CTAs, one per SM (tensor memory and shared memory admit no more), fewer if there is less work
+  const long long items = static_cast<long long>((p.S_k + kTile - 1) / kTile) * p.B * (p.N / p.kv_group);
+  int dev = 0, sms = 0;
+  cudaError_t e0 = cudaGetDevice(&dev);
+  if (e0 == cudaSuccess) e0 = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e0 != cudaSuccess) return e0;
+  dim3 grid(static_cast<unsigned>(items < sms ? items : sms));
   // (row groups of a multiple of 128 rows never cut a tile: the tile ranges alone take care of them)
   const bool masked = p.mods.mask_kind != 0 || (p.mods.tri_block > 0 && p.mods.tri_block % kTile != 0);
   const int drop = p.mods.drop_philox != 0 ? 1 : (p.mods.drop != nullptr ? 2 : 0);

@@ -49,6 +49,7 @@ struct alignas(64) BwdParams {
   float* dq_acc;                    // [B,N,S_q,D] fp32, zeroed before launch
   unsigned int* dq_order;           // [B,N,ceil(S_q/128)] turn counters (x 2 for head_dim > 128), zeroed before launch;
                                     // nullptr = any order
+  unsigned int* work_counter;       // one word, zeroed before launch: the next work item of the persistent CTAs
   void* dk;
   void* dv;
   int grads_f32;
