@@ -139,20 +139,37 @@ __global__ void __launch_bounds__(kGqaThreads) decode_gqa_kernel(const DecodePar
   // tiles of 16 rows, dealt to the warps in turn
   const int n_tiles = k1 > k0 ? (k1 - k0 + kTileRows - 1) / kTileRows : 0;
   const int my_tiles = n_tiles > warp ? (n_tiles - warp + kGqaWarps - 1) / kGqaWarps : 0;
+  // A copy instruction moves 32 consecutive 16-byte chunks: kRowsPerCopy whole rows.  This lane always copies chunk
+  // `lcol` of row `lrow` (+ kRowsPerCopy per instruction), so everything but the tile's first row is constant.
+  constexpr int kRowsPerCopy = 32 / kChunksPerRow;
+  const int lrow = lane / kChunksPerRow, lcol = lane % kChunksPerRow;
+  const bool col_ok = lcol * 8 < p.D;
+  const uint32_t dst_lane = lrow * kRowBytes + lcol * 16;
+  const int64_t copy_step = static_cast<int64_t>(kRowsPerCopy) * p.kv_stride_s;
   auto issue_tile = [&](int it) {     // `it`-th tile of this warp into ring slot it % kRing
     const int row0 = k0 + (warp + it * kGqaWarps) * kTileRows;
-    uint8_t* dstK = ring + (it % kRing) * 2 * kTileBytes;
-    uint8_t* dstV = dstK + kTileBytes;
+    const uint32_t dstK = smem_addr(ring + (it % kRing) * 2 * kTileBytes) + dst_lane;
+    const uint32_t dstV = dstK + kTileBytes;
+    if (!paged && row0 + kTileRows <= k1) {
+      // whole tile inside the split, contiguous cache: one address, stepped by a constant
+      int64_t off = static_cast<int64_t>(row0 + lrow) * p.kv_stride_s + lcol * 8;
+      const uint32_t nbytes = col_ok ? 16u : 0u;
+      if (!col_ok) off = 0;
 #pragma unroll
-    for (int c = 0; c < kCopies; ++c) {
-      const int chunk = c * 32 + lane;
-      const int r = chunk / kChunksPerRow, col = chunk % kChunksPerRow;
-      const int row = row0 + r;
-      const bool ok = row < k1 && col * 8 < p.D;
-      const int64_t off = ok ? row_offset(row) + col * 8 : 0;
-      const uint32_t d = r * kRowBytes + col * 16;
-      cp_async16(smem_addr(dstK + d), kbase + off, ok ? 16u : 0u);
-      cp_async16(smem_addr(dstV + d), vbase + off, ok ? 16u : 0u);
+      for (int c = 0; c < kCopies; ++c) {
+        cp_async16(dstK + c * kRowsPerCopy * kRowBytes, kbase + off, nbytes);
+        cp_async16(dstV + c * kRowsPerCopy * kRowBytes, vbase + off, nbytes);
+        if (col_ok) off += copy_step;
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < kCopies; ++c) {
+        const int row = row0 + c * kRowsPerCopy + lrow;
+        const bool ok = row < k1 && col_ok;
+        const int64_t off = ok ? row_offset(row) + lcol * 8 : 0;
+        cp_async16(dstK + c * kRowsPerCopy * kRowBytes, kbase + off, ok ? 16u : 0u);
+        cp_async16(dstV + c * kRowsPerCopy * kRowBytes, vbase + off, ok ? 16u : 0u);
+      }
     }
   };
 

@@ -41,6 +41,8 @@ def parse_args():
     ap.add_argument("--decode-only", action="store_true",
                     help="run only the decode measurement on a quarter-size cache (B=8; 3 x 1.07 GB), for profiling, "
                          "and print its JSON object")
+    ap.add_argument("--decode-group", type=int, default=1,
+                    help="with --decode-only: query heads per cache head (N_kv = 32 / group), e.g. 8 for the tensor-core path")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-aux", action="store_true", help="skip the other configurations (2, 3, 4, 5a)")
@@ -407,6 +409,9 @@ def run_ours(args):
         # configuration 5b is ONE job of 1 024 (sequence, head) units: with several GPUs the heads are dealt out
         # (every GPU keeps all 32 sequences, so the ragged lengths load them equally) and no data crosses
         decode = bench_decode(torch, ops, dev, peaks, rank=rank, world=world, dist=dist if world > 1 else None)
+        if world == 1 and not args.no_aux:
+            # the same step with 4 and 8 query heads per cache head (cache bytes per second; informational)
+            decode["grouped_gbs"] = {f"g{g_}": bench_decode(torch, ops, dev, peaks, group=g_)["achieved_gbs"] for g_ in (4, 8)}
     other = None
     if not args.no_aux and rank == 0 and world == 1 and args.workload == "H":
         other = bench_other_configs(torch, ops, dev, peaks)
@@ -552,7 +557,7 @@ def bench_other_configs(torch, ops, dev, peaks):
     return short
 
 
-def bench_decode(torch, ops, dev, peaks, small=False, rank=0, world=1, dist=None):
+def bench_decode(torch, ops, dev, peaks, small=False, rank=0, world=1, dist=None, group=1):
     """Decode step of configuration 5b (B=32 N=32 KV<=16384 D=128 fp16, per-sequence lengths): achieved HBM GB/s
     counting only the valid K and V rows.  Three cache sets (25.8 GB) are rotated so that no step finds its
     cache in L2.  ``small``: B=8 (3 x 2.1 GB, still far above L2), few iterations, for a profiler capture.
@@ -564,11 +569,14 @@ def bench_decode(torch, ops, dev, peaks, small=False, rank=0, world=1, dist=None
     B, N_job, S, D = (8 if small else c["B"]), c["N"], c["S"], c["D"]
     h0, h1 = unit_slice(N_job, rank, world)
     N = h1 - h0
+    # grouped key/value heads (not part of configuration 5b, whose caches have one head per query head): the caches
+    # then have N / group heads and every cache row serves `group` query heads
+    N_c = max(1, N // group)
     g = torch.Generator(device=dev).manual_seed(6 + 100 * h0)
     sets = []
-    for _ in range(3):
-        kc = torch.empty(B, N, S, D, device=dev, dtype=torch.float16)
-        vc = torch.empty(B, N, S, D, device=dev, dtype=torch.float16)
+    for _ in range(3 if group == 1 else min(12, 3 * group)):      # enough sets that no step finds its cache in L2
+        kc = torch.empty(B, N_c, S, D, device=dev, dtype=torch.float16)
+        vc = torch.empty(B, N_c, S, D, device=dev, dtype=torch.float16)
         kc.normal_(generator=g)
         vc.normal_(generator=g)
         sets.append((kc, vc))
@@ -577,8 +585,9 @@ def bench_decode(torch, ops, dev, peaks, small=False, rank=0, world=1, dist=None
     lens = torch.randint(c["len_lo"], S + 1, (B,), generator=gl, dtype=torch.int32).to(dev)
     ws = ops.DecodeWorkspace(B, N, D, dev)
     y = torch.empty_like(qd)
+    ns = len(sets)
     for i in range(3 if small else 6):
-        ops.infer_decode(qd, sets[i % 3][0], sets[i % 3][1], lens, workspace=ws, out=y)
+        ops.infer_decode(qd, sets[i % ns][0], sets[i % ns][1], lens, workspace=ws, out=y)
     iters = 6 if small else 30
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if dist is not None:
@@ -586,7 +595,7 @@ def bench_decode(torch, ops, dev, peaks, small=False, rank=0, world=1, dist=None
     torch.cuda.synchronize()
     e0.record()
     for i in range(iters):
-        ops.infer_decode(qd, sets[i % 3][0], sets[i % 3][1], lens, workspace=ws, out=y)
+        ops.infer_decode(qd, sets[i % ns][0], sets[i % ns][1], lens, workspace=ws, out=y)
     e1.record()
     torch.cuda.synchronize()
     ms_rank = e0.elapsed_time(e1) / iters
@@ -595,10 +604,11 @@ def bench_decode(torch, ops, dev, peaks, small=False, rank=0, world=1, dist=None
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    nbytes_rank = float(lens.sum().item()) * N * D * 2 * 2
-    nbytes = float(lens.sum().item()) * N_job * D * 2 * 2
+    nbytes_rank = float(lens.sum().item()) * N_c * D * 2 * 2
+    nbytes = float(lens.sum().item()) * (N_job // group) * D * 2 * 2
     gbps = nbytes / (ms * 1e-3) / 1e9
-    return {"workload": f"cfg5b decode B={B} N={N_job} q_len=1 KV<=16384 D=128 fp16, {N} heads per GPU on {world} GPU(s)",
+    return {"workload": f"cfg5b decode B={B} N={N_job} q_len=1 KV<=16384 D=128 fp16, {N} heads per GPU on {world} GPU(s)"
+                        + (f", {group} query heads per cache head" if group > 1 else ""),
             "ms": ms, "bytes": nbytes, "achieved_gbs": gbps, "peak_gbs": world * peaks["hbm_gbs"],
             "frac": gbps / (world * peaks["hbm_gbs"]), "per_gpu_gbs_rank0": nbytes_rank / (ms_rank * 1e-3) / 1e9,
             "peak_source": f"{peaks['which']} hbm_gbs x {world}"}
@@ -613,7 +623,8 @@ def main():
         from acctransformer_b200 import ops
         dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
         torch.cuda.set_device(dev)
-        print(json.dumps({"decode": bench_decode(torch, ops, dev, measured_peaks(), small=True)}), flush=True)
+        print(json.dumps({"decode": bench_decode(torch, ops, dev, measured_peaks(), small=True, group=args.decode_group)}),
+              flush=True)
         return 0
     return run_ours(args)
 
