@@ -131,7 +131,7 @@ def _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask
 def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dropout_mask=None,
                keep_prob=1.0, alibi=None, alibi_slopes=None, prev_block_num=BAND_UNBOUNDED,
                next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None, need_lse=True, tri_block=0,
-               dropout_seed=None, dropout_offset=0, mask_tiles=None):
+               dropout_seed=None, dropout_offset=0, mask_tiles=None, out=None, lse_out=None):
     """Forward primitive: returns (output [B,N,S_q,D] in q's dtype, lse [B,N,S_q] fp32 or None).
 
     ``mask_tiles`` (optional, from ``mask_tile_classes(attn_mask)``) lets the kernel skip reading the 128x128 tiles
@@ -139,10 +139,19 @@ def fa_forward(q, k, v, attn_mask=None, *, mask_tile128=False, causal=False, dro
 
     Dropout comes either as a tensor (``dropout_mask`` + ``keep_prob``) or is decided inside the kernel from
     ``dropout_seed`` / ``dropout_offset`` + ``keep_prob`` (no [B,N,S_q,S_k] tensor exists then; the backward must
-    be given the same three values)."""
+    be given the same three values).
+
+    ``out`` / ``lse_out``: tensors to write into instead of new ones (a caller that steps in a loop and wants no
+    allocation in it)."""
     lib = load()
-    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if need_lse else None
+    o = out if out is not None else torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    if o.shape != q.shape or o.dtype != q.dtype or not o.is_cuda:
+        raise ValueError("out must be a CUDA tensor shaped and typed like q")
+    lse = None
+    if need_lse:
+        lse = lse_out if lse_out is not None else torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
+        if tuple(lse.shape) != tuple(q.shape[:3]) or lse.dtype != torch.float32 or not lse.is_contiguous():
+            raise ValueError("lse_out must be a contiguous float32 tensor [B, N, S_q]")
     a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
                             alibi_slopes, prev_block_num, next_block_num, scale, seq_lens, tri_block=tri_block,
                             dropout_seed=dropout_seed, dropout_offset=dropout_offset, mask_tiles=mask_tiles)
@@ -156,9 +165,13 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
                 dropout_mask=None, keep_prob=1.0, alibi=None, alibi_slopes=None,
                 prev_block_num=BAND_UNBOUNDED, next_block_num=BAND_UNBOUNDED, scale=1.0, seq_lens=None,
                 grads_fp32=False, tri_block=0, deterministic=False, dropout_seed=None, dropout_offset=0,
-                kernel_events=None, mask_tiles=None):
+                kernel_events=None, mask_tiles=None, out=None, workspace=None):
     """Grad primitive: returns (dq, dk, dv), fp32 when ``grads_fp32`` (what the reference primitive
-    returns) else in q's dtype (what its bprop hands back after the cast)."""
+    returns) else in q's dtype (what its bprop hands back after the cast).
+
+    ``out`` = (dq, dk, dv) to write into and ``workspace`` = a uint8 CUDA tensor of at least
+    ``acct_fa_bwd_workspace_bytes`` bytes (see ``fa_backward_workspace_bytes``), for callers that want no allocation
+    inside their step loop."""
     lib = load()
     _require_cuda("o", o)
     _require_cuda("d_o", d_o)
@@ -167,9 +180,15 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
         d_o = d_o.contiguous()
         o = o.contiguous()
     gdt = torch.float32 if grads_fp32 else q.dtype
-    dq = torch.empty(q.shape, dtype=gdt, device=q.device)
-    dk = torch.empty(k.shape, dtype=gdt, device=q.device)
-    dv = torch.empty(v.shape, dtype=gdt, device=q.device)
+    if out is not None:
+        dq, dk, dv = out
+        for t, like in ((dq, q), (dk, k), (dv, v)):
+            if t.shape != like.shape or t.dtype != gdt or not t.is_contiguous() or not t.is_cuda:
+                raise ValueError("out must be contiguous CUDA tensors (dq, dk, dv) shaped like q, k, v in the gradient dtype")
+    else:
+        dq = torch.empty(q.shape, dtype=gdt, device=q.device)
+        dk = torch.empty(k.shape, dtype=gdt, device=q.device)
+        dv = torch.empty(v.shape, dtype=gdt, device=q.device)
     lse = lse.contiguous()
     a, keep = _fill_fa_args(q, k, v, o, lse, attn_mask, mask_tile128, causal, dropout_mask, keep_prob, alibi,
                             alibi_slopes, prev_block_num, next_block_num, scale, seq_lens,
@@ -177,7 +196,12 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
                             tri_block=tri_block, dropout_seed=dropout_seed, dropout_offset=dropout_offset,
                             mask_tiles=mask_tiles)
     nbytes = lib.acct_fa_bwd_workspace_bytes(C.byref(a))
-    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    if workspace is not None:
+        if workspace.dtype != torch.uint8 or not workspace.is_cuda or workspace.numel() < nbytes or workspace.data_ptr() % 256:
+            raise ValueError(f"workspace must be a 256-byte aligned uint8 CUDA tensor of at least {nbytes} bytes")
+        ws = workspace
+    else:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     g = FaBwdIO()
     g.d_o, g.dq, g.dk, g.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     g.workspace, g.workspace_bytes = ws.data_ptr(), nbytes
@@ -190,6 +214,15 @@ def fa_backward(q, k, v, o, lse, d_o, attn_mask=None, *, mask_tile128=False, cau
         check(lib.acct_fa_bwd(C.byref(a), C.byref(g), _stream()))
     del keep
     return dq, dk, dv
+
+
+def fa_backward_workspace_bytes(q, k, grads_fp32=False):
+    """Bytes of scratch ``fa_backward`` needs for inputs shaped like q [B,N,S_q,D] and k [B,N_kv,S_k,D]."""
+    a = FaArgs()
+    a.B, a.N, a.S_q, a.D = q.shape
+    a.S_k = k.shape[2]
+    a.flags = FLAG_GRAD_F32 if grads_fp32 else 0
+    return int(load().acct_fa_bwd_workspace_bytes(C.byref(a)))
 
 
 _causal_cache = {}     # id(tensor) -> (weak reference to that tensor, its version counter, answer)

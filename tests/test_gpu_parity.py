@@ -586,3 +586,26 @@ def test_cell_trains_at_head_dim_160(dev):
     for g, want, name in zip((qd.grad, kd.grad, vd.grad),
                              ref.sa_grad(q.numpy(), k.numpy(), v.numpy(), do.numpy(), mask.numpy(), scale=scale), ("dq", "dk", "dv")):
         _check_g(g, want, name)
+
+
+def test_caller_provided_outputs_and_workspace(dev):
+    """fa_forward / fa_backward write into tensors the caller brings (for step loops that must not allocate) and give
+    the same bits as the allocating form."""
+    ops = _ops()
+    B, N, S, D = 2, 3, 300, 64
+    q, k, v, do = (_rand((B, N, S, D), 180 + i).to(dev) for i in range(4))
+    o_ref, lse_ref = ops.fa_forward(q, k, v, causal=True, scale=0.125)
+    g_ref = ops.fa_backward(q, k, v, o_ref, lse_ref, do, causal=True, scale=0.125, deterministic=True)
+    o, lse = torch.empty_like(q), torch.empty(B, N, S, dtype=torch.float32, device=dev)
+    got = ops.fa_forward(q, k, v, causal=True, scale=0.125, out=o, lse_out=lse)
+    assert got[0] is o and got[1] is lse and torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
+    outs = tuple(torch.empty_like(t) for t in (q, k, v))
+    ws = torch.empty(ops.fa_backward_workspace_bytes(q, k) + 512, dtype=torch.uint8, device=dev)
+    ws = ws[(-ws.data_ptr()) % 256:]
+    for _ in range(2):          # the workspace is reused as it is: the call re-initialises what it needs
+        g = ops.fa_backward(q, k, v, o, lse, do, causal=True, scale=0.125, deterministic=True, out=outs, workspace=ws)
+        _status()
+        for a, b_, c in zip(g, outs, g_ref):
+            assert a is b_ and torch.equal(a, c)
+    with pytest.raises(ValueError):
+        ops.fa_backward(q, k, v, o, lse, do, workspace=ws[:1024])
