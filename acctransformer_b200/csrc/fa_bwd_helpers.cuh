@@ -7,26 +7,31 @@ namespace acct {
 
 // Keep bits of in-kernel dropout for one key row and 32 consecutive queries q0 .. q0+31 (bit e = query q0 + e).
 // The generator works on (query, 16 consecutive keys); the 32 lanes of a warp hold 32 consecutive key rows, i.e.
-// two such groups of 16.  Every lane makes the calls of two of the 32 queries for its half-warp's key group and
-// the 16-bit results are handed round by shuffles, so a warp makes 64 calls for its 32 x 32 decisions.
+// two such groups of 16.  Every lane makes the calls of two of the 32 queries (q0 + s and q0 + 16 + s, s = lane % 16)
+// for its half-warp's key group, which gives each half-warp a 32 x 16 bit matrix spread over its lanes (lane s holds
+// rows s and 16 + s, one 16-bit result each); what a lane needs is COLUMN (lane % 16) of it.  The two 16 x 16 blocks
+// are transposed in place by four butterfly rounds (one shuffle and a few logic operations each) instead of one
+// shuffle per query: a warp makes 64 calls and 4 shuffles per lane for its 32 x 32 decisions.
 // All 32 lanes must call this together.
 __device__ __forceinline__ uint32_t philox_keep_column(const ScoreMods& mods, int bh, int q0, int q_max, int kv_idx,
                                                        int lane) {
   const DropoutRng rng = {mods.drop_seed_lo, mods.drop_seed_hi, mods.drop_offset, mods.drop_threshold};
   const uint32_t key16 = static_cast<uint32_t>(kv_idx) >> 4;
-  uint32_t mine[2];
+  uint32_t w = 0;
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
-    const int q = min(q0 + 2 * (lane & 15) + u, q_max);
-    mine[u] = dropout_keep16(rng, static_cast<uint32_t>(bh), static_cast<uint32_t>(q), key16);
+    const int q = min(q0 + 16 * u + (lane & 15), q_max);
+    w |= dropout_keep16(rng, static_cast<uint32_t>(bh), static_cast<uint32_t>(q), key16) << (16 * u);
   }
-  uint32_t bits = 0;
+  // w: bit 16u + b = (query q0 + 16u + s, key 16*key16 + b).  After the rounds: bit 16u + s' of lane d = the decision
+  // of (query q0 + 16u + s', key 16*key16 + d), i.e. bit e of the result belongs to query q0 + e.
 #pragma unroll
-  for (int e = 0; e < 32; ++e) {
-    const uint32_t m16 = __shfl_sync(0xffffffffu, mine[e & 1], (lane & 16) | (e >> 1));
-    bits |= ((m16 >> (kv_idx & 15)) & 1u) << e;
+  for (int k = 3; k >= 0; --k) {
+    const uint32_t m = k == 3 ? 0x00ff00ffu : k == 2 ? 0x0f0f0f0fu : k == 1 ? 0x33333333u : 0x55555555u;
+    const uint32_t x = __shfl_xor_sync(0xffffffffu, w, 1 << k);
+    w = (lane & (1 << k)) ? ((w & ~m) | ((x & ~m) >> (1 << k))) : ((w & m) | ((x & m) << (1 << k)));
   }
-  return bits;
+  return w;
 }
 
 }  // namespace acct

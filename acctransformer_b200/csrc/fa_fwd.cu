@@ -384,7 +384,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
       tmem_wait_ld();
 
       if constexpr ((MODS & 2) != 0) if (generic && !use_mask) {
-        // alibi only: added in registers, in log2 units (no pass through tensor memory)
+        // alibi only: added in registers, in log2 units (no pass through tensor memory), two scores per instruction;
+        // positions that do not exist are only looked for in tiles that have any (`partial`)
+        const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2);
         if (mods.alibi != nullptr) {
           const float* al = sh.alibi[qt][n & 1];
 #pragma unroll
@@ -392,23 +394,33 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
               const float4 a4 = *reinterpret_cast<const float4*>(al + c * 32 + 4 * i4);
-              const float a[4] = {a4.x, a4.y, a4.z, a4.w};
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const int i = 4 * i4 + u;
-                const float x = fmaf(__uint_as_float(s[c][i]), p.scale_log2, a[u]);
-                s[c][i] = __float_as_uint(col_base + c * 32 + i >= bound ? kNegInf : x);
-              }
+              float x0, x1, x2, x3;
+              f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c][4 * i4]), __uint_as_float(s[c][4 * i4 + 1])), sc2, f2_pack(a4.x, a4.y)), x0, x1);
+              f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c][4 * i4 + 2]), __uint_as_float(s[c][4 * i4 + 3])), sc2, f2_pack(a4.z, a4.w)), x2, x3);
+              s[c][4 * i4] = __float_as_uint(x0); s[c][4 * i4 + 1] = __float_as_uint(x1);
+              s[c][4 * i4 + 2] = __float_as_uint(x2); s[c][4 * i4 + 3] = __float_as_uint(x3);
             }
         } else {
+          // bias = slope * key position = slope * (first key of the tile) + slope * (offset inside the tile): the second
+          // factor is a compile-time constant, so no integer-to-float conversion competes with the exponentials
+          const float base = slope_l2 * static_cast<float>(col_base);
+          const uint64_t base2 = f2_pack(base, base), slope2 = f2_pack(slope_l2, slope_l2);
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float x = fmaf(__uint_as_float(s[c][i]), p.scale_log2,
-                                   slope_l2 * static_cast<float>(col_base + c * 32 + i));
-              s[c][i] = __float_as_uint(col_base + c * 32 + i >= bound ? kNegInf : x);
+            for (int i = 0; i < 32; i += 2) {
+              const uint64_t bias2 = f2_fma(slope2, f2_pack(static_cast<float>(c * 32 + i), static_cast<float>(c * 32 + i + 1)), base2);
+              float x0, x1;
+              f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, bias2), x0, x1);
+              s[c][i] = __float_as_uint(x0); s[c][i + 1] = __float_as_uint(x1);
             }
+        }
+        if (partial) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              s[c][i] = (col_base + c * 32 + i >= bound) ? __float_as_uint(kNegInf) : s[c][i];
         }
       }
       if (!generic && partial) {
