@@ -14,7 +14,7 @@
 // pass over tensor memory.  O leaves through shared memory (the CTA's own Q tile, dead by then)
 // and a TMA store.
 //
-// CTAs are numbered so that, inside a group of kUnitGroup (batch, head) slices, the tile pairs
+// CTAs are numbered so that, inside a group of `unit_group` (batch, head) slices, the tile pairs
 // with the most K/V tiles (the latest rows under a causal mask) start first, while the slices that
 // run at the same time stay few enough for their K and V to sit in L2.
 //
@@ -37,7 +37,6 @@ namespace {
 constexpr int kFwdThreads = 384;   // warps 10 and 11 only complete the third warpgroup (register re-split)
 constexpr int kRegsSoftmax = 208, kRegsControl = 88;
 constexpr int kStages = 2;   // K/V ring depth for head_dim <= 128 (one stage above that)
-constexpr int kUnitGroup = 8;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
 struct TileRange {
@@ -100,11 +99,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
   const int lane = tid & 31;
   const ScoreMods& mods = p.mods;
 
-  // linear CTA number -> ((batch, head) slice, tile pair): groups of kUnitGroup slices, heaviest pairs first
+  // linear CTA number -> ((batch, head) slice, tile pair): groups of unit_group slices, heaviest pairs first
   const int n_pairs = (p.S_q + NQ * kTile - 1) / (NQ * kTile);
   const int n_units = p.B * p.N;
   int bh, pair;
   {
+    const int kUnitGroup = p.unit_group;
     const int per_group = n_pairs * kUnitGroup;
     const int g = blockIdx.x / per_group;
     const int within = blockIdx.x % per_group;
@@ -728,6 +728,25 @@ cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(nq + 2 * stages) * (dpad / 64) * 16384 + 1024;
   const int n_pairs = (p.S_q + nq * kTile - 1) / (nq * kTile);
   dim3 grid(static_cast<unsigned>(n_pairs) * static_cast<unsigned>(p.B * p.N));
+  // Slices per group: 8 (measured best from 4 096 keys up: larger groups lose more in L2 than the order gains).  Short
+  // sequences have so few tile pairs per slice that two groups of 8 do not even fill the SMs once; heaviest-first
+  // then balances nothing, and the group is widened until it gives every SM two thread blocks (K and V of a group,
+  // what its thread blocks share through L2, stay small at such lengths; bounded by 48 MB all the same).
+  FwdParams pp = p;
+  {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    long long group = 8;
+    if (16ll * n_pairs <= sms) {
+      const long long unit_bytes = 4ll * p.S_k * p.D;                    // K and V of one slice, 16-bit
+      const long long fit = (48ll << 20) / (unit_bytes > 0 ? unit_bytes : 1);
+      group = (2ll * sms + n_pairs - 1) / n_pairs;
+      if (group > fit) group = fit;
+      if (group < 8) group = 8;
+      if (group > 256) group = 256;
+    }
+    pp.unit_group = static_cast<int>(group);
+  }
   int mods = (p.mods.mask_kind != 0 ? 1 : 0) | ((p.mods.alibi != nullptr || p.mods.alibi_slopes != nullptr) ? 2 : 0);
   const int drop = p.mods.drop_philox != 0 ? 1 : (p.mods.drop != nullptr ? 2 : 0);
   // head_dim 128 has every combination; the other two widths have "no mask, no alibi" and "both may be present"
@@ -747,7 +766,7 @@ cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
 #undef ACCT_FWD_DROP
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  kern<<<grid, kFwdThreads, smem, stream>>>(p);
+  kern<<<grid, kFwdThreads, smem, stream>>>(pp);
   return cudaGetLastError();
 }
 

@@ -36,6 +36,7 @@ struct alignas(64) FwdParams {
   int64_t o_stride_b, o_stride_h, o_stride_s;
   int B, N, S_q, S_k, D;
   int kv_group;                     // query heads per key/value head (1 unless grouped-query attention)
+  int unit_group;                   // (batch, head) slices whose thread blocks are interleaved, heaviest tile pairs first
   float scale_log2;                 // scale * log2(e)
   ScoreMods mods;
   unsigned int* status;
