@@ -201,7 +201,8 @@ __device__ __forceinline__ int next_item(uint64_t* item_full, uint64_t* item_emp
 }  // namespace
 
 // MASKED = a mask tensor or TriangleAttention row groups may be present: tiles that need them get a pass over S^T
-// in tensor memory before the common code.  DROP = 0 no dropout, 1 in-kernel generator, 2 dropout mask tensor.  The
+// in tensor memory before the common code.  DROP = 0 no dropout, 1 in-kernel generator, 2 dropout mask tensor of any
+// type, 3 uint8 {0,1} mask tensor read as keep bits (4-byte aligned, S_k a multiple of 4).  The
 // plain instantiation carries none of that code, so its register allocation is not disturbed by it.
 template <int DPAD, bool BF16, bool MASKED, int DROP>
 __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_constant__ BwdParams p) {
@@ -599,11 +600,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
           if constexpr (DROP == 2)
             load_col32_raw(mods.drop, mods.drop_dtype, static_cast<int64_t>(bh) * p.S_q, q_base + c * 32, p.S_q - 1, p.S_k,
                            min(kv_idx, p.S_k - 1), draw);
+          uint32_t raw8[8];        // uint8 mask as keep bits: eight words per lane, likewise in flight
+          if constexpr (DROP == 3)
+            u8_keep_load(mods.drop, static_cast<int64_t>(bh) * p.S_q, q_base + c * 32, p.S_q - 1, p.S_k, kv_idx - lane, lane, raw8);
           if (diag) p_fast<true>(s[cc], lse2 + c * 32, p.scale_log2, tile_bias, kv_idx, q_base + c * 32, pr[cc]);
           else p_fast<false>(s[cc], lse2 + c * 32, p.scale_log2, tile_bias, kv_idx, q_base + c * 32, pr[cc]);
           uint32_t pk[16];
-          if constexpr (DROP == 1) {
-            keep_bits[cc] = philox_keep_column(mods, bh, q_base + c * 32, p.S_q - 1, kv_idx, lane);
+          if constexpr (DROP == 1 || DROP == 3) {
+            if constexpr (DROP == 1) keep_bits[cc] = philox_keep_column(mods, bh, q_base + c * 32, p.S_q - 1, kv_idx, lane);
+            else keep_bits[cc] = u8_keep_bits(raw8, lane);
 #pragma unroll
             for (int e = 0; e < 16; ++e)   // (explicit roundings: both dropout forms must give the same bits)
               pk[e] = pack2<BF16>(__fmul_rn(pr[cc][2 * e], ((keep_bits[cc] >> (2 * e)) & 1u) ? mods.drop_scale : 0.f),
@@ -668,7 +673,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
               for (int u = 0; u < 4; ++u) {
                 const int e = 4 * e4 + u;
                 float f;
-                if constexpr (DROP == 1) f = ((keep_bits[cc] >> e) & 1u) ? mods.drop_scale : 0.f;
+                if constexpr (DROP == 1 || DROP == 3) f = ((keep_bits[cc] >> e) & 1u) ? mods.drop_scale : 0.f;
                 else f = __fmul_rn(col_value(draw[e >> 1], mods.drop_dtype, e & 1), mods.drop_scale);
                 d[u] = __fmul_rn(pr[cc][e], __fmaf_rn(__uint_as_float(dp[cc][e]), f, -dl[u]));
               }
@@ -834,16 +839,18 @@ cudaError_t launch_fa_bwd(const BwdParams& p, bool bf16, cudaStream_t stream) {
   dim3 grid(static_cast<unsigned>(items < sms ? items : sms));
   // (row groups of a multiple of 128 rows never cut a tile: the tile ranges alone take care of them)
   const bool masked = p.mods.mask_kind != 0 || (p.mods.tri_block > 0 && p.mods.tri_block % kTile != 0);
-  const int drop = p.mods.drop_philox != 0 ? 1 : (p.mods.drop != nullptr ? 2 : 0);
+  const bool drop_u8_bits = p.mods.drop != nullptr && p.mods.drop_dtype == 2 /*U8*/ && p.S_k % 4 == 0 &&
+                            (reinterpret_cast<uintptr_t>(p.mods.drop) & 3u) == 0;
+  const int drop = p.mods.drop_philox != 0 ? 1 : (p.mods.drop != nullptr ? (drop_u8_bits ? 3 : 2) : 0);
   void (*kern)(const BwdParams) = nullptr;
-#define ACCT_BWD_PICK(DP, BF)                                                                          \
-  (masked ? (drop == 0 ? fa_bwd_kernel<DP, BF, true, 0> : drop == 1 ? fa_bwd_kernel<DP, BF, true, 1>   \
-                                                                    : fa_bwd_kernel<DP, BF, true, 2>)  \
-          : (drop == 0 ? fa_bwd_kernel<DP, BF, false, 0> : drop == 1 ? fa_bwd_kernel<DP, BF, false, 1> \
-                                                                     : fa_bwd_kernel<DP, BF, false, 2>))
+#define ACCT_BWD_DROP(DP, BF, MK)                                                                      \
+  (drop == 0 ? fa_bwd_kernel<DP, BF, MK, 0> : drop == 1 ? fa_bwd_kernel<DP, BF, MK, 1>                 \
+   : drop == 2 ? fa_bwd_kernel<DP, BF, MK, 2> : fa_bwd_kernel<DP, BF, MK, 3>)
+#define ACCT_BWD_PICK(DP, BF) (masked ? ACCT_BWD_DROP(DP, BF, true) : ACCT_BWD_DROP(DP, BF, false))
   if (dpad == 64) kern = bf16 ? ACCT_BWD_PICK(64, true) : ACCT_BWD_PICK(64, false);
   else kern = bf16 ? ACCT_BWD_PICK(128, true) : ACCT_BWD_PICK(128, false);
 #undef ACCT_BWD_PICK
+#undef ACCT_BWD_DROP
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   kern<<<grid, kBwdThreads, smem, stream>>>(p);

@@ -34,4 +34,35 @@ __device__ __forceinline__ uint32_t philox_keep_column(const ScoreMods& mods, in
   return w;
 }
 
+// The same 32 keep bits (bit e = query q0 + e keeps this lane's key) read from a uint8 {0,1} dropout mask
+// [units, S_q, S_k]: a lane would otherwise make 32 single-byte loads down a column of the mask, twice per tile.
+// Instead lane L loads, for 8 queries q0 + 4i + L/8, the FOUR bytes of keys 4 (L%8) .. +3 of the warp's 32 keys (a
+// warp instruction then reads 32 contiguous bytes of each of 4 mask rows), squeezes each word into a nibble, and the
+// nibbles travel to the lanes that own the keys by 4 shuffles.  Needs S_k % 4 == 0 and a 4-byte aligned mask;
+// addresses are clamped into the row, so keys past S_k get bits of other keys (their P is 0 anyway).
+// All 32 lanes must call this together.
+// Split in two so that the loads can be in flight under other work: u8_keep_load issues them, u8_keep_bits turns
+// the eight words into this lane's 32 bits.
+__device__ __forceinline__ void u8_keep_load(const void* drop, int64_t unit_row0, int q0, int q_max, int S_k, int kv_warp0,
+                                             int lane, uint32_t (&raw)[8]) {
+  const uint8_t* base = reinterpret_cast<const uint8_t*>(drop) + min(kv_warp0 + 4 * (lane & 7), S_k - 4);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int q = min(q0 + 4 * i + (lane >> 3), q_max);
+    raw[i] = *reinterpret_cast<const uint32_t*>(base + (unit_row0 + q) * S_k);
+  }
+}
+__device__ __forceinline__ uint32_t u8_keep_bits(const uint32_t (&raw)[8], int lane) {
+  uint32_t pw = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) pw |= ((((raw[i] & 0x01010101u) * 0x01020408u) >> 24) & 0xfu) << (4 * i);
+  uint32_t bits = 0;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const uint32_t x = __shfl_sync(0xffffffffu, pw, g * 8 + (lane >> 2));
+    bits |= ((x >> (lane & 3)) & 0x11111111u) << g;
+  }
+  return bits;
+}
+
 }  // namespace acct

@@ -75,7 +75,7 @@ struct FwdShared {
 }  // namespace
 
 // MODS: bit 0 = a mask tensor may be present, bit 1 = alibi may be present.  DROP: 0 no dropout, 1 in-kernel
-// generator, 2 dropout mask tensor.  Every instantiation carries only the code of what it may meet: code that is
+// generator, 2 dropout mask tensor of any type, 3 uint8 {0,1} mask tensor with 16-byte aligned rows read as byte masks.  Every instantiation carries only the code of what it may meet: code that is
 // compiled in but never run still costs the common path of every tile (register allocation, spills).
 template <int DPAD, bool BF16, int MODS, int DROP>
 __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_constant__ FwdParams p) {
@@ -440,15 +440,28 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fa_fwd_kernel(const __grid_con
         if constexpr (DROP != 0) {
           dropped = true;
           const int col0 = col_base + c * 32;
-          if constexpr (DROP == 1) {
-            // the mask is computed, not loaded: two generator calls give this row's 32 keep decisions of the chunk
-            // as byte masks, which are widened to 16-bit lane masks and ANDed onto the packed, scaled probabilities
-            // (a dropped probability becomes +0, as p * 0 would)
-            const DropoutRng rng = {mods.drop_seed_lo, mods.drop_seed_hi, mods.drop_offset, mods.drop_threshold};
-            const uint32_t q_u = static_cast<uint32_t>(min(q_row, p.S_q - 1)), k16 = static_cast<uint32_t>(col0) >> 4;
+          if constexpr (DROP == 1 || DROP == 3) {
+            // DROP 1: the mask is computed, not loaded: two generator calls give this row's 32 keep decisions of the
+            // chunk as byte masks.  DROP 3: a uint8 {0,1} mask tensor (16-byte aligned rows): the row's 32 bytes come
+            // with two 128-bit loads and become byte masks by one multiplication per word (addresses clamped into the
+            // row: keys past S_k get other keys' bytes, their P is 0 anyway).  Either way the byte masks are widened
+            // to 16-bit lane masks and ANDed onto the packed, scaled probabilities (a dropped probability becomes +0,
+            // as p * 0 would).
             uint32_t km[8];
-            dropout_keep16_bytes(rng, static_cast<uint32_t>(bh), q_u, k16, *reinterpret_cast<uint32_t(*)[4]>(&km[0]));
-            dropout_keep16_bytes(rng, static_cast<uint32_t>(bh), q_u, k16 + 1, *reinterpret_cast<uint32_t(*)[4]>(&km[4]));
+            if constexpr (DROP == 1) {
+              const DropoutRng rng = {mods.drop_seed_lo, mods.drop_seed_hi, mods.drop_offset, mods.drop_threshold};
+              const uint32_t q_u = static_cast<uint32_t>(min(q_row, p.S_q - 1)), k16 = static_cast<uint32_t>(col0) >> 4;
+              dropout_keep16_bytes(rng, static_cast<uint32_t>(bh), q_u, k16, *reinterpret_cast<uint32_t(*)[4]>(&km[0]));
+              dropout_keep16_bytes(rng, static_cast<uint32_t>(bh), q_u, k16 + 1, *reinterpret_cast<uint32_t(*)[4]>(&km[4]));
+            } else {
+              const uint8_t* row = reinterpret_cast<const uint8_t*>(mods.drop) + drop_row;
+              const uint4 u0 = *reinterpret_cast<const uint4*>(row + min(col0, p.S_k - 16));
+              const uint4 u1 = *reinterpret_cast<const uint4*>(row + min(col0 + 16, p.S_k - 16));
+              km[0] = (u0.x & 0x01010101u) * 255u; km[1] = (u0.y & 0x01010101u) * 255u;
+              km[2] = (u0.z & 0x01010101u) * 255u; km[3] = (u0.w & 0x01010101u) * 255u;
+              km[4] = (u1.x & 0x01010101u) * 255u; km[5] = (u1.y & 0x01010101u) * 255u;
+              km[6] = (u1.z & 0x01010101u) * 255u; km[7] = (u1.w & 0x01010101u) * 255u;
+            }
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               float x0, x1;
@@ -748,12 +761,15 @@ cudaError_t launch_fa_fwd(const FwdParams& p, bool bf16, cudaStream_t stream) {
     pp.unit_group = static_cast<int>(group);
   }
   int mods = (p.mods.mask_kind != 0 ? 1 : 0) | ((p.mods.alibi != nullptr || p.mods.alibi_slopes != nullptr) ? 2 : 0);
-  const int drop = p.mods.drop_philox != 0 ? 1 : (p.mods.drop != nullptr ? 2 : 0);
+  const bool drop_u8 = p.mods.drop != nullptr && p.mods.drop_dtype == 2 /*U8*/ && p.S_k % 16 == 0 &&
+                       (reinterpret_cast<uintptr_t>(p.mods.drop) & 15u) == 0;
+  const int drop = p.mods.drop_philox != 0 ? 1 : (p.mods.drop != nullptr ? (drop_u8 ? 3 : 2) : 0);
   // head_dim 128 has every combination; the other two widths have "no mask, no alibi" and "both may be present"
   if (dpad != 128 && mods != 0) mods = 3;
   void (*kern)(const FwdParams) = nullptr;
-#define ACCT_FWD_DROP(DP, BF, M) \
-  (drop == 0 ? fa_fwd_kernel<DP, BF, M, 0> : drop == 1 ? fa_fwd_kernel<DP, BF, M, 1> : fa_fwd_kernel<DP, BF, M, 2>)
+#define ACCT_FWD_DROP(DP, BF, M)                                                                           \
+  (drop == 0 ? fa_fwd_kernel<DP, BF, M, 0> : drop == 1 ? fa_fwd_kernel<DP, BF, M, 1>                       \
+   : drop == 2 ? fa_fwd_kernel<DP, BF, M, 2> : fa_fwd_kernel<DP, BF, M, 3>)
 #define ACCT_FWD_BF(DP, M) (bf16 ? ACCT_FWD_DROP(DP, true, M) : ACCT_FWD_DROP(DP, false, M))
   if (dpad == 128) {
     kern = mods == 0 ? ACCT_FWD_BF(128, 0) : mods == 1 ? ACCT_FWD_BF(128, 1) : mods == 2 ? ACCT_FWD_BF(128, 2) : ACCT_FWD_BF(128, 3);
