@@ -54,7 +54,7 @@ struct BwdShared {
   uint64_t kv_empty;             // MMA -> producer: every product of the work item has finished, K and V may be replaced
   uint64_t acc_free;             // compute -> MMA: dK and dV of the work item have been read out of tensor memory
   uint64_t q_full[kStages];
-  uint64_t q_empty[kStages];     // MMA -> producer: the dK product reading this Q stage has finished
+  uint64_t q_empty[kStages];     // drain (on dq_full) -> producer: the products reading this Q stage have finished
   uint64_t do_full;
   uint64_t do_empty;             // MMA -> producer: the dV product reading dO has finished
   uint64_t st_full, dp_full;     // MMA -> compute: S^T / dP^T are in tensor memory
@@ -394,8 +394,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
 #pragma unroll
             for (int kk = 0; kk < kTile / 16; ++kk)
               umma_ss_lohi(tmem + kColDP, mDS + kk * 128u, mn_hi, mK + kk * 128u, mn_hi, idesc_dq, kk > 0);
-            umma_commit(&sh.dq_full);
-            umma_commit(&sh.q_empty[st]);
+            umma_commit(&sh.dq_full);     // (the drain passes it on to the producer as q_empty[st]: one commit less here)
           }
           umma_commit(&sh.kv_empty);
           g0 += n_iter;
@@ -425,6 +424,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       const int bh = b * p.N + h;
       mbar_wait(&sh.dq_full, (g0 + n) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
+      // every product of this step has finished: its Q stage may be refilled (told to the producer from here, so that
+      // the MMA-issuing thread, which issues nothing while it commits, has one commit less per step)
+      if (elected) mbar_arrive(&sh.q_empty[(g0 + n) % kStages]);
       uint32_t dq[kChunks][32];
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) tmem_ld32(t_dq + c * 32, dq[c]);
