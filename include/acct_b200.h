@@ -207,8 +207,9 @@ ACCT_API uint8_t* acct_mask_tiles_scratch(size_t bytes);
 /* Forward: writes o and (if non-NULL) lse. */
 ACCT_API int acct_fa_fwd(const acct_fa_args* a, void* stream);
 
-/* Bytes of scratch acct_fa_bwd needs for `a` (row sums Dl, turn counters and, unless ACCT_FLAG_GRAD_F32 is set in
- * a->flags, an fp32 dQ accumulator).
+/* Bytes of scratch acct_fa_bwd needs for `a` (row sums Dl, turn counters, the work counter of the kernel's persistent
+ * thread blocks and, unless ACCT_FLAG_GRAD_F32 is set in a->flags, an fp32 dQ accumulator).  The call initialises
+ * what it needs itself: the same workspace can be handed to call after call as it is.
  * The reference declares its fp32 gradient outputs "atomic add" buffers that the runtime zero-fills
  * (flash_attention_bwd.py:55-57); here the library zero-fills its own accumulator on `stream`. */
 ACCT_API size_t acct_fa_bwd_workspace_bytes(const acct_fa_args* a);
