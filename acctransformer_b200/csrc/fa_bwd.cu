@@ -1,8 +1,10 @@
 // FlashAttention-2 backward for sm_100a.
 //
-// One CTA owns one 128-row K/V tile of one (batch, head) slice and walks the Q tiles that touch
+// A work item is one 128-row K/V tile of one (batch, head) slice together with the Q tiles that touch
 // it; dK and dV accumulate in tensor memory for the whole walk, dQ tiles are added into an fp32
-// global accumulator by TMA reduce.  Scores are recomputed TRANSPOSED (rows = keys, columns =
+// global accumulator by TMA reduce.  The kernel is persistent: one CTA per SM takes work items from a
+// global counter, heaviest tiles first (decode_item), and requests the next item's K and V while the
+// current item's dK / dV are being written out.  Scores are recomputed TRANSPOSED (rows = keys, columns =
 // queries) so that P^T and dS^T come out in the layout the dV / dK products need:
 //   S^T  = K_j Q_i^T          (tcgen05, both operands K-major from shared memory)
 //   dP^T = V_j dO_i^T
