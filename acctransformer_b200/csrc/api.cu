@@ -556,13 +556,23 @@ int acct_infer_decode(const acct_decode_args* a, void* stream) {
   DeviceInfo info;
   if ((rc = device_info(&info))) return rc;
   if (splits == 0) {
-    // enough CTAs for ~4 waves of 2 resident CTAs per SM, but never splits shorter than 256 keys
+    // Automatic choice.  Sequence lengths differ between the sequences of a batch (1 024 .. 16 384 keys in the
+    // benchmark configuration), and a (sequence, cache head) slice cut into few parts leaves the SMs unevenly
+    // loaded at the end.  Measured on B200 at head_dim 128 with 32 .. 1 024 slices: one query head per cache head is
+    // within 2 % of its best with 8 parts per slice for 512 slices or more, rising to 16 parts for 128 slices or
+    // fewer (2 parts, the earlier choice at 1 024 slices, was 7-18 % below); grouped heads, whose parts each carry
+    // the partial results of the whole group, do best with 8 to 12 parts.  Never parts shorter than 512 keys, and
+    // never more parts than the caller's workspace holds.
     const int64_t units = static_cast<int64_t>(a->B) * n_kv;
-    int64_t want = (static_cast<int64_t>(info.sm_count) * 8 + units - 1) / units;
-    int64_t cap = (a->S_max + 255) / 256;
-    splits = static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
-    if (splits > 64) splits = 64;
-    if (splits < 1) splits = 1;
+    const int64_t per_sm = group > 1 ? 4 : 24, most = group > 1 ? 12 : 16;
+    int64_t want = (static_cast<int64_t>(info.sm_count) * per_sm + units - 1) / units;
+    if (want < 8) want = 8;
+    if (want > most) want = most;
+    const int64_t cap = (a->S_max + 511) / 512;
+    if (want > cap) want = cap;
+    const int64_t fit = static_cast<int64_t>(a->workspace_bytes / (static_cast<size_t>(a->B) * a->N * (static_cast<size_t>(a->D) + 2) * 4));
+    if (want > fit) want = fit;
+    splits = static_cast<int>(want < 1 ? 1 : want);
   }
   const size_t need = static_cast<size_t>(a->B) * a->N * splits * (static_cast<size_t>(a->D) + 2) * 4;
   if (a->workspace == nullptr || a->workspace_bytes < need)

@@ -258,7 +258,8 @@ typedef struct acct_decode_args {
   const int32_t* seq_lens;  /* device [B] int32, each in [1, S_max]; NULL = S_max everywhere */
   void* y;                  /* device [B,N,1,D] packed */
   float scale;
-  int32_t num_splits;       /* 0 = choose from the device's SM count */
+  int32_t num_splits;       /* 0 = chosen from the SM count, the number of (sequence, cache head) slices and S_max:
+                               8 to 16 ranges of at least 512 keys, and no more than `workspace_bytes` holds */
   void* workspace;          /* device, >= acct_infer_decode_workspace_bytes() */
   size_t workspace_bytes;
   int32_t N_kv;             /* heads of the caches: 0 or N, or a divisor of N (grouped-query attention: the query heads
@@ -283,7 +284,9 @@ ACCT_API int acct_infer_decode(const acct_decode_args* a, void* stream);
  * Same arguments and results as acct_infer_decode, except that `workspace` / `workspace_bytes` are ignored: the
  * partial results go to an array of ACCT_DECODE_STATIC_SCRATCH_BYTES built into the library, which every GPU that
  * loads the library holds until the process exits.  Returns ACCT_ERR_WORKSPACE if the call needs more than that
- * (B*N*splits*(D+2)*4 bytes).  All calls on a GPU share the array: calls that overlap on the GPU race, so keep
+ * (B*N*splits*(D+2)*4 bytes); with num_splits = 0 the split count is lowered to what the array holds instead (the
+ * result then differs in rounding from a call that was given room for more ranges).  All calls on a GPU share the
+ * array: calls that overlap on the GPU race, so keep
  * them ordered on one stream; nothing in the array needs clearing between calls.  The first call on each GPU
  * resolves the array's device address and should come before any stream capture.  Calls no cudaMalloc/cudaFree. */
 #define ACCT_DECODE_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)

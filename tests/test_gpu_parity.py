@@ -388,6 +388,30 @@ def test_seq_lens_zero_and_full(dev):
     _check_o(y[1:], y_ref)
 
 
+def test_band_that_leaves_q_tiles_without_keys(dev):
+    # S_q > S_k + prev_block_num * 128: the trailing Q tiles lie outside the band of every K/V tile.  Their rows are
+    # defined as zeros (output and dQ; the reference leaves them undefined), and no K/V tile ever adds into their dQ,
+    # so the backward cannot leave the 16-bit conversion of dQ to "the last tile that adds".
+    ops = _ops()
+    B, N, Sq, Sk, D = 1, 2, 640, 128, 64
+    q, do = _rand((B, N, Sq, D), 140), _rand((B, N, Sq, D), 143)
+    k, v = _rand((B, N, Sk, D), 141), _rand((B, N, Sk, D), 142)
+    kw = dict(prev_block_num=1, scale=0.125)
+    o, lse = ops.fa_forward(q.to(dev), k.to(dev), v.to(dev), **kw)
+    dq = torch.full((B, N, Sq, D), 7.0, dtype=torch.float16, device=dev)        # stale contents must not survive
+    dk, dv = torch.empty(B, N, Sk, D, dtype=torch.float16, device=dev), torch.empty(B, N, Sk, D, dtype=torch.float16, device=dev)
+    ops.fa_backward(q.to(dev), k.to(dev), v.to(dev), o, lse, do.to(dev), out=(dq, dk, dv), **kw)
+    _status()
+    seen = 256                                                                   # rows of Q tiles 0 and 1
+    assert float(o[:, :, seen:].float().abs().max()) == 0.0
+    assert float(dq[:, :, seen:].float().abs().max()) == 0.0
+    o_ref, _ = ref.sa_fwd(q.numpy()[:, :, :seen], k.numpy(), v.numpy(), **kw)
+    _check_o(o[:, :, :seen], o_ref)
+    gq, gk, gv = ref.sa_grad(q.numpy()[:, :, :seen], k.numpy(), v.numpy(), do.numpy()[:, :, :seen], **kw)
+    for a, r, n in ((dq[:, :, :seen], gq, "dq"), (dk, gk, "dk"), (dv, gv, "dv")):
+        _check_g(a, r, n)
+
+
 @pytest.mark.parametrize("kw", [dict(causal=True), dict(), dict(prev_block_num=2, next_block_num=1), dict(tri_block=384)])
 def test_deterministic_backward_is_bit_reproducible(dev, kw):
     # the reference requires run-to-run equality of its gradients (tests/train/flash_attention/st/test_sharding.py:91-115)
