@@ -89,3 +89,34 @@ def test_static_scratch_decode_refuses_what_does_not_fit():
     assert rc == 6       # ACCT_ERR_WORKSPACE
     msg = lib.acct_last_error().decode()
     assert "built-in scratch" in msg and str(_lib.DECODE_STATIC_SCRATCH_BYTES) in msg
+
+
+def test_static_scratch_decode_lowers_an_automatic_split_count_to_what_fits():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from acctransformer_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # 4 096 (sequence, head) slices of up to 2 048 keys: the automatic choice would be 4 key ranges (17 MB of partial
+    # results); the 8 MiB array holds 3, and the call must use 3 rather than fail
+    B, N, S, D = 64, 64, 2048, 128
+    assert B * N * 4 * (D + 2) * 4 > _lib.DECODE_STATIC_SCRATCH_BYTES >= B * N * 3 * (D + 2) * 4
+    g = torch.Generator(device=dev).manual_seed(11)
+    q = torch.randn(B, N, 1, D, device=dev, generator=g).to(torch.float16)
+    kc = torch.randn(B, N, S, D, device=dev, generator=g, dtype=torch.float16)
+    lens = torch.randint(1, S + 1, (B,), device=dev, generator=g, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(D)
+    y_auto, y_three = torch.zeros_like(q), torch.zeros_like(q)
+    _lib.check(lib.acct_infer_decode_static(C.byref(_args(_lib, q, kc, kc, lens, y_auto, scale, 0)), stream))
+    probe = _args(_lib, q, kc, kc, lens, y_three, scale, 3)
+    ws = torch.empty(lib.acct_infer_decode_workspace_bytes(C.byref(probe)), dtype=torch.uint8, device=dev)
+    _lib.check(lib.acct_infer_decode(C.byref(_args(_lib, q, kc, kc, lens, y_three, scale, 3, ws)), stream))
+    torch.cuda.synchronize()
+    _lib.device_status()
+    assert torch.equal(y_auto, y_three)
+    for b in (0, B - 1):           # first and last sequence against the CPU oracle
+        want = ref.decode_ref(q[b:b + 1].float().cpu().numpy(), kc[b:b + 1].float().cpu().numpy(),
+                              kc[b:b + 1].float().cpu().numpy(), lens[b:b + 1].cpu().numpy(), scale)
+        assert float((y_auto[b:b + 1].float().cpu() - torch.tensor(want)).abs().max()) <= TOL
