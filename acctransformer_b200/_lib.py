@@ -30,7 +30,7 @@ EXPORTS = [
     "acct_last_error", "acct_abi_version",
     "acct_ms_set_fa_attrs", "acct_ms_fa_fwd", "acct_ms_fa_grad", "acct_ms_infer_fa", "acct_dropout_mask",
     "acct_mask_is_causal", "acct_mask_tiles_bytes", "acct_mask_classify_tiles", "acct_mask_tiles_scratch",
-    "acct_selftest_wait_timeout", "acct_ms_fa_attrs_slot",
+    "acct_selftest_wait_timeout", "acct_ms_fa_attrs_slot", "acct_ms_fa_attrs_slot_ex",
 ] + [f"acct_ms_fa_{kind}_s{k}" for k in range(32) for kind in ("fwd", "grad")]
 
 

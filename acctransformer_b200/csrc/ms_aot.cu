@@ -31,6 +31,7 @@ struct FaAttrs {
   float keep_prob = 1.0f;
   float scale = 1.0f;   // the raw primitive does not scale (the cell pre-multiplies q and k)
   int causal = 0;
+  int optional_inputs = -1;   // which optional inputs the primitive passes (ACCT_MS_HAS_* bits); -1 = tell by shape
 };
 constexpr int kSlots = 32;
 FaAttrs g_attrs;                     // the process-wide default (slot -1)
@@ -81,34 +82,64 @@ bool is_shape4(int i, const int* ndims, int64_t** shapes, const char** dtypes, i
          dtype_code(dtypes[i]) == dt;
 }
 
-// Classifies params[first .. last) as attn_mask / dropout_mask / alibi_mask; false on an input it cannot place.
+// One optional input, known (by declaration) or found (by shape) to be the attn_mask; false if its shape or type
+// would make the kernels read out of bounds.
+bool place_attn_mask(acct_fa_args& a, int i, void** params, const int* ndims, int64_t** shapes, const char** dtypes) {
+  const int r = ndims[i];
+  const int64_t* s = shapes[i];
+  const int dt = dtype_code(dtypes[i]);
+  if ((r != 3 && r != 2) || a.attn_mask != nullptr || dt < 0 || dt == ACCT_F32) return false;
+  const bool tile = (r == 3 && s[0] == 1 && s[1] == 128 && s[2] == 128 && !(a.S_q == 128 && a.S_k == 128)) ||
+                    (r == 2 && s[0] == 128 && s[1] == 128);
+  if (!tile) {   // a full mask is [1 or B, S_q, S_k] (or [S_q, S_k]): anything else would be read out of bounds
+    const int64_t mq = r == 3 ? s[1] : s[0], mk = r == 3 ? s[2] : s[1];
+    if (mq != a.S_q || mk != a.S_k) return false;
+    if (r == 3 && s[0] != 1 && s[0] != a.B) return false;
+  }
+  a.attn_mask = params[i];
+  a.mask_dtype = dt;
+  a.mask_kind = tile ? ACCT_MASK_TILE128 : ACCT_MASK_FULL;   // attention.py:279-285
+  a.mask_batch = (tile || r == 2) ? 1 : static_cast<int32_t>(s[0]);
+  return true;
+}
+bool place_alibi(acct_fa_args& a, int i, void** params, const int* ndims, int64_t** shapes, const char** dtypes) {
+  const int64_t* s = shapes[i];
+  if (ndims[i] != 4 || s[0] != a.B || s[1] != a.N || s[2] != 1 || s[3] != a.S_k) return false;
+  if (a.alibi != nullptr || dtype_code(dtypes[i]) != a.dtype) return false;
+  a.alibi = params[i];
+  return true;
+}
+bool place_dropout(acct_fa_args& a, int i, void** params, const int* ndims, int64_t** shapes, const char** dtypes) {
+  const int64_t* s = shapes[i];
+  const int dt = dtype_code(dtypes[i]);
+  if (ndims[i] != 4 || s[0] != a.B || s[1] != a.N || s[2] != a.S_q || s[3] != a.S_k) return false;
+  if (a.dropout_mask != nullptr || dt < 0 || dt == ACCT_F32) return false;
+  a.dropout_mask = params[i];
+  a.dropout_dtype = dt;
+  return true;
+}
+
+// Places params[first .. last) as attn_mask / dropout_mask / alibi_mask; false on an input it cannot place.
+// `declared` >= 0 (ACCT_MS_HAS_* bits, from the primitive's attribute slot): exactly those inputs, in the reference's
+// order (flash_attention_impl.py:146-152), each checked against the shape its name demands.  `declared` < 0: by rank
+// and shape, which cannot tell an alibi_mask from a dropout_mask when S_q = 1 (taken for the dropout mask).
 bool fill_optionals(acct_fa_args& a, int first, int last, void** params, const int* ndims, int64_t** shapes,
-                    const char** dtypes) {
+                    const char** dtypes, int declared) {
+  if (declared >= 0) {
+    int i = first;
+    if (declared & ACCT_MS_HAS_ATTN_MASK) { if (i >= last || !place_attn_mask(a, i, params, ndims, shapes, dtypes)) return false; ++i; }
+    if (declared & ACCT_MS_HAS_DROPOUT_MASK) { if (i >= last || !place_dropout(a, i, params, ndims, shapes, dtypes)) return false; ++i; }
+    if (declared & ACCT_MS_HAS_ALIBI_MASK) { if (i >= last || !place_alibi(a, i, params, ndims, shapes, dtypes)) return false; ++i; }
+    return i == last;
+  }
   for (int i = first; i < last; ++i) {
     const int r = ndims[i];
     const int64_t* s = shapes[i];
-    const int dt = dtype_code(dtypes[i]);
     if (r == 3 || r == 2) {
-      if (a.attn_mask != nullptr || dt < 0 || dt == ACCT_F32) return false;
-      const bool tile = (r == 3 && s[0] == 1 && s[1] == 128 && s[2] == 128 && !(a.S_q == 128 && a.S_k == 128)) ||
-                        (r == 2 && s[0] == 128 && s[1] == 128);
-      if (!tile) {   // a full mask is [1 or B, S_q, S_k] (or [S_q, S_k]): anything else would be read out of bounds
-        const int64_t mq = r == 3 ? s[1] : s[0], mk = r == 3 ? s[2] : s[1];
-        if (mq != a.S_q || mk != a.S_k) return false;
-        if (r == 3 && s[0] != 1 && s[0] != a.B) return false;
-      }
-      a.attn_mask = params[i];
-      a.mask_dtype = dt;
-      a.mask_kind = tile ? ACCT_MASK_TILE128 : ACCT_MASK_FULL;   // attention.py:279-285
-      a.mask_batch = (tile || r == 2) ? 1 : static_cast<int32_t>(s[0]);
-    } else if (r == 4 && s[0] == a.B && s[1] == a.N && s[2] == 1 && s[3] == a.S_k && a.S_q != 1) {
-      if (a.alibi != nullptr || dt != a.dtype) return false;
-      a.alibi = params[i];
-    } else if (r == 4 && s[0] == a.B && s[1] == a.N && s[2] == a.S_q && s[3] == a.S_k) {
-      if (a.dropout_mask != nullptr || dt < 0 || dt == ACCT_F32) return false;
-      a.dropout_mask = params[i];
-      a.dropout_dtype = dt;
-    } else {
+      if (!place_attn_mask(a, i, params, ndims, shapes, dtypes)) return false;
+    } else if (r == 4 && s[2] == 1 && a.S_q != 1) {
+      if (!place_alibi(a, i, params, ndims, shapes, dtypes)) return false;
+    } else if (!place_dropout(a, i, params, ndims, shapes, dtypes)) {
       return false;
     }
   }
@@ -126,7 +157,8 @@ int summarise_mask(acct_fa_args& a, void* stream) {
   return rc;
 }
 
-void apply_attrs(acct_fa_args& a, int slot) {
+// copies the slot's attributes into `a`; returns its declaration of the optional inputs
+int apply_attrs(acct_fa_args& a, int slot) {
   FaAttrs at;
   {
     std::lock_guard<std::mutex> lock(g_attrs_mutex);
@@ -137,6 +169,7 @@ void apply_attrs(acct_fa_args& a, int slot) {
   a.keep_prob = at.keep_prob;
   a.scale = at.scale;
   a.causal = at.causal;
+  return at.optional_inputs;
 }
 
 }  // namespace
@@ -164,7 +197,8 @@ int ms_fa_fwd(int slot, int nparam, void** params, int* ndims, int64_t** shapes,
   acct_fa_args a;
   std::memset(&a, 0, sizeof a);
   if (!fill_qkv(a, params, ndims, shapes, dtypes)) return ACCT_ERR_SHAPE;
-  if (!fill_optionals(a, 3, nparam - 2, params, ndims, shapes, dtypes)) return ACCT_ERR_SHAPE;
+  const int declared = apply_attrs(a, slot);
+  if (!fill_optionals(a, 3, nparam - 2, params, ndims, shapes, dtypes, declared)) return ACCT_ERR_SHAPE;
   if (dtype_code(dtypes[nparam - 1]) != ACCT_F32) return ACCT_ERR_DTYPE;   // rowsum is fp32 (impl.py:134-136)
   // output is shaped and typed like q, rowsum is [B, N, S_q]
   if (!is_shape4(nparam - 2, ndims, shapes, dtypes, a.B, a.N, a.S_q, a.D, a.dtype)) return ACCT_ERR_SHAPE;
@@ -172,7 +206,6 @@ int ms_fa_fwd(int slot, int nparam, void** params, int* ndims, int64_t** shapes,
     return ACCT_ERR_SHAPE;
   a.o = params[nparam - 2];
   a.lse = static_cast<float*>(params[nparam - 1]);
-  apply_attrs(a, slot);
   if (const int rc = summarise_mask(a, stream)) return rc;
   return acct_fa_fwd(&a, stream);
 }
@@ -187,7 +220,8 @@ int ms_fa_grad(int slot, int nparam, void** params, int* ndims, int64_t** shapes
   std::memset(&a, 0, sizeof a);
   if (!fill_qkv(a, params, ndims, shapes, dtypes)) return ACCT_ERR_SHAPE;
   const int first_out = nparam - 4;
-  if (!fill_optionals(a, 6, first_out, params, ndims, shapes, dtypes)) return ACCT_ERR_SHAPE;
+  const int declared = apply_attrs(a, slot);
+  if (!fill_optionals(a, 6, first_out, params, ndims, shapes, dtypes, declared)) return ACCT_ERR_SHAPE;
   for (int i = first_out; i < first_out + 3; ++i)
     if (dtype_code(dtypes[i]) != ACCT_F32) return ACCT_ERR_DTYPE;
   if (ndims[nparam - 1] != 1) return ACCT_ERR_WORKSPACE;
@@ -199,7 +233,6 @@ int ms_fa_grad(int slot, int nparam, void** params, int* ndims, int64_t** shapes
     if (!is_shape4(i, ndims, shapes, dtypes, a.B, a.N_kv, a.S_k, a.D, ACCT_F32)) return ACCT_ERR_SHAPE;
   a.o = params[3];
   a.lse = static_cast<float*>(params[5]);
-  apply_attrs(a, slot);
   if (const int rc = summarise_mask(a, stream)) return rc;
   a.flags |= ACCT_FLAG_GRAD_F32;
   acct_fa_bwd_io g;
@@ -228,12 +261,14 @@ ACCT_API int acct_ms_fa_grad(int nparam, void** params, int* ndims, int64_t** sh
 
 // Stores a tuple of attributes and returns the number k of its slot (an identical tuple gets the slot it already
 // has); -1 when all slots hold other tuples.  Operators registered on acct_ms_fa_fwd_s<k> / acct_ms_fa_grad_s<k> use it.
-ACCT_API int acct_ms_fa_attrs_slot(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal) {
+ACCT_API int acct_ms_fa_attrs_slot_ex(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal,
+                                      int optional_inputs) {
+  if (optional_inputs < -1 || optional_inputs > 7) return -1;
   std::lock_guard<std::mutex> lock(g_attrs_mutex);
   for (int i = 0; i < g_slots_used; ++i) {
     const FaAttrs& t = g_slot[i];
     if (t.prev_block_num == prev_block_num && t.next_block_num == next_block_num && t.keep_prob == keep_prob &&
-        t.scale == scale && t.causal == causal)
+        t.scale == scale && t.causal == causal && t.optional_inputs == optional_inputs)
       return i;
   }
   if (g_slots_used >= kSlots) return -1;
@@ -243,7 +278,11 @@ ACCT_API int acct_ms_fa_attrs_slot(int prev_block_num, int next_block_num, float
   t.keep_prob = keep_prob;
   t.scale = scale;
   t.causal = causal;
+  t.optional_inputs = optional_inputs;
   return g_slots_used++;
+}
+ACCT_API int acct_ms_fa_attrs_slot(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal) {
+  return acct_ms_fa_attrs_slot_ex(prev_block_num, next_block_num, keep_prob, scale, causal, -1);
 }
 
 #define ACCT_MS_SLOT(k)                                                                                               \

@@ -77,14 +77,24 @@ def grad_out_dtype(q_dtype, k_dtype, v_dtype, o_dtype, do_dtype, l_dtype, attn_m
     return float32, float32, float32, uint8
 
 
-def attrs_slot(prev_block_num=65536, next_block_num=65536, keep_prob=1.0, scale=1.0, causal=False):
+HAS_ATTN_MASK, HAS_DROPOUT_MASK, HAS_ALIBI_MASK = 1, 2, 4     # ACCT_MS_HAS_* of include/acct_b200.h
+
+
+def attrs_slot(prev_block_num=65536, next_block_num=65536, keep_prob=1.0, scale=1.0, causal=False, optional_inputs=None):
     """Number of the library's attribute slot that holds these values (an identical tuple gets the slot it already
-    has).  Raises when all slots are taken by other tuples."""
+    has).  Raises when all slots are taken by other tuples.
+
+    ``optional_inputs``: which of attn_mask / dropout_mask / alibi_mask the primitive will pass (a sum of ``HAS_*``);
+    the library then takes exactly those, by position, and checks each one's shape.  ``None``: the library tells the
+    optional inputs apart by their shapes (it cannot tell an alibi_mask from a dropout_mask when S_q = 1)."""
     lib = _lib.load()
-    lib.acct_ms_fa_attrs_slot.argtypes = [C.c_int, C.c_int, C.c_float, C.c_float, C.c_int]
-    lib.acct_ms_fa_attrs_slot.restype = C.c_int
-    slot = lib.acct_ms_fa_attrs_slot(int(min(prev_block_num, 65536)), int(min(next_block_num, 65536)), float(keep_prob),
-                                     float(scale), 1 if causal else 0)
+    lib.acct_ms_fa_attrs_slot_ex.argtypes = [C.c_int, C.c_int, C.c_float, C.c_float, C.c_int, C.c_int]
+    lib.acct_ms_fa_attrs_slot_ex.restype = C.c_int
+    declared = -1 if optional_inputs is None else int(optional_inputs)
+    if not -1 <= declared <= 7:
+        raise ValueError(f"optional_inputs = {optional_inputs}: a sum of HAS_ATTN_MASK, HAS_DROPOUT_MASK, HAS_ALIBI_MASK")
+    slot = lib.acct_ms_fa_attrs_slot_ex(int(min(prev_block_num, 65536)), int(min(next_block_num, 65536)), float(keep_prob),
+                                        float(scale), 1 if causal else 0, declared)
     if slot < 0:
         raise RuntimeError(f"all {MAX_SLOTS} attribute slots of libacct_b200.so are in use by other attribute tuples")
     return slot
@@ -129,14 +139,14 @@ def _ms():
 
 
 def get_flash_attention_grad(prev_block_num=65536, next_block_num=65536, tiling_stgy_name='sparse', keep_prob=1.0,
-                             scale=1.0, causal=False):
+                             scale=1.0, causal=False, optional_inputs=None):
     """Returns the ``bprop`` function of the forward primitive, built around the grad primitive
     (flash_attention_impl.py:96-126)."""
     ms = _ms()
     from mindspore import ops
     from mindspore.common import dtype as mstype
     from mindspore.ops import Custom
-    slot = attrs_slot(prev_block_num, next_block_num, keep_prob, scale, causal)
+    slot = attrs_slot(prev_block_num, next_block_num, keep_prob, scale, causal, optional_inputs)
 
     def out_dtype(*dtypes):
         return mstype.float32, mstype.float32, mstype.float32, mstype.uint8
@@ -163,18 +173,20 @@ def get_flash_attention_grad(prev_block_num=65536, next_block_num=65536, tiling_
 
 
 def get_flash_attention(prev_block_num=65536, next_block_num=65536, tiling_stgy_name='sparse', keep_prob=1.0, scale=1.0,
-                        causal=False):
+                        causal=False, optional_inputs=None):
     """Returns the forward primitive ``fa(query, key, value, attn_mask, dropout_mask, alibi_mask) -> (output, rowsum)``
-    with its ``bprop`` attached (flash_attention_impl.py:129-154)."""
+    with its ``bprop`` attached (flash_attention_impl.py:129-154).  ``optional_inputs`` (a sum of ``HAS_*``) declares
+    which of the three optional inputs the caller will pass; see ``attrs_slot``."""
     _ms()
     from mindspore.common import dtype as mstype
     from mindspore.ops import Custom
-    slot = attrs_slot(prev_block_num, next_block_num, keep_prob, scale, causal)
+    slot = attrs_slot(prev_block_num, next_block_num, keep_prob, scale, causal, optional_inputs)
 
     def out_dtype(q_dtype, *rest):
         return q_dtype, mstype.float32
 
-    bprop = get_flash_attention_grad(prev_block_num, next_block_num, tiling_stgy_name, keep_prob, scale, causal)
+    bprop = get_flash_attention_grad(prev_block_num, next_block_num, tiling_stgy_name, keep_prob, scale, causal,
+                                     optional_inputs)
     fa_forward = Custom(aot_func("fwd", slot), out_shape=forward_out_shape, out_dtype=out_dtype, func_type="aot",
                         bprop=bprop)
     fa_forward.add_prim_attr("prev_block_num", prev_block_num)

@@ -314,9 +314,17 @@ ACCT_API int acct_infer_decode_static(const acct_decode_args* a, void* stream);
  * identical tuple gets the slot it already has; -1 when all slots hold other tuples), and the operator pair is
  * registered on acct_ms_fa_fwd_s<k> / acct_ms_fa_grad_s<k>.  Layers of one graph with different band widths, dropout
  * rates or scales thus keep their own values.  The unnumbered entry points use one process-wide tuple, set with
- * acct_ms_set_fa_attrs; its defaults are "no band, keep_prob 1, scale 1, not causal". */
+ * acct_ms_set_fa_attrs; its defaults are "no band, keep_prob 1, scale 1, not causal".
+ * acct_ms_fa_attrs_slot_ex() also records WHICH optional inputs the primitive passes (ACCT_MS_HAS_* bits, in the
+ * reference's order attn_mask, dropout_mask, alibi_mask): the call then takes exactly those, by position, and checks
+ * each against the shape its name demands, instead of guessing from shapes (-1 = guess, as the other two do). */
+#define ACCT_MS_HAS_ATTN_MASK 1
+#define ACCT_MS_HAS_DROPOUT_MASK 2
+#define ACCT_MS_HAS_ALIBI_MASK 4
 ACCT_API void acct_ms_set_fa_attrs(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal);
 ACCT_API int acct_ms_fa_attrs_slot(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal);
+ACCT_API int acct_ms_fa_attrs_slot_ex(int prev_block_num, int next_block_num, float keep_prob, float scale, int causal,
+                                      int optional_inputs);
 #define ACCT_MS_SLOT_ENTRY(k)                                                                                       \
   ACCT_API int acct_ms_fa_fwd_s##k(int nparam, void** params, int* ndims, int64_t** shapes, const char** dtypes,    \
                                    void* stream, void* extra);                                                      \

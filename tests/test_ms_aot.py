@@ -167,6 +167,63 @@ def test_attribute_slots_are_per_tuple_and_reused(lib):
         assert hasattr(lib, f"acct_ms_fa_fwd_s{k}") and hasattr(lib, f"acct_ms_fa_grad_s{k}")
 
 
+def _slot_fn(lib, kind, k):
+    fn = getattr(lib, f"acct_ms_fa_{kind}_s{k}")
+    fn.argtypes = [C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.POINTER(C.POINTER(C.c_int64)),
+                   C.POINTER(C.c_char_p), C.c_void_p, C.c_void_p]
+    fn.restype = C.c_int
+    return fn
+
+
+def test_declared_optional_inputs_are_taken_by_position_and_checked_by_name(lib):
+    """A primitive bound to a slot that declares its optional inputs (ACCT_MS_HAS_* bits) gets exactly those, in the
+    reference's order attn_mask, dropout_mask, alibi_mask; shapes no longer decide what an input is.
+    No call here may get as far as a kernel (the pointers are fake): every one carries a rowsum / dq of the wrong
+    type, which is looked at right AFTER the optional inputs -- so ACCT_ERR_DTYPE means "the optional inputs were
+    accepted" and ACCT_ERR_SHAPE "they were not"."""
+    lib.acct_ms_fa_attrs_slot_ex.argtypes = [C.c_int, C.c_int, C.c_float, C.c_float, C.c_int, C.c_int]
+    lib.acct_ms_fa_attrs_slot_ex.restype = C.c_int
+    MASK, DROP, ALIBI = 1, 2, 4
+    assert lib.acct_ms_fa_attrs_slot_ex(65536, 65536, 1.0, 1.0, 0, 8) == -1              # not a sum of the three bits
+    plain = lib.acct_ms_fa_attrs_slot_ex(65536, 65536, 1.0, 0.25, 0, -1)
+    only_alibi = lib.acct_ms_fa_attrs_slot_ex(65536, 65536, 1.0, 0.25, 0, ALIBI)
+    mask_alibi = lib.acct_ms_fa_attrs_slot_ex(65536, 65536, 1.0, 0.25, 0, MASK | ALIBI)
+    none = lib.acct_ms_fa_attrs_slot_ex(65536, 65536, 1.0, 0.25, 0, 0)
+    assert len({plain, only_alibi, mask_alibi, none}) == 4 and min(plain, only_alibi, mask_alibi, none) >= 0
+    assert lib.acct_ms_fa_attrs_slot_ex(65536, 65536, 1.0, 0.25, 0, ALIBI) == only_alibi  # the same tuple, the same slot
+    ACCEPTED, REFUSED = ERR_DTYPE, ERR_SHAPE
+    # decode-like shapes, S_q = 1: [B,N,1,S_k] is an alibi_mask where the slot says so ...
+    q = ((2, 4, 1, 64), b"float16")
+    k = ((2, 4, 384, 64), b"float16")
+    bad_lse = ((2, 4, 1), b"float16")
+    row16, row8 = ((2, 4, 1, 384), b"float16"), ((2, 4, 1, 384), b"uint8")
+    fwd = lambda slot: _slot_fn(lib, "fwd", slot)
+    assert aot_call(fwd(only_alibi), [q, k, k, row16, q, bad_lse]) == ACCEPTED
+    assert aot_call(fwd(only_alibi), [q, k, k, row8, q, bad_lse]) == REFUSED             # an alibi has q's type
+    assert aot_call(fwd(plain), [q, k, k, row8, q, bad_lse]) == ACCEPTED                 # by shape: a uint8 dropout mask
+    # ... the count must match the declaration ...
+    assert aot_call(fwd(only_alibi), [q, k, k, q, bad_lse]) == REFUSED                   # declared, not passed
+    assert aot_call(fwd(none), [q, k, k, row16, q, bad_lse]) == REFUSED                  # passed, not declared
+    assert aot_call(fwd(none), [q, k, k, q, bad_lse]) == ACCEPTED
+    # ... and so must the order: attn_mask before alibi_mask
+    q2, o2, bad_l2 = ((2, 4, 256, 64), b"float16"), ((2, 4, 256, 64), b"float16"), ((2, 4, 256), b"float16")
+    m, al = ((2, 256, 384), b"float16"), ((2, 4, 1, 384), b"float16")
+    assert aot_call(fwd(mask_alibi), [q2, k, k, m, al, o2, bad_l2]) == ACCEPTED
+    assert aot_call(fwd(mask_alibi), [q2, k, k, al, m, o2, bad_l2]) == REFUSED
+    assert aot_call(fwd(plain), [q2, k, k, al, m, o2, bad_l2]) == ACCEPTED               # by shape: any order
+    # the grad primitive reads the same declaration (dq of the wrong type stops the accepted calls)
+    g32 = lambda shp: (shp, b"float32")
+    l2 = ((2, 4, 256), b"float32")
+    outs = [((2, 4, 256, 64), b"float16"), g32((2, 4, 384, 64)), g32((2, 4, 384, 64)), ((1 << 20,), b"uint8")]
+    grad = _slot_fn(lib, "grad", only_alibi)
+    assert aot_call(grad, [q2, k, k, o2, o2, l2, al] + outs) == ACCEPTED
+    assert aot_call(grad, [q2, k, k, o2, o2, l2, m] + outs) == REFUSED                   # an attn_mask where an alibi is due
+    from acctransformer_b200 import mindspore_adapter as ad
+    assert ad.attrs_slot(65536, 65536, 1.0, 0.25, False, ad.HAS_ALIBI_MASK) == only_alibi
+    with pytest.raises(ValueError):
+        ad.attrs_slot(optional_inputs=9)
+
+
 def test_mismatched_key_value_and_mask_shapes_are_rejected_before_any_read(lib):
     q = ((2, 4, 256, 64), b"float16")
     o, l = ((2, 4, 256, 64), b"float16"), ((2, 4, 256), b"float32")
