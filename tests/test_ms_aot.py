@@ -311,3 +311,41 @@ def test_two_primitives_with_different_attributes_in_one_process():
                               prev_block_num=kw["prev_block_num"], next_block_num=kw["next_block_num"])
         assert np.max(np.abs(_np(o) - o_ref)) <= 2e-3
     assert torch.equal(outs[0], outs[2]) and not torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.gpu
+def test_one_query_row_with_a_declared_alibi_mask():
+    """S_q = 1: by shape alone [B,N,1,S_k] would be taken for a dropout mask; a slot that declares the input as the
+    alibi_mask gets the bias added (against the CPU oracle), through the forward and the grad primitive."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from acctransformer_b200 import mindspore_adapter as ad
+    lb = _lib.load()
+    sig = [C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.POINTER(C.POINTER(C.c_int64)), C.POINTER(C.c_char_p),
+           C.c_void_p, C.c_void_p]
+    dev = torch.device("cuda", 0)
+    B, N, S_k, D = 2, 4, 384, 64
+    rs = np.random.RandomState(13)
+    q, do = (torch.tensor(rs.randn(B, N, 1, D).astype(np.float32)).half().to(dev) for _ in range(2))
+    k, v = (torch.tensor(rs.randn(B, N, S_k, D).astype(np.float32)).half().to(dev) for _ in range(2))
+    alibi_np = np.ascontiguousarray(ref.alibi_bias(B, N, S_k))                           # [B,N,1,S_k] fp16
+    alibi = torch.tensor(alibi_np).to(dev)
+    slot = ad.attrs_slot(scale=0.125, optional_inputs=ad.HAS_ALIBI_MASK)
+    stream = torch.cuda.current_stream().cuda_stream
+    fwd, grad = getattr(lb, f"acct_ms_fa_fwd_s{slot}"), getattr(lb, f"acct_ms_fa_grad_s{slot}")
+    fwd.argtypes, fwd.restype, grad.argtypes, grad.restype = sig, C.c_int, sig, C.c_int
+    o = torch.empty_like(q)
+    lse = torch.empty(B, N, 1, dtype=torch.float32, device=dev)
+    assert aot_call(fwd, [q, k, v, alibi, o, lse], stream) == 0
+    dq = torch.empty(B, N, 1, D, dtype=torch.float32, device=dev)
+    dk, dv = (torch.empty(B, N, S_k, D, dtype=torch.float32, device=dev) for _ in range(2))
+    ws = torch.empty(ad.bwd_workspace_bytes((B, N, 1, D)), dtype=torch.uint8, device=dev)
+    assert aot_call(grad, [q, k, v, o, do, lse, alibi, dq, dk, dv, ws], stream) == 0
+    torch.cuda.synchronize()
+    _lib.device_status()
+    o_ref, l_ref = ref.sa_fwd(_np(q), _np(k), _np(v), alibi=alibi_np, scale=0.125)
+    assert np.max(np.abs(_np(o) - o_ref)) <= 2e-3 and np.max(np.abs(_np(lse) - l_ref)) <= 2e-3
+    o_plain, _ = ref.sa_fwd(_np(q), _np(k), _np(v), scale=0.125)
+    assert np.max(np.abs(o_ref - o_plain)) > 2e-2                   # (the bias matters at these sizes)
+    for got, want in zip((dq, dk, dv), ref.sa_grad(_np(q), _np(k), _np(v), _np(do), alibi=alibi_np, scale=0.125)):
+        assert np.max(np.abs(_np(got) - want)) <= 1e-2 * np.max(np.abs(want))
