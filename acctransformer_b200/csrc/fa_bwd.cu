@@ -498,9 +498,31 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     const uint32_t t_dp = tmem + lane_base + kColDP;
     uint8_t* my_ds = sDS + hf * 16384u;                  // this half's dS^T block
     int g0 = 0;
-    for (int k = 0;; ++k) {
-    const int item_no = next_item(sh.item_full, sh.item_empty, sh.item, k, abort_flag, p.status);
-    if (item_no >= total_items) break;
+    // What an item needs from global memory before its first step -- the statistics of its first Q tile and the key
+    // row's alibi term -- is requested before the write-out of the item BEFORE it and left raw until then, so that
+    // the latency of those loads does not sit between two items (it did: the compute warps came out of the
+    // write-out, loaded, and only then looked at an S^T that had been waiting for them).
+    float pre_lse = 0.f, pre_dlt = 0.f;
+    uint32_t pre_bias = 0u;
+    auto request_first = [&](const BwdItem& t) {
+      if (t.n_iter <= 0) return;
+      const int h0 = t.h_kv * p.kv_group;
+      if (hf == 0) {
+        const int64_t idx = (static_cast<int64_t>(t.b) * p.N + h0) * p.S_q + min(t.i_lo * kTile + r, p.S_q - 1);
+        pre_lse = p.lse[idx];
+        pre_dlt = p.delta[idx];
+      }
+      const int kv = t.j * kTile + r;
+      if (kv < t.kv_len) {
+        if (mods.alibi != nullptr)
+          pre_bias = reinterpret_cast<const uint16_t*>(mods.alibi)[(static_cast<int64_t>(t.b) * p.N + h0) * p.S_k + kv];
+        else if (mods.alibi_slopes != nullptr)
+          pre_bias = __float_as_uint(mods.alibi_slopes[h0]);
+      }
+    };
+    int item_no = next_item(sh.item_full, sh.item_empty, sh.item, 0, abort_flag, p.status);
+    if (item_no < total_items) request_first(decode_item(p, item_no));
+    for (int k = 0; item_no < total_items; ++k) {
     const BwdItem it = decode_item(p, item_no);
     const int b = it.b, j = it.j, kv_len = it.kv_len, i_lo = it.i_lo, n_per = it.n_per, n_iter = it.n_iter;
     const int bh_kv = it.bh_kv;
@@ -519,6 +541,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       return v;
     };
     float bias = kNegInf;
+    float bias_first = kNegInf;          // bias_of(head_of(0)), from the value requested ahead
+    if (kv_ok) {
+      bias_first = 0.f;
+      if (mods.alibi != nullptr)
+        bias_first = (BF16 ? __uint_as_float(pre_bias << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(pre_bias)))) * kLog2e;
+      else if (mods.alibi_slopes != nullptr)
+        bias_first = __uint_as_float(pre_bias) * static_cast<float>(kv_idx) * kLog2e;
+    }
 
     // statistics of the first Q tile
     // The next tile's statistics are fetched one tile ahead and kept RAW until they are parked: any arithmetic on a
@@ -528,11 +558,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     if (hf == 0 && n_iter > 0) {
       const int q_row = i_lo * kTile + r;
       const bool q_ok = q_row < p.S_q;
-      const int64_t idx = (static_cast<int64_t>(b) * p.N + head_of(0)) * p.S_q + min(q_row, p.S_q - 1);
       // (buffer g0 & 1 was last read for the step before last, whose dS part every thread finished before the
       // products this thread has since waited for could be issued)
-      sh.lse2[g0 & 1][r] = q_ok ? p.lse[idx] * kLog2e : INFINITY;
-      sh.delta[g0 & 1][r] = q_ok ? p.delta[idx] : 0.f;
+      sh.lse2[g0 & 1][r] = q_ok ? pre_lse * kLog2e : INFINITY;
+      sh.delta[g0 & 1][r] = q_ok ? pre_dlt : 0.f;
       mbar_arrive(&sh.stats_ready);
     }
 
@@ -549,7 +578,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       const int q_base = i * kTile;
       const int bh = b * p.N + head_of(n);
       const int gn = g0 + n;                                    // running step number: the phase of the per-step barriers
-      if (n % max(n_per, 1) == 0) bias = bias_of(head_of(n));   // first tile of a query head
+      if (n % max(n_per, 1) == 0) bias = n == 0 ? bias_first : bias_of(head_of(n));   // first tile of a query head
       mask_class = mask_class_next;
       if (tile_class != nullptr && n + 1 < n_iter) mask_class_next = tile_class[static_cast<int64_t>(tile_of(n + 1)) * tiles_k];
       // ---- P part: needs S^T only
@@ -707,6 +736,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     // (the tensor-memory loads are warp-collective: every lane runs them, only the stores are guarded)
     if (n_iter > 0) mbar_wait(&sh.dq_full, (g0 + n_iter - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
     tc_fence_after_sync();
+    // the next item (the producer published it while this item's last tiles were loading): its first loads go out now
+    const int next_no = next_item(sh.item_full, sh.item_empty, sh.item, k + 1, abort_flag, p.status);
+    if (next_no < total_items) request_first(decode_item(p, next_no));
     const bool row_ok = kv_idx < p.S_k;
     const int64_t row_off = (static_cast<int64_t>(bh_kv) * p.S_k + kv_idx) * p.D;
 #pragma unroll 1
@@ -754,6 +786,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     // dK and dV are out of tensor memory: the next item's first products may overwrite them
     if (n_iter > 0) mbar_arrive(&sh.acc_free);
     g0 += n_iter;
+    item_no = next_no;
     }
   }
 
