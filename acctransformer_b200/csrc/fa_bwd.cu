@@ -57,13 +57,14 @@ struct BwdShared {
   uint64_t acc_free;             // compute -> MMA: dK and dV of the work item have been read out of tensor memory
   uint64_t q_full[kStages];
   uint64_t q_empty[kStages];     // drain (on dq_full) -> producer: the products reading this Q stage have finished
-  uint64_t do_full;
+  uint64_t do_full;              // producer (dO of step n has landed) + drain (dQ of step n-1 is in registers, the dP^T
+                                 // columns are free again) -> MMA: dP^T of step n may be issued.  One barrier for both:
+                                 // every wait costs the issuing thread time in which the tensor pipe may idle
   uint64_t do_empty;             // MMA -> producer: the dV product reading dO has finished
   uint64_t st_full, dp_full;     // MMA -> compute: S^T / dP^T are in tensor memory
   uint64_t p_ready;              // compute -> MMA: P^T is in tensor memory
   uint64_t ds_ready;             // compute -> MMA: dS^T is in shared memory
   uint64_t dq_full;              // MMA -> drain: dV, dK and dQ products of this Q tile have finished
-  uint64_t dq_read;              // drain -> MMA: dQ is in registers, the dP^T columns are free again
   uint64_t stats_ready;          // compute -> compute: lse2 / delta of this Q tile are in shared memory
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
@@ -248,14 +249,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     mbar_init(&sh.kv_empty, 1);
     mbar_init(&sh.acc_free, kComputeThreads);
     for (int s = 0; s < kStages; ++s) { mbar_init(&sh.q_full[s], 1); mbar_init(&sh.q_empty[s], 1); }
-    mbar_init(&sh.do_full, 1);
+    mbar_init(&sh.do_full, 1 + kTile);
     mbar_init(&sh.do_empty, 1);
     mbar_init(&sh.st_full, 1);
     mbar_init(&sh.dp_full, 1);
     mbar_init(&sh.p_ready, kComputeThreads);
     mbar_init(&sh.ds_ready, kComputeThreads);
     mbar_init(&sh.dq_full, 1);
-    mbar_init(&sh.dq_read, kTile);
     mbar_init(&sh.stats_ready, kTile);
     sh.abort_flag = 0;
     mbar_fence_init();
@@ -361,7 +361,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
             const uint32_t mQ = mQ0 + st * kTileUnits;
             // dP^T = V dO^T as early as possible: it only needs dO and the previous dQ out of its columns
             mbar_wait(&sh.do_full, gn & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
-            if (gn > 0) mbar_wait(&sh.dq_read, (gn - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
             tc_fence_after_sync();
 #pragma unroll
             for (int kk = 0; kk < DPAD / 16; ++kk) {
@@ -412,6 +411,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     const int r = tid - kDrainWarp0 * 32;
     const uint32_t t_dq = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kColDP;
     const bool elected = (r == 0);
+    mbar_arrive(&sh.do_full);              // the first step of the kernel has no dQ before it to wait for
     int g0 = 0;
     for (int k = 0;; ++k) {
     const int w = next_item(sh.item_full, sh.item_empty, sh.item, k, abort_flag, p.status);
@@ -434,7 +434,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       for (int c = 0; c < kChunks; ++c) tmem_ld32(t_dq + c * 32, dq[c]);
       tmem_wait_ld();
       tc_fence_before_sync();
-      mbar_arrive(&sh.dq_read);
+      mbar_arrive(&sh.do_full);          // (counts towards the NEXT step's phase: this step's has completed)
 #pragma unroll
       for (int rd = 0; rd < kChunks / 2; ++rd) {
         // the staging area is free once the previous round's reduce has read it
