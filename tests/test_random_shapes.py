@@ -1,0 +1,133 @@
+"""Randomly drawn shapes and option combinations of the training and decode operators against the CPU oracle.
+
+The hand-picked cases of the other GPU tests cover what the reference's own tests cover; this file draws sizes (1 .. 900
+rows, every head_dim family incl. the wide backward), head groupings, dtypes and option mixes (causal, band, mask
+tensor of either type, alibi, dropout tensor, valid lengths, ordered dQ) from fixed seeds, so that index arithmetic at
+odd sizes is exercised in combinations nobody thought of.  Tolerances are the stated ones: max|O - O_ref| <= 2e-3 (fp16;
+bf16 inputs 1.6e-2), gradients within 1e-2 (bf16 3e-2) of the tensor's largest magnitude."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention_ref as ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _np(t):
+    return t.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("seed", [101, 102, 103])
+def test_training_operators_on_random_shapes(seed):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from acctransformer_b200 import _lib, ops
+    dev = torch.device("cuda", 0)
+    rs = np.random.RandomState(seed)
+    for case in range(25):
+        D = int(rs.choice([40, 64, 80, 128, 128, 128, 160, 256]))
+        B, G, Nkv = int(rs.randint(1, 4)), int(rs.choice([1, 1, 1, 2, 4])), int(rs.randint(1, 4))
+        N = Nkv * G
+        Sq, Sk = int(rs.randint(1, 900)), int(rs.randint(2, 900))
+        if rs.rand() < 0.4:
+            Sq = Sk
+        dt = torch.bfloat16 if rs.rand() < 0.3 else torch.float16
+        std = 0.5 if dt == torch.bfloat16 else 1.0
+        draw = lambda *s: (torch.tensor(rs.randn(*s).astype(np.float32)) * std).to(dt)
+        q, do, k, v = draw(B, N, Sq, D), draw(B, N, Sq, D), draw(B, Nkv, Sk, D), draw(B, Nkv, Sk, D)
+        kw = dict(scale=float(rs.choice([1 / math.sqrt(D), 0.1])))
+        mode = str(rs.choice(["plain", "causal", "band", "mask", "alibi", "drop", "lens", "ordered", "mix"]))
+        mask = None
+        if mode in ("causal", "ordered") and Sq <= Sk:
+            kw["causal"] = True
+        if mode in ("band", "mix"):
+            kw["prev_block_num"], kw["next_block_num"] = int(rs.randint(0, 4)), int(rs.randint(0, 4))
+            # rows that no K/V tile reaches are undefined in the oracle (and zeros here): keep every Q tile in the band
+            if (Sq + 127) // 128 - 1 - kw["prev_block_num"] > (Sk + 127) // 128 - 1:
+                kw.pop("prev_block_num")
+        if mode in ("mask", "mix"):
+            m = rs.random_sample((B if rs.rand() < 0.5 else 1, Sq, Sk)) < 0.3
+            mask = torch.tensor(m.astype(np.float16)).to(dt if rs.rand() < 0.5 else torch.uint8)
+        if mode in ("alibi", "mix"):
+            kw["alibi"] = (torch.tensor(ref.alibi_bias(B, N, Sk, np.float32)) * 0.05).to(dt)
+        if mode in ("drop", "mix"):
+            kw["dropout_mask"] = torch.tensor((rs.random_sample((B, N, Sq, Sk)) < 0.8).astype(np.uint8))
+            kw["keep_prob"] = 0.8
+        if mode == "lens":
+            kw["seq_lens"] = torch.tensor(rs.randint(2, Sk + 1, size=(B,)).astype(np.int32))
+        if mode == "ordered":
+            kw["deterministic"] = True
+        what = (seed, case, mode, (B, N, Nkv, Sq, Sk, D), str(dt), {a: b for a, b in kw.items() if not torch.is_tensor(b)})
+        on_dev = {a: (b.to(dev) if torch.is_tensor(b) else b) for a, b in kw.items()}
+        fwd_kw = {a: b for a, b in on_dev.items() if a != "deterministic"}
+        md = None if mask is None else mask.to(dev)
+        o, lse = ops.fa_forward(q.to(dev), k.to(dev), v.to(dev), md, **fwd_kw)
+        dq, dk, dv = ops.fa_backward(q.to(dev), k.to(dev), v.to(dev), o, lse, do.to(dev), md, **on_dev)
+        torch.cuda.synchronize()
+        _lib.device_status()
+        okw = {}
+        for a, b in kw.items():
+            if a == "dropout_mask":
+                okw["drop_mask"] = b.numpy()
+            elif a in ("alibi", "seq_lens"):
+                okw[a] = _np(b) if a == "alibi" else b.numpy()
+            elif a != "deterministic":
+                okw[a] = b
+        if mask is not None:
+            okw["attn_mask"] = _np(mask)
+        kn, vn = np.repeat(_np(k), G, axis=1), np.repeat(_np(v), G, axis=1)     # the reference's own prescription
+        with np.errstate(all="ignore"):
+            o_ref, _ = ref.sa_fwd(_np(q), kn, vn, **okw)
+            gq, gk, gv = ref.sa_grad(_np(q), kn, vn, _np(do), **okw)
+        gk, gv = (g.reshape(B, Nkv, G, Sk, D).sum(2) for g in (gk, gv))
+        defined = np.isfinite(o_ref).all(-1, keepdims=True)                     # (a row whose every key is masked by the band)
+        tol_o, tol_g = (2e-3, 1e-2) if dt == torch.float16 else (1.6e-2, 3e-2)
+        assert float(np.abs(np.where(defined, _np(o) - o_ref, 0.0)).max()) <= tol_o, what
+        for got, want, name in ((dq, gq, "dq"), (dk, gk, "dk"), (dv, gv, "dv")):
+            want = np.nan_to_num(want)
+            assert float(np.abs(_np(got) - want).max()) <= tol_g * max(float(np.abs(want).max()), 1e-3), (name, what)
+
+
+@pytest.mark.parametrize("seed", [201, 202])
+def test_decode_on_random_shapes(seed):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from acctransformer_b200 import _lib, ops
+    dev = torch.device("cuda", 0)
+    rs = np.random.RandomState(seed)
+    for case in range(40):
+        D = int(rs.choice([40, 64, 80, 128, 128, 128, 256]))
+        G = int(rs.choice([1, 1, 2, 3, 4, 8, 16])) if D <= 128 else int(rs.choice([1, 2, 4, 8]))
+        Nkv, B = int(rs.randint(1, 5)), int(rs.randint(1, 9))
+        N = Nkv * G
+        S = int(rs.choice([1, 17, 100, 511, 512, 513, 1500, 3000, 5000]))
+        dt = torch.bfloat16 if rs.rand() < 0.3 else torch.float16
+        splits = min(int(rs.choice([0, 0, 0, 1, 3, 7])), S)
+        draw = lambda *s: torch.tensor(rs.randn(*s).astype(np.float32)).to(dt)
+        q, kc, vc = draw(B, N, 1, D), draw(B, Nkv, S, D), draw(B, Nkv, S, D)
+        lens = torch.tensor(rs.randint(1, S + 1, size=(B,)).astype(np.int32))
+        scale = 1 / math.sqrt(D)
+        paged = bool(rs.rand() < 0.35 and S >= 16)
+        what = (seed, case, (B, N, Nkv, S, D), str(dt), splits, paged)
+        if paged:       # the same caches cut into pages that lie in the pool in a random order
+            ps = int(rs.choice([16, 64, 128]))
+            mp = (S + ps - 1) // ps
+            table = rs.permutation(B * mp + 3)[:B * mp].reshape(B, mp)
+            pools = []
+            for cache in (kc, vc):
+                padded = torch.zeros(B, Nkv, mp * ps, D, dtype=dt)
+                padded[:, :, :S] = cache
+                pool = torch.zeros(B * mp + 3, Nkv, ps, D, dtype=dt)
+                pool[torch.tensor(table.reshape(-1))] = padded.reshape(B, Nkv, mp, ps, D).permute(0, 2, 1, 3, 4).reshape(B * mp, Nkv, ps, D)
+                pools.append(pool.to(dev))
+            y = ops.infer_decode(q.to(dev), pools[0], pools[1], lens.to(dev), scale=scale, num_splits=splits,
+                                 block_table=torch.tensor(table.astype(np.int32)).to(dev))
+        else:
+            y = ops.infer_decode(q.to(dev), kc.to(dev), vc.to(dev), lens.to(dev), scale=scale, num_splits=splits)
+        torch.cuda.synchronize()
+        _lib.device_status()
+        want = ref.decode_ref(_np(q), np.repeat(_np(kc), G, axis=1), np.repeat(_np(vc), G, axis=1), lens.numpy(), scale)
+        assert float(np.abs(_np(y) - want).max()) <= (2e-3 if dt == torch.float16 else 1.6e-2), what
