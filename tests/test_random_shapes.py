@@ -131,3 +131,38 @@ def test_decode_on_random_shapes(seed):
         _lib.device_status()
         want = ref.decode_ref(_np(q), np.repeat(_np(kc), G, axis=1), np.repeat(_np(vc), G, axis=1), lens.numpy(), scale)
         assert float(np.abs(_np(y) - want).max()) <= (2e-3 if dt == torch.float16 else 1.6e-2), what
+
+
+@pytest.mark.parametrize("seed", [301])
+def test_inference_op_on_random_shapes(seed):
+    """FlashAttentionTik(q, k, v) at rank 3 and 4 (op_proto/flash_attention_tik.cpp:163-185), with the scale / causal /
+    seq_lens additions drawn at random."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from acctransformer_b200 import _lib, flash_attention_tik
+    dev = torch.device("cuda", 0)
+    rs = np.random.RandomState(seed)
+    for case in range(30):
+        D = int(rs.choice([40, 64, 80, 128, 128, 200, 256]))
+        B, N = int(rs.randint(1, 4)), int(rs.randint(1, 5))
+        Sq, Sk = int(rs.randint(1, 1200)), int(rs.randint(1, 1200))
+        dt = torch.bfloat16 if rs.rand() < 0.3 else torch.float16
+        causal = bool(rs.rand() < 0.4)
+        if causal:
+            Sk = max(Sk, Sq)                       # every query row then sees at least key 0
+        scale = float(rs.choice([1.0 / math.sqrt(D), 0.05]))
+        std = 0.5 if dt == torch.bfloat16 else 1.0
+        draw = lambda *s: (torch.tensor(rs.randn(*s).astype(np.float32)) * std).to(dt)
+        q, k, v = draw(B, N, Sq, D), draw(B, N, Sk, D), draw(B, N, Sk, D)
+        lens = torch.tensor(rs.randint(1, Sk + 1, size=(B,)).astype(np.int32)) if rs.rand() < 0.3 and not causal else None
+        rank3 = bool(rs.rand() < 0.4) and lens is None
+        what = (seed, case, (B, N, Sq, Sk, D), str(dt), causal, scale, lens is not None, rank3)
+        shape = (lambda t: t.reshape(B * N, t.shape[2], D)) if rank3 else (lambda t: t)
+        y = flash_attention_tik(shape(q).to(dev), shape(k).to(dev), shape(v).to(dev), scale=scale, causal=causal,
+                                seq_lens=None if lens is None else lens.to(dev))
+        torch.cuda.synchronize()
+        _lib.device_status()
+        assert tuple(y.shape) == tuple(shape(q).shape) and y.dtype == dt, what
+        want = ref.infer_fwd(_np(shape(q)), _np(shape(k)), _np(shape(v)), scale=scale, causal=causal,
+                             seq_lens=None if lens is None else lens.numpy())
+        assert float(np.abs(_np(y) - want).max()) <= (2e-3 if dt == torch.float16 else 1.6e-2), what
