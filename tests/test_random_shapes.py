@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _np(t):
-    return t.float().cpu().numpy()
+    return t.detach().float().cpu().numpy()
 
 
 @pytest.mark.parametrize("seed", [101, 102, 103])
@@ -166,3 +166,64 @@ def test_inference_op_on_random_shapes(seed):
         want = ref.infer_fwd(_np(shape(q)), _np(shape(k)), _np(shape(v)), scale=scale, causal=causal,
                              seq_lens=None if lens is None else lens.numpy())
         assert float(np.abs(_np(y) - want).max()) <= (2e-3 if dt == torch.float16 else 1.6e-2), what
+
+
+@pytest.mark.parametrize("seed", [401])
+def test_cells_on_random_shapes_through_autograd(seed):
+    """The two cells with the reference's constructors and call signatures (nn/layer/flash_attention.py:49-130,
+    triangle_attention.py:28-165), random sizes, masks and band limits, gradients through torch autograd."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from acctransformer_b200 import FlashAttention, TriangleAttention, _lib
+    dev = torch.device("cuda", 0)
+    rs = np.random.RandomState(seed)
+    draw = lambda *s: torch.tensor((rs.randn(*s) * 0.7).astype(np.float32)).half()
+
+    def grads_match(leaves, want, what):
+        for t, w, name in zip(leaves, want, ("dq", "dk", "dv")):
+            assert float(np.abs(_np(t.grad) - w).max()) <= 1e-2 * float(np.abs(w).max()), (name, what)
+
+    for case in range(12):
+        # ---- FlashAttention: the cell scales by head_dim^-1/2 in all (two fp16 multiplies by d^-1/4 in the reference)
+        D = int(rs.choice([40, 64, 80, 128, 160]))
+        B, N, S = int(rs.randint(1, 3)), int(rs.randint(1, 4)), int(rs.randint(2, 700))
+        with_batch = bool(rs.rand() < 0.5)
+        prev, nxt = (int(rs.randint(1, 4)), int(rs.randint(0, 3))) if rs.rand() < 0.4 else (65536, 65536)
+        use_alibi = bool(rs.rand() < 0.3)
+        m = rs.random_sample((B if with_batch else 1, S, S)) < 0.25
+        m[..., np.arange(S), np.arange(S)] = False          # the diagonal stays visible: no row without keys
+        mask = torch.tensor(m.astype(np.float16))
+        q, k, v, do = draw(B, N, S, D), draw(B, N, S, D), draw(B, N, S, D), draw(B, N, S, D)
+        alibi = (torch.tensor(ref.alibi_bias(B, N, S, np.float32)) * 0.05).half() if use_alibi else None
+        what = ("FlashAttention", seed, case, (B, N, S, D), with_batch, prev, nxt, use_alibi)
+        cell = FlashAttention(head_dim=D, prev_block_num=prev, next_block_num=nxt, have_attention_mask_batch=with_batch,
+                              alibi=use_alibi)
+        leaves = [t.to(dev).requires_grad_(True) for t in (q, k, v)]
+        o = cell(*leaves, mask.to(dev), None if alibi is None else alibi.to(dev))
+        o.backward(do.to(dev))
+        torch.cuda.synchronize()
+        _lib.device_status()
+        okw = dict(attn_mask=_np(mask), scale=1.0 / math.sqrt(D), alibi=None if alibi is None else _np(alibi),
+                   prev_block_num=prev if prev < 65536 else None, next_block_num=nxt if nxt < 65536 else None)
+        o_ref, _ = ref.sa_fwd(_np(q), _np(k), _np(v), **okw)
+        assert float(np.abs(_np(o) - o_ref).max()) <= 2e-3, what
+        grads_match(leaves, ref.sa_grad(_np(q), _np(k), _np(v), _np(do), **okw), what)
+
+        # ---- TriangleAttention: no scaling inside, row groups of block_size, any mask
+        D = int(rs.choice([64, 128]))
+        S, block = int(rs.randint(2, 1400)), int(rs.choice([100, 128, 256, 300, 512]))
+        m = rs.random_sample((B, S, S)) < 0.25
+        m[..., 0] = False                                   # key 0 lies in every row group
+        mask = torch.tensor(m.astype(np.float16))
+        q, k, v, do = (draw(B, N, S, D) * 0.4 for _ in range(4))
+        what = ("TriangleAttention", seed, case, (B, N, S, D), block)
+        leaves = [t.to(dev).requires_grad_(True) for t in (q, k, v)]
+        o = TriangleAttention(block_size=block)(*leaves, mask.to(dev))
+        o.backward(do.to(dev))
+        torch.cuda.synchronize()
+        _lib.device_status()
+        assert float(np.abs(_np(o) - ref.triangle_fwd(_np(q), _np(k), _np(v), _np(mask), block_size=block)).max()) <= 2e-3, what
+        # keys past the end of a row's group do not exist for it: as a mask, for the gradient oracle
+        rows = np.arange(S)
+        beyond = np.arange(S)[None, :] >= ((rows // block + 1) * block)[:, None]
+        grads_match(leaves, ref.sa_grad(_np(q), _np(k), _np(v), _np(do), np.maximum(_np(mask), beyond[None].astype(np.float32))), what)
