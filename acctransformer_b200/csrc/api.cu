@@ -460,6 +460,18 @@ int acct_fa_bwd(const acct_fa_args* a, const acct_fa_bwd_io* g, void* stream) {
   t.strides[0] = a->D; t.strides[1] = static_cast<int64_t>(a->S_q) * a->D;
   t.strides[2] = static_cast<int64_t>(a->N) * a->S_q * a->D;
   if ((rc = make_tmap_4d(&p.map_dq, t, wide ? 64 : kTile))) return rc;
+  if (!wide && !(a->flags & ACCT_FLAG_GRAD_F32)) {
+    // 16-bit dk, dv, packed [B,N_kv,S_k,D]: the kernel writes a tile through shared memory and one TMA store
+    const int n_kv = kv_heads(a);
+    t.dtype = a->dtype;
+    t.dims[0] = a->D; t.dims[1] = a->S_k; t.dims[2] = n_kv; t.dims[3] = a->B;
+    t.strides[0] = a->D; t.strides[1] = static_cast<int64_t>(a->S_k) * a->D;
+    t.strides[2] = static_cast<int64_t>(n_kv) * a->S_k * a->D;
+    t.ptr = g->dk;
+    if ((rc = make_tmap_4d(&p.map_dk, t, kTile))) return rc;
+    t.ptr = g->dv;
+    if ((rc = make_tmap_4d(&p.map_dv, t, kTile))) return rc;
+  }
 
   // one helper pass before the main kernel: row sums, and the zero-fill of the accumulator and the turn counters
   cudaError_t e = launch_bwd_delta(a->o, g->d_o, delta, static_cast<int64_t>(rows), a->D, st.o[0], st.o[1], st.o[2], a->N,

@@ -741,6 +741,54 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     if (next_no < total_items) request_first(decode_item(p, next_no));
     const bool row_ok = kv_idx < p.S_k;
     const int64_t row_off = (static_cast<int64_t>(bh_kv) * p.S_k + kv_idx) * p.D;
+    if (!p.grads_f32) {
+      // 16-bit dK, dV: each tile goes through shared memory (swizzled, conflict-free 16-byte stores) and leaves by
+      // one TMA store, which also drops the rows past S_k and the columns past head_dim.  Direct stores -- one key row
+      // per lane, so every store instruction touches 32 different 256-byte rows -- took the compute warps 10 000 to
+      // 12 000 clk per work item, during which the next item's first scores sat waiting for them.
+      // The staging area is this CTA's dS^T tile: the last dQ product has finished reading it, and the next item's
+      // first dS^T is only written after this write-out.
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t t_src = tmem + lane_base + (which == 0 ? kColDK : kColDV);
+        const float mul = which == 0 ? p.scale : 1.0f;
+        if (which == 1) {                     // dK's store must have read the tile before dV goes over it
+          if (tid == 0) tma_store_wait_read();
+          named_barrier(4, kComputeThreads);
+        }
+#pragma unroll 1
+        for (int cq = 0; cq < kChunks / 2; ++cq) {
+          const int c = hf * (kChunks / 2) + cq;
+          uint32_t v[32];
+          if (n_iter > 0) { tmem_ld32(t_src + c * 32, v); tmem_wait_ld(); }
+          else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0u;
+          }
+          uint8_t* blk = sDS + (c >> 1) * 16384u;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              w[e] = pack2<BF16>(__uint_as_float(v[8 * g + 2 * e]) * mul, __uint_as_float(v[8 * g + 2 * e + 1]) * mul);
+            *reinterpret_cast<uint4*>(blk + swz128(r, (c & 1) * 4 + g)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        named_barrier(4, kComputeThreads);
+        if (tid == 0) {
+          for (int nb = 0; nb < NB; ++nb)
+            if (nb * 64 < p.D) tma_store_4d(which == 0 ? &p.map_dk : &p.map_dv, sDS + nb * 16384, nb * 64, j * kTile, it.h_kv, b);
+          tma_store_commit();
+        }
+      }
+      tc_fence_before_sync();
+      // dK and dV are out of tensor memory: the next item's first products may overwrite them
+      if (n_iter > 0) mbar_arrive(&sh.acc_free);
+      if (tid == 0) tma_store_wait_read();
+      named_barrier(4, kComputeThreads);
+    } else {
 #pragma unroll 1
     for (int which = 0; which < 2; ++which) {
       const uint32_t t_src = tmem + lane_base + (which == 0 ? kColDK : kColDV);
@@ -785,6 +833,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     tc_fence_before_sync();
     // dK and dV are out of tensor memory: the next item's first products may overwrite them
     if (n_iter > 0) mbar_arrive(&sh.acc_free);
+    }
     g0 += n_iter;
     item_no = next_no;
     }

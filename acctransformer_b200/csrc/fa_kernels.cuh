@@ -45,6 +45,7 @@ struct alignas(64) FwdParams {
 struct alignas(64) BwdParams {
   CUtensorMap map_q, map_k, map_v, map_do;
   CUtensorMap map_dq;               // fp32 dQ accumulator [B,N,S_q,D], box 32 x 128
+  CUtensorMap map_dk, map_dv;       // 16-bit dk, dv [B,N_kv,S_k,D], box 64 x 128 (unused with fp32 gradients and above head_dim 128)
   const float* lse;                 // [B,N,S_q]
   const float* delta;               // [B,N,S_q]  rowsum(dO * O)
   float* dq_acc;                    // [B,N,S_q,D] fp32, zeroed before launch
