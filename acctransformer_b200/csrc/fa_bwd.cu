@@ -54,7 +54,7 @@ struct BwdShared {
   uint64_t item_empty[2];        // everyone -> producer: the slot has been read by the MMA, drain and compute threads
   uint64_t kv_full;
   uint64_t kv_empty;             // MMA -> producer: every product of the work item has finished, K and V may be replaced
-  uint64_t acc_free;             // compute -> MMA: dK and dV of the work item have been read out of tensor memory
+  uint64_t acc_free;             // compute, drain -> MMA: dK and dV of the work item have been read out of tensor memory
   uint64_t q_full[kStages];
   uint64_t q_empty[kStages];     // drain (on dq_full) -> producer: the products reading this Q stage have finished
   uint64_t do_full;              // producer (dO of step n has landed) + drain (dQ of step n-1 is in registers, the dP^T
@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     mbar_init(&sh.item_empty[1], 1 + kTile + kComputeThreads);
     mbar_init(&sh.kv_full, 1);
     mbar_init(&sh.kv_empty, 1);
-    mbar_init(&sh.acc_free, kComputeThreads);
+    mbar_init(&sh.acc_free, kComputeThreads + kTile);   // dK is written out by the compute warps, dV by the drain warps
     for (int s = 0; s < kStages; ++s) { mbar_init(&sh.q_full[s], 1); mbar_init(&sh.q_empty[s], 1); }
     mbar_init(&sh.do_full, 1 + kTile);
     mbar_init(&sh.do_empty, 1);
@@ -485,6 +485,44 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         }
       }
     }
+    // dV of the item (16-bit gradients): out of tensor memory once the item's last products have finished (the last
+    // dq_full above), through this warpgroup's staging area and one TMA store, while the compute warps write dK
+    // through theirs.  Thread t owns key row t here.
+    if (!p.grads_f32) {
+      if (elected) tma_store_wait_read();        // the item's last dQ round has been read out of the staging area
+      named_barrier(3, kTile);
+      const uint32_t t_dv = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kColDV;
+      // (one 32-column chunk at a time, not unrolled: this runs once per item, and the drain's per-step code must keep
+      // its place in the instruction cache)
+#pragma unroll 1
+      for (int c = 0; c < kChunks; ++c) {
+        uint32_t dv[32];
+        if (it.n_iter > 0) { tmem_ld32(t_dv + c * 32, dv); tmem_wait_ld(); }
+        else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) dv[e] = 0u;
+        }
+        uint8_t* blk = sStage + (c >> 1) * 16384u;
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          *reinterpret_cast<uint4*>(blk + swz128(r, (c & 1) * 4 + g)) =
+              make_uint4(pack2<BF16>(__uint_as_float(dv[8 * g]), __uint_as_float(dv[8 * g + 1])),
+                         pack2<BF16>(__uint_as_float(dv[8 * g + 2]), __uint_as_float(dv[8 * g + 3])),
+                         pack2<BF16>(__uint_as_float(dv[8 * g + 4]), __uint_as_float(dv[8 * g + 5])),
+                         pack2<BF16>(__uint_as_float(dv[8 * g + 6]), __uint_as_float(dv[8 * g + 7])));
+      }
+      tc_fence_before_sync();
+      if (it.n_iter > 0) mbar_arrive(&sh.acc_free);
+      fence_proxy_async_smem();
+      named_barrier(3, kTile);
+      if (elected) {
+        for (int nb = 0; nb < NB; ++nb)
+          if (nb * 64 < p.D) tma_store_4d(&p.map_dv, sStage + nb * 16384, nb * 64, j * kTile, it.h_kv, b);
+        tma_store_commit();
+      }
+    } else if (it.n_iter > 0) {
+      mbar_arrive(&sh.acc_free);                  // fp32 gradients: the compute warps write both tiles out
+    }
     g0 += it.n_iter;
     }
     if (elected) tma_store_wait_all();
@@ -498,6 +536,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     const uint32_t t_dp = tmem + lane_base + kColDP;
     uint8_t* my_ds = sDS + hf * 16384u;                  // this half's dS^T block
     int g0 = 0;
+    bool ds_stage_busy = false;     // a dK store may still be reading the dS^T tile (uniform over the compute threads)
     // What an item needs from global memory before its first step -- the statistics of its first Q tile and the key
     // row's alibi term -- is requested before the write-out of the item BEFORE it and left raw until then, so that
     // the latency of those loads does not sit between two items (it did: the compute warps came out of the
@@ -665,6 +704,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       // ---- dS part: dS^T = P^T * (dP^T * M - D) into this half's shared-memory block
       mbar_wait(&sh.dp_full, gn & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
       tc_fence_after_sync();
+      if (ds_stage_busy) {       // first step after a write-out: the dK store has long read the tile by now
+        if (tid == 0) tma_store_wait_read();
+        named_barrier(4, kComputeThreads);
+        ds_stage_busy = false;
+      }
       {
         uint32_t dp[2][32];
         if constexpr (DROP == 0) {
@@ -742,20 +786,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     const bool row_ok = kv_idx < p.S_k;
     const int64_t row_off = (static_cast<int64_t>(bh_kv) * p.S_k + kv_idx) * p.D;
     if (!p.grads_f32) {
-      // 16-bit dK, dV: each tile goes through shared memory (swizzled, conflict-free 16-byte stores) and leaves by
-      // one TMA store, which also drops the rows past S_k and the columns past head_dim.  Direct stores -- one key row
-      // per lane, so every store instruction touches 32 different 256-byte rows -- took the compute warps 10 000 to
-      // 12 000 clk per work item, during which the next item's first scores sat waiting for them.
-      // The staging area is this CTA's dS^T tile: the last dQ product has finished reading it, and the next item's
-      // first dS^T is only written after this write-out.
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t t_src = tmem + lane_base + (which == 0 ? kColDK : kColDV);
-        const float mul = which == 0 ? p.scale : 1.0f;
-        if (which == 1) {                     // dK's store must have read the tile before dV goes over it
+      // 16-bit gradients: dK goes through shared memory (swizzled, conflict-free 16-byte stores) and leaves by one TMA
+      // store, which also drops the rows past S_k and the columns past head_dim; dV takes the same way through the
+      // drain warps' staging area at the same time.  Direct stores -- one key row per lane, so every store
+      // instruction touches 32 different 256-byte rows -- took the compute warps 10 000 to 12 000 clk per work item,
+      // during which the next item's first scores sat waiting for them.
+      // The staging area is this CTA's dS^T tile: the last dQ product has finished reading it, and the store's own
+      // read of it is waited for right before the next dS^T is written (ds_stage_busy).
+      {
+        if (ds_stage_busy) {     // (an item without steps right after another write-out)
           if (tid == 0) tma_store_wait_read();
           named_barrier(4, kComputeThreads);
         }
+        const uint32_t t_src = tmem + lane_base + kColDK;
 #pragma unroll 1
         for (int cq = 0; cq < kChunks / 2; ++cq) {
           const int c = hf * (kChunks / 2) + cq;
@@ -771,23 +814,21 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-              w[e] = pack2<BF16>(__uint_as_float(v[8 * g + 2 * e]) * mul, __uint_as_float(v[8 * g + 2 * e + 1]) * mul);
+              w[e] = pack2<BF16>(__uint_as_float(v[8 * g + 2 * e]) * p.scale, __uint_as_float(v[8 * g + 2 * e + 1]) * p.scale);
             *reinterpret_cast<uint4*>(blk + swz128(r, (c & 1) * 4 + g)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
+        tc_fence_before_sync();
+        if (n_iter > 0) mbar_arrive(&sh.acc_free);      // dK is out of tensor memory (the drain warps answer for dV)
         fence_proxy_async_smem();
         named_barrier(4, kComputeThreads);
         if (tid == 0) {
           for (int nb = 0; nb < NB; ++nb)
-            if (nb * 64 < p.D) tma_store_4d(which == 0 ? &p.map_dk : &p.map_dv, sDS + nb * 16384, nb * 64, j * kTile, it.h_kv, b);
+            if (nb * 64 < p.D) tma_store_4d(&p.map_dk, sDS + nb * 16384, nb * 64, j * kTile, it.h_kv, b);
           tma_store_commit();
         }
+        ds_stage_busy = true;
       }
-      tc_fence_before_sync();
-      // dK and dV are out of tensor memory: the next item's first products may overwrite them
-      if (n_iter > 0) mbar_arrive(&sh.acc_free);
-      if (tid == 0) tma_store_wait_read();
-      named_barrier(4, kComputeThreads);
     } else {
 #pragma unroll 1
     for (int which = 0; which < 2; ++which) {
@@ -837,6 +878,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     g0 += n_iter;
     item_no = next_no;
     }
+    if (ds_stage_busy && tid == 0) tma_store_wait_read();   // shared memory must outlive the last store's read of it
   }
 
   linger_after_abort(abort_flag);
