@@ -49,6 +49,13 @@ constexpr int kBwdUnitGroup = 8;        // (batch, head) slices whose thread blo
 // 256 x 152 + 128 x 152 + 128 x 56 = 65536.
 constexpr int kRegsCompute = 152, kRegsDrain = 152, kRegsControl = 56;
 
+// One work item: a 128-row K/V tile of one (batch, key/value head) slice and the Q tiles that touch it.
+struct BwdItem {
+  int b, h_kv, bh_kv, j;
+  int i_lo, n_per, n_iter;     // first Q tile, Q tiles per query head, steps (n_per x query heads of the group)
+  int kv_len;
+};
+
 struct BwdShared {
   uint64_t item_full[2];         // producer -> everyone: the number of the CTA's next work item is in item[]
   uint64_t item_empty[2];        // everyone -> producer: the slot has been read by the MMA, drain and compute threads
@@ -69,6 +76,7 @@ struct BwdShared {
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   int item[2];
+  BwdItem decoded[2];            // the same two items, decoded by the producer (see next_item)
   alignas(16) float lse2[2][kTile];   // L * log2(e) per query of the tile (+inf for rows past S_q); read as float4
   alignas(16) float delta[2][kTile];
 };
@@ -137,12 +145,6 @@ __device__ __noinline__ void mask_prepass(const ScoreMods& mods, uint32_t t_st, 
   tmem_wait_st();
 }
 
-// One work item: a 128-row K/V tile of one (batch, key/value head) slice and the Q tiles that touch it.
-struct BwdItem {
-  int b, h_kv, bh_kv, j;
-  int i_lo, n_per, n_iter;     // first Q tile, Q tiles per query head, steps (n_per x query heads of the group)
-  int kv_len;
-};
 
 // Work item number -> item.  Items are numbered so that, inside a group of kBwdUnitGroup slices, the heaviest
 // K/V tiles of ALL slices come first (under a causal mask tile 0 walks every Q tile, the last tile one): the CTAs take
@@ -180,13 +182,13 @@ __device__ __forceinline__ BwdItem decode_item(const BwdParams& p, int w) {
   return it;
 }
 
-// Every role learns the number of its CTA's k-th work item here.  This wait does not look at the abort flag: the
-// producer's own waits are all bounded, so it always gets to publish the next number (after a failure: the end
-// marker), and all threads of a role must see the SAME number -- their loops, named barriers and warp-collective
-// instructions depend on it.  Its own limit is generous and is not expected to be reached.
-__device__ __forceinline__ int next_item(uint64_t* item_full, uint64_t* item_empty, const int* item, int k,
-                                         volatile uint32_t* abort_flag, unsigned int* status) {
-  uint64_t* bar = &item_full[k & 1];
+// Every role learns its CTA's k-th work item here: its number and, decoded by the producer (the integer divisions of
+// decode_item are not repeated by 400 threads between two items), what it stands for.  This wait does not look at the
+// abort flag: the producer's own waits are all bounded, so it always gets to publish the next item (after a failure:
+// the end marker), and all threads of a role must see the SAME item -- their loops, named barriers and
+// warp-collective instructions depend on it.  Its own limit is generous and is not expected to be reached.
+__device__ __forceinline__ int next_item(BwdShared& sh, int k, volatile uint32_t* abort_flag, unsigned int* status, BwdItem& out) {
+  uint64_t* bar = &sh.item_full[k & 1];
   const uint32_t parity = (k >> 1) & 1;
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
@@ -196,8 +198,9 @@ __device__ __forceinline__ int next_item(uint64_t* item_full, uint64_t* item_emp
       break;
     }
   }
-  const int w = item[k & 1];
-  mbar_arrive(&item_empty[k & 1]);     // the slot may be reused once every consumer has read it
+  const int w = sh.item[k & 1];
+  out = sh.decoded[k & 1];                // (stale behind the end marker: never looked at)
+  mbar_arrive(&sh.item_empty[k & 1]);     // the slot may be reused once every consumer has read it
   return w;
 }
 
@@ -276,11 +279,30 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_do);
         prefetch_tmap(&p.map_dq);
         int g0 = 0, live = 0;
-        int w = static_cast<int>(atomicAdd(p.work_counter, 1u));
-        sh.item[0] = w;
-        mbar_arrive(&sh.item_full[0]);
-        for (int k = 0; w < total_items; ++k) {
-          const BwdItem it = decode_item(p, w);
+        // The item after the current one is claimed and published while the loads of the current item's last step but
+        // one go out: late enough that no CTA sits on an unstarted item for long (that unbalances the end of the
+        // kernel when a CTA has only a handful of items), early enough that the other roles know it before they
+        // finish the current item (the compute warps request its first statistics at the end of the last step) and
+        // that the counter's latency -- a global atomic next to 148 SMs' reduce traffic -- is not on their path.
+        int w_cur = static_cast<int>(atomicAdd(p.work_counter, 1u));
+        int w_nxt = total_items;
+        auto publish = [&](int slot, int w) {
+          sh.item[slot] = w;
+          if (w < total_items) sh.decoded[slot] = decode_item(p, w);
+          mbar_arrive(&sh.item_full[slot]);      // (release: the stores above are visible to whoever sees the phase)
+        };
+        publish(0, w_cur);
+        for (int k = 0; w_cur < total_items; ++k) {
+          const BwdItem it = sh.decoded[k & 1];  // (slot k & 1 is rewritten for item k + 2 at the earliest: next round)
+          bool published = false;
+          // the next item goes into the other slot once every consumer has read item k-1 out of it; after a failure
+          // the end marker, so that every role leaves its loop at the same item
+          auto publish_next = [&]() {
+            if (k >= 1) mbar_wait(&sh.item_empty[(k + 1) & 1], ((k - 1) >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
+            w_nxt = *abort_flag == 0u ? static_cast<int>(atomicAdd(p.work_counter, 1u)) : total_items;
+            publish((k + 1) & 1, w_nxt);
+            published = true;
+          };
           if (it.n_iter > 0 && *abort_flag == 0u) {
             // K and V of the previous item are free once all of its products have finished
             if (live > 0) mbar_wait(&sh.kv_empty, (live - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
@@ -302,17 +324,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
               mbar_expect_tx(&sh.do_full, kTileBytes);
               for (int nb = 0; nb < NB; ++nb)
                 tma_load_4d(sDO + nb * 16384, &p.map_do, &sh.do_full, nb * 64, i * kTile, h, it.b);
+              if (n == (it.n_iter >= 2 ? it.n_iter - 2 : 0)) publish_next();
             }
             g0 += it.n_iter;
             ++live;
           }
-          // the next item, once every consumer has read item k-1 out of the slot it goes into (items of one or two
-          // steps let this thread run ahead); after a failure the end marker, so that every role leaves its loop at
-          // the same item
-          if (k >= 1) mbar_wait(&sh.item_empty[(k + 1) & 1], ((k - 1) >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_SYNC);
-          w = *abort_flag == 0u ? static_cast<int>(atomicAdd(p.work_counter, 1u)) : total_items;
-          sh.item[(k + 1) & 1] = w;
-          mbar_arrive(&sh.item_full[(k + 1) & 1]);
+          if (!published) publish_next();
+          w_cur = w_nxt;
         }
       }
     } else if (warp == kMmaWarp) {
@@ -345,9 +363,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
 
         int g0 = 0, live = 0;
         for (int k = 0;; ++k) {
-          const int w = next_item(sh.item_full, sh.item_empty, sh.item, k, abort_flag, p.status);
+          BwdItem it;
+          const int w = next_item(sh, k, abort_flag, p.status, it);
           if (w >= total_items) break;
-          const BwdItem it = decode_item(p, w);
           if (it.n_iter == 0) continue;
           const int n_iter = it.n_iter;
           mbar_wait(&sh.kv_full, live & 1, abort_flag, p.status, DEV_TIMEOUT_TMA);
@@ -414,9 +432,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
     mbar_arrive(&sh.do_full);              // the first step of the kernel has no dQ before it to wait for
     int g0 = 0;
     for (int k = 0;; ++k) {
-    const int w = next_item(sh.item_full, sh.item_empty, sh.item, k, abort_flag, p.status);
+    BwdItem it;
+    const int w = next_item(sh, k, abort_flag, p.status, it);
     if (w >= total_items) break;
-    const BwdItem it = decode_item(p, w);
     const int b = it.b, j = it.j, kv_len = it.kv_len;
     auto head_of = [&](int n) { return it.h_kv * p.kv_group + n / max(it.n_per, 1); };
     auto tile_of = [&](int n) { return it.i_lo + n % max(it.n_per, 1); };
@@ -559,10 +577,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
           pre_bias = __float_as_uint(mods.alibi_slopes[h0]);
       }
     };
-    int item_no = next_item(sh.item_full, sh.item_empty, sh.item, 0, abort_flag, p.status);
-    if (item_no < total_items) request_first(decode_item(p, item_no));
+    BwdItem it_next;
+    int item_no = next_item(sh, 0, abort_flag, p.status, it_next);
+    if (item_no < total_items) request_first(it_next);
     for (int k = 0; item_no < total_items; ++k) {
-    const BwdItem it = decode_item(p, item_no);
+    const BwdItem it = it_next;
+    int next_no = total_items;
+    bool next_known = false;
     const int b = it.b, j = it.j, kv_len = it.kv_len, i_lo = it.i_lo, n_per = it.n_per, n_iter = it.n_iter;
     const int bh_kv = it.bh_kv;
     auto head_of = [&](int n) { return it.h_kv * p.kv_group + n / max(n_per, 1); };
@@ -773,16 +794,24 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&sh.ds_ready);
-
+      // The next item has been published since this item's first loads went out: learn it one step before the end and
+      // request what its first step needs from global memory now, so that those loads return while the last products
+      // of this item finish -- not behind the write-out, whose proxy fence would wait for them.
+      if (n + 1 == n_iter) {
+        next_no = next_item(sh, k + 1, abort_flag, p.status, it_next);
+        next_known = true;
+        if (next_no < total_items) request_first(it_next);
+      }
     }
 
     // epilogue: dK (scaled) and dV rows of this tile; each half writes its half of head_dim.
     // (the tensor-memory loads are warp-collective: every lane runs them, only the stores are guarded)
     if (n_iter > 0) mbar_wait(&sh.dq_full, (g0 + n_iter - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_MMA);
     tc_fence_after_sync();
-    // the next item (the producer published it while this item's last tiles were loading): its first loads go out now
-    const int next_no = next_item(sh.item_full, sh.item_empty, sh.item, k + 1, abort_flag, p.status);
-    if (next_no < total_items) request_first(decode_item(p, next_no));
+    if (!next_known) {      // (an item without steps)
+      next_no = next_item(sh, k + 1, abort_flag, p.status, it_next);
+      if (next_no < total_items) request_first(it_next);
+    }
     const bool row_ok = kv_idx < p.S_k;
     const int64_t row_off = (static_cast<int64_t>(bh_kv) * p.S_k + kv_idx) * p.D;
     if (!p.grads_f32) {
