@@ -859,23 +859,23 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
         ds_stage_busy = true;
       }
     } else {
+      // fp32 gradients (what the reference's grad primitive returns): each thread stores its key row's half of the
+      // 128 x D fp32 tiles directly (a tile is 64 KB: it would take the staging area twice)
 #pragma unroll 1
-    for (int which = 0; which < 2; ++which) {
-      const uint32_t t_src = tmem + lane_base + (which == 0 ? kColDK : kColDV);
-      const float mul = which == 0 ? p.scale : 1.0f;
-      void* out = which == 0 ? p.dk : p.dv;
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t t_src = tmem + lane_base + (which == 0 ? kColDK : kColDV);
+        const float mul = which == 0 ? p.scale : 1.0f;
+        float* dst = reinterpret_cast<float*>(which == 0 ? p.dk : p.dv) + row_off;
 #pragma unroll 1
-      for (int cq = 0; cq < kChunks / 2; ++cq) {
-        const int c = hf * (kChunks / 2) + cq;
-        uint32_t v[32];
-        if (n_iter > 0) { tmem_ld32(t_src + c * 32, v); tmem_wait_ld(); }
-        else {
+        for (int cq = 0; cq < kChunks / 2; ++cq) {
+          const int c = hf * (kChunks / 2) + cq;
+          uint32_t v[32];
+          if (n_iter > 0) { tmem_ld32(t_src + c * 32, v); tmem_wait_ld(); }
+          else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] = 0u;
-        }
-        if (!row_ok) continue;
-        if (p.grads_f32) {
-          float* dst = reinterpret_cast<float*>(out) + row_off;
+            for (int e = 0; e < 32; ++e) v[e] = 0u;
+          }
+          if (!row_ok) continue;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const int col = c * 32 + g * 4;
@@ -884,25 +884,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_kernel(const __grid_con
                   make_float4(__uint_as_float(v[4 * g]) * mul, __uint_as_float(v[4 * g + 1]) * mul,
                               __uint_as_float(v[4 * g + 2]) * mul, __uint_as_float(v[4 * g + 3]) * mul);
           }
-        } else {
-          uint8_t* dst = reinterpret_cast<uint8_t*>(out) + row_off * 2;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = c * 32 + g * 8;
-            if (col + 8 <= p.D) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                w[e] = pack2<BF16>(__uint_as_float(v[8 * g + 2 * e]) * mul, __uint_as_float(v[8 * g + 2 * e + 1]) * mul);
-              *reinterpret_cast<uint4*>(dst + col * 2) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          }
         }
       }
-    }
-    tc_fence_before_sync();
-    // dK and dV are out of tensor memory: the next item's first products may overwrite them
-    if (n_iter > 0) mbar_arrive(&sh.acc_free);
+      tc_fence_before_sync();
+      // dK and dV are out of tensor memory: the next item's first products may overwrite them
+      if (n_iter > 0) mbar_arrive(&sh.acc_free);
     }
     g0 += n_iter;
     item_no = next_no;
