@@ -21,6 +21,10 @@
 // out of its columns, dV as soon as P^T is written (the compute warps go on to dS^T meanwhile), S^T
 // of the next tile right behind it.  The compute warps never wait for dQ: the drain warpgroup takes
 // it through a staging area in shared memory into the fp32 accumulator with TMA reduce-add.
+// At the end of an item 16-bit dK and dV leave through shared memory and TMA stores, dK by the compute
+// warps (through the dS^T tile) and dV by the drain warps (through their staging area) at the same
+// time; fp32 gradients are stored directly.  The producer hands the items to the other roles decoded,
+// through a two-slot mailbox, one step before the current item ends.
 //
 // Follows the reference's backward (train/acctransformer/flash_attention/ops/flash_attention/
 // flash_attention_bwd.py:259-415): K/V tile outer, Q tile inner, P recomputed from L, D = rowsum(dO*O)
